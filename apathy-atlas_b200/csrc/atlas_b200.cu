@@ -1,0 +1,384 @@
+// C ABI of the B200 NVFP4 + multi-LoRA linear path: argument validation, variant dispatch and
+// kernel launches.  Single translation unit (the kernels share one device status word).
+//
+// Host-side operator layer (namespace atlas::ops) mirrors the reference's launch wrappers:
+//   ops::apply_lora_bgmv   <- crates/spark-model/src/layers/ops/lora_delta.rs:269-314
+//   ops::apply_lora_delta  <- crates/spark-model/src/layers/ops/lora_delta.rs:145-235
+//   ops::w4a16_gemm        <- crates/spark-model/src/layers/ops/gemm_dense.rs:258-281
+//   ops::nvfp4_lora_linear    (fused; new)
+// Like them it only launches: no allocation, no synchronisation, no host read of device data.
+#include "atlas_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "kernel_tc.cuh"
+#include "kernels_simt.cuh"
+
+namespace atlas {
+
+static thread_local int t_last_variant = ATLAS_B200_VARIANT_NONE;
+
+static inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? ATLAS_B200_OK : ATLAS_B200_ERR_CUDA_BASE - int(e); }
+static inline int launch_status() { return cuda_status(cudaGetLastError()); }
+static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// ---------------------------------------------------------------------------------------------
+// device capability and the tensor-map encoder (resolved from the driver at first use; the
+// library does not link libcuda)
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct Runtime {
+    bool sm100 = false;
+    EncodeTiledFn encode = nullptr;
+    bool tc_attr_set[5] = {false, false, false, false, false};
+};
+
+static Runtime& runtime() {
+    static Runtime rt;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return;
+        int major = 0;
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        rt.sm100 = (major == 10);
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            rt.encode = reinterpret_cast<EncodeTiledFn>(fn);
+    });
+    return rt;
+}
+
+static bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem, const void* base, uint64_t inner,
+                      uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+                      CUtensorMapSwizzle swz) {
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    (void)elem;
+    return runtime().encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------------------------
+// launches
+// ---------------------------------------------------------------------------------------------
+namespace ops {
+
+static int launch_shrink(const ShrinkParams& p, uint32_t n_slots, cudaStream_t st) {
+    if (p.M == 0 || p.max_rank == 0) return ATLAS_B200_OK;
+    dim3 grid(n_slots, (p.max_rank + SHRINK_RT - 1) / SHRINK_RT, (p.M + SHRINK_TC - 1) / SHRINK_TC);
+    if (grid.y > 65535 || grid.z > 65535) return ATLAS_B200_ERR_LIMIT;
+    lora_shrink_grouped_kernel<<<grid, SHRINK_THREADS, 0, st>>>(p);
+    return launch_status();
+}
+
+static int launch_expand(const ExpandParams& p, cudaStream_t st) {
+    if (p.M == 0 || p.n_out == 0) return ATLAS_B200_OK;
+    if (p.max_rank > EXPAND_MAX_RANK) return ATLAS_B200_ERR_LIMIT;
+    dim3 grid((p.n_out + EXPAND_OUTS - 1) / EXPAND_OUTS, (p.M + EXPAND_ROWS - 1) / EXPAND_ROWS);
+    if (grid.y > 65535) return ATLAS_B200_ERR_LIMIT;
+    lora_expand_fold_kernel<<<grid, EXPAND_OUTS, 0, st>>>(p);
+    return launch_status();
+}
+
+int apply_lora_bgmv(const void* x, const int32_t* seq_slot, const uint64_t* a_table, const uint64_t* b_table,
+                    const float* scale_table, void* base_out, void* lora_xa, uint32_t n, uint32_t k_in,
+                    uint32_t n_out, uint32_t max_rank, uint32_t x_row_stride, uint32_t out_row_stride,
+                    uint32_t max_loras, cudaStream_t st) {
+    if (n == 0) return ATLAS_B200_OK;
+    if (!x || !seq_slot || !a_table || !b_table || !scale_table || !base_out || !lora_xa) return ATLAS_B200_ERR_NULL;
+    if (k_in == 0 || n_out == 0 || max_rank == 0 || max_loras == 0) return ATLAS_B200_ERR_DIMS;
+    if (x_row_stride < k_in || out_row_stride < n_out) return ATLAS_B200_ERR_DIMS;
+    if (max_loras > 65535 || max_rank > EXPAND_MAX_RANK) return ATLAS_B200_ERR_LIMIT;
+    if (!aligned(x, 2) || !aligned(base_out, 2) || !aligned(lora_xa, 2)) return ATLAS_B200_ERR_ALIGN;
+
+    ShrinkParams sp{};
+    sp.x = static_cast<const uint16_t*>(x);
+    sp.seq_slot = seq_slot;
+    sp.a_table = a_table;
+    sp.b_table = nullptr;            // the reference's shrink looks at the A entry only (lora_bgmv.cu:63-65)
+    sp.out = static_cast<uint16_t*>(lora_xa);
+    sp.M = n; sp.k_in = k_in; sp.max_rank = max_rank; sp.x_row_stride = x_row_stride; sp.max_loras = max_loras;
+    sp.post = 0.0f;
+    int rc = launch_shrink(sp, max_loras, st);
+    if (rc) return rc;
+
+    ExpandParams ep{};
+    ep.xa = static_cast<const uint16_t*>(lora_xa);
+    ep.seq_slot = seq_slot;
+    ep.a_table = a_table;            // a row whose shrink was skipped has no valid xa: skip its expand too
+    ep.b_table = b_table;
+    ep.scale_table = scale_table;
+    ep.out = static_cast<uint16_t*>(base_out);
+    ep.M = n; ep.n_out = n_out; ep.max_rank = max_rank; ep.out_row_stride = out_row_stride; ep.max_loras = max_loras;
+    return launch_expand(ep, st);
+}
+
+int apply_lora_delta(const void* x, const void* a, const void* b, float scale, void* base_out, void* lora_xa,
+                     void* lora_delta, uint32_t m, uint32_t k_in, uint32_t n_out, uint32_t max_rank, cudaStream_t st) {
+    if (m == 0) return ATLAS_B200_OK;
+    if (!x || !a || !b || !base_out || !lora_xa) return ATLAS_B200_ERR_NULL;
+    if (k_in == 0 || n_out == 0 || max_rank == 0) return ATLAS_B200_ERR_DIMS;
+    if (max_rank > EXPAND_MAX_RANK) return ATLAS_B200_ERR_LIMIT;
+
+    ShrinkParams sp{};
+    sp.x = static_cast<const uint16_t*>(x);
+    sp.a_uniform = static_cast<const uint16_t*>(a);
+    sp.out = static_cast<uint16_t*>(lora_xa);
+    sp.M = m; sp.k_in = k_in; sp.max_rank = max_rank; sp.x_row_stride = k_in; sp.max_loras = 1;
+    int rc = launch_shrink(sp, 1, st);
+    if (rc) return rc;
+
+    ExpandParams ep{};
+    ep.xa = static_cast<const uint16_t*>(lora_xa);
+    ep.b_uniform = static_cast<const uint16_t*>(b);
+    ep.scale_uniform = scale;
+    ep.out = static_cast<uint16_t*>(base_out);
+    ep.delta_out = static_cast<uint16_t*>(lora_delta);
+    ep.M = m; ep.n_out = n_out; ep.max_rank = max_rank; ep.out_row_stride = n_out; ep.max_loras = 1;
+    return launch_expand(ep, st);
+}
+
+static int launch_simt_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
+    SimtLinearParams p{};
+    p.x = static_cast<const uint16_t*>(d.x);
+    p.w_packed = static_cast<const uint8_t*>(d.w_packed);
+    p.w_scale = static_cast<const uint8_t*>(d.w_scale);
+    p.w_bf16 = static_cast<const uint16_t*>(d.w_bf16);
+    p.y = static_cast<uint16_t*>(d.y);
+    p.M = d.m; p.N = d.n; p.K = d.k; p.x_row_stride = d.x_row_stride; p.out_row_stride = d.out_row_stride;
+    p.scale2 = d.w_bf16 ? 1.0f : d.scale2;
+    dim3 grid((d.n + SIMT_TF - 1) / SIMT_TF, (d.m + SIMT_TM - 1) / SIMT_TM);
+    if (grid.y > 65535) return ATLAS_B200_ERR_LIMIT;
+    linear_simt_kernel<<<grid, 256, 0, st>>>(p);
+    return launch_status();
+}
+
+// Shapes the tcgen05 path takes.  Everything here is a property of host-visible arguments.
+static bool tc_eligible(const atlas_b200_linear_desc& d) {
+    Runtime& rt = runtime();
+    if (!rt.sm100 || !rt.encode) return false;
+    if (d.w_bf16) return false;                                   // dense base: CUDA-core path
+    if (d.k % tc::KRAW != 0) return false;                        // TMA row strides of codes and scales: 16-byte multiples
+    if (d.x_row_stride % 8 != 0) return false;
+    if (!aligned(d.x, 16) || !aligned(d.w_packed, 16) || !aligned(d.w_scale, 16)) return false;
+    if (d.seq_slot) {
+        if (d.max_rank > tc::MAX_RANK_TC || d.max_rank % 8 != 0) return false;
+        if (d.max_loras > tc::MAX_LORAS_TC) return false;
+        if (!aligned(d.lora_t, 16)) return false;
+    }
+    if (!(d.scale2 != 0.0f) || !std::isfinite(d.scale2)) return false;
+    return true;
+}
+
+template <int MT>
+static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, cudaStream_t st) {
+    using C = tc::Cfg<MT>;
+    Runtime& rt = runtime();
+    if (!rt.tc_attr_set[slot_idx]) {
+        cudaError_t e = cudaFuncSetAttribute(tc::nvfp4_lora_linear_tc_kernel<MT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return cuda_status(e);
+        rt.tc_attr_set[slot_idx] = true;
+    }
+    CUtensorMap map_x, map_w, map_s;
+    if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.x, d.k, d.m, uint64_t(d.x_row_stride) * 2, tc::KB, MT,
+                   CU_TENSOR_MAP_SWIZZLE_128B))
+        return ATLAS_B200_ERR_DIMS;
+    if (!encode_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.w_packed, d.k / 2, d.n, d.k / 2, tc::KRAW / 2, tc::FT,
+                   CU_TENSOR_MAP_SWIZZLE_128B))
+        return ATLAS_B200_ERR_DIMS;
+    if (!encode_2d(&map_s, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.w_scale, d.k / 16, d.n, d.k / 16, tc::KRAW / 16, tc::FT,
+                   CU_TENSOR_MAP_SWIZZLE_NONE))
+        return ATLAS_B200_ERR_DIMS;
+
+    tc::Params p{};
+    p.seq_slot = d.seq_slot;
+    p.a_table = d.a_table;
+    p.b_table = d.b_table;
+    p.rank_table = d.rank_table;
+    p.t = static_cast<const uint16_t*>(d.lora_t);
+    p.y = static_cast<uint16_t*>(d.y);
+    p.M = d.m; p.N = d.n; p.K = d.k; p.out_row_stride = d.out_row_stride;
+    p.max_loras = d.max_loras; p.max_rank = d.max_rank;
+    p.out_scale = d.scale2 * kWeightPreScale;
+    dim3 grid((d.n + tc::FT - 1) / tc::FT, (d.m + MT - 1) / MT);
+    if (grid.y > 65535) return ATLAS_B200_ERR_LIMIT;
+    tc::nvfp4_lora_linear_tc_kernel<MT><<<grid, tc::NUM_THREADS, C::SMEM_BYTES, st>>>(map_x, map_w, map_s, p);
+    return launch_status();
+}
+
+static int validate_linear(const atlas_b200_linear_desc& d) {
+    if (!d.x || !d.y) return ATLAS_B200_ERR_NULL;
+    if (!d.w_bf16 && (!d.w_packed || !d.w_scale)) return ATLAS_B200_ERR_NULL;
+    if (d.k == 0 || d.n == 0) return ATLAS_B200_ERR_DIMS;
+    if (!d.w_bf16 && d.k % 16 != 0) return ATLAS_B200_ERR_DIMS;   // NVFP4 scale groups are 16 wide
+    if (d.x_row_stride < d.k || d.out_row_stride < d.n) return ATLAS_B200_ERR_DIMS;
+    if (d.seq_slot) {
+        if (!d.a_table || !d.b_table || !d.scale_table || !d.lora_t) return ATLAS_B200_ERR_NULL;
+        if (d.max_loras == 0 || d.max_rank == 0) return ATLAS_B200_ERR_DIMS;
+        if (d.max_loras > 65535 || d.max_rank > EXPAND_MAX_RANK) return ATLAS_B200_ERR_LIMIT;
+    }
+    if ((d.flags & ATLAS_B200_FLAG_FORCE_SIMT) && (d.flags & ATLAS_B200_FLAG_FORCE_TCGEN05)) return ATLAS_B200_ERR_DIMS;
+    return ATLAS_B200_OK;
+}
+
+int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
+    int rc = validate_linear(d);
+    if (rc) return rc;
+    t_last_variant = ATLAS_B200_VARIANT_NONE;
+    if (d.m == 0) return ATLAS_B200_OK;
+
+    const bool staged = (d.flags & ATLAS_B200_FLAG_STAGED_LORA) != 0;
+    bool use_tc = !(d.flags & ATLAS_B200_FLAG_FORCE_SIMT) && !staged && tc_eligible(d);
+    if (!use_tc && (d.flags & ATLAS_B200_FLAG_FORCE_TCGEN05)) return ATLAS_B200_ERR_DIMS;
+
+    if (use_tc) {
+        if (d.seq_slot) {
+            // shrink first: t = scale_s / (scale2 * 2^8) * (A_s x), the unit of the MMA accumulator
+            ShrinkParams sp{};
+            sp.x = static_cast<const uint16_t*>(d.x);
+            sp.seq_slot = d.seq_slot;
+            sp.a_table = d.a_table;
+            sp.b_table = d.b_table;
+            sp.scale_table = d.scale_table;
+            sp.rank_table = d.rank_table;
+            sp.out = static_cast<uint16_t*>(d.lora_t);
+            sp.M = d.m; sp.k_in = d.k; sp.max_rank = d.max_rank; sp.x_row_stride = d.x_row_stride; sp.max_loras = d.max_loras;
+            sp.post = 1.0f / (d.scale2 * kWeightPreScale);
+            rc = launch_shrink(sp, d.max_loras, st);
+            if (rc) return rc;
+        }
+        if (d.m <= 16) rc = launch_tc<16>(d, 0, st);
+        else if (d.m <= 32) rc = launch_tc<32>(d, 1, st);
+        else if (d.m <= 64) rc = launch_tc<64>(d, 2, st);
+        else if (d.m <= 128) rc = launch_tc<128>(d, 3, st);
+        else rc = launch_tc<256>(d, 4, st);
+        if (rc == ATLAS_B200_OK) t_last_variant = ATLAS_B200_VARIANT_TCGEN05;
+        return rc;
+    }
+
+    // CUDA-core path: base linear, then the reference's two-stage LoRA in place
+    rc = launch_simt_linear(d, st);
+    if (rc) return rc;
+    if (d.seq_slot) {
+        ShrinkParams sp{};
+        sp.x = static_cast<const uint16_t*>(d.x);
+        sp.seq_slot = d.seq_slot;
+        sp.a_table = d.a_table;
+        sp.b_table = d.b_table;
+        sp.rank_table = d.rank_table;
+        sp.out = static_cast<uint16_t*>(d.lora_t);
+        sp.M = d.m; sp.k_in = d.k; sp.max_rank = d.max_rank; sp.x_row_stride = d.x_row_stride; sp.max_loras = d.max_loras;
+        sp.post = 0.0f;
+        rc = launch_shrink(sp, d.max_loras, st);
+        if (rc) return rc;
+        ExpandParams ep{};
+        ep.xa = static_cast<const uint16_t*>(d.lora_t);
+        ep.seq_slot = d.seq_slot;
+        ep.a_table = d.a_table;
+        ep.b_table = d.b_table;
+        ep.scale_table = d.scale_table;
+        ep.out = static_cast<uint16_t*>(d.y);
+        ep.M = d.m; ep.n_out = d.n; ep.max_rank = d.max_rank; ep.out_row_stride = d.out_row_stride; ep.max_loras = d.max_loras;
+        rc = launch_expand(ep, st);
+        if (rc) return rc;
+    }
+    t_last_variant = ATLAS_B200_VARIANT_SIMT;
+    return ATLAS_B200_OK;
+}
+
+}  // namespace ops
+}  // namespace atlas
+
+// =============================================================================================
+// extern "C"
+// =============================================================================================
+using namespace atlas;
+
+extern "C" {
+
+int atlas_b200_lora_bgmv(const void* x, const int32_t* seq_slot, const uint64_t* a_table, const uint64_t* b_table,
+                         const float* scale_table, void* base_out, void* lora_xa, uint32_t n, uint32_t k_in,
+                         uint32_t n_out, uint32_t max_rank, uint32_t x_row_stride, uint32_t out_row_stride,
+                         uint32_t max_loras, void* stream) {
+    return ops::apply_lora_bgmv(x, seq_slot, a_table, b_table, scale_table, base_out, lora_xa, n, k_in, n_out, max_rank,
+                                x_row_stride, out_row_stride, max_loras, static_cast<cudaStream_t>(stream));
+}
+
+int atlas_b200_lora_delta(const void* x, const void* a, const void* b, float scale, void* base_out, void* lora_xa,
+                          void* lora_delta, uint32_t m, uint32_t k_in, uint32_t n_out, uint32_t max_rank, void* stream) {
+    return ops::apply_lora_delta(x, a, b, scale, base_out, lora_xa, lora_delta, m, k_in, n_out, max_rank,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int atlas_b200_w4a16_gemm(const void* a_bf16, const void* b_packed, const void* b_scale, float scale2, void* c_bf16,
+                          uint32_t m, uint32_t n, uint32_t k, void* ws, size_t ws_bytes, void* stream) {
+    (void)ws; (void)ws_bytes;
+    atlas_b200_linear_desc d;
+    std::memset(&d, 0, sizeof(d));
+    d.x = a_bf16; d.m = m; d.k = k; d.x_row_stride = k;
+    d.n = n; d.w_packed = b_packed; d.w_scale = b_scale; d.scale2 = scale2;
+    d.y = c_bf16; d.out_row_stride = n;
+    return ops::nvfp4_lora_linear(d, static_cast<cudaStream_t>(stream));
+}
+
+int atlas_b200_dequant_nvfp4_to_bf16(const void* packed, const void* scales, void* out_bf16, float combined_global,
+                                     uint32_t n, uint32_t k, void* stream) {
+    if (n == 0 || k == 0) return ATLAS_B200_OK;
+    if (!packed || !scales || !out_bf16) return ATLAS_B200_ERR_NULL;
+    if (k % 16 != 0) return ATLAS_B200_ERR_DIMS;
+    if (!aligned(out_bf16, 4)) return ATLAS_B200_ERR_ALIGN;
+    dequant_nvfp4_kernel<<<n, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(packed), static_cast<const uint8_t*>(scales), static_cast<uint16_t*>(out_bf16),
+        combined_global, n, k);
+    return launch_status();
+}
+
+int atlas_b200_quantize_bf16_to_nvfp4(const void* in_bf16, void* packed, void* scales, float scale2, uint32_t n,
+                                      uint32_t k, void* stream) {
+    if (n == 0 || k == 0) return ATLAS_B200_OK;
+    if (!in_bf16 || !packed || !scales) return ATLAS_B200_ERR_NULL;
+    if (k % 16 != 0) return ATLAS_B200_ERR_DIMS;
+    const size_t groups = size_t(n) * (k / 16);
+    const unsigned blocks = unsigned(std::min<size_t>((groups + 255) / 256, 148 * 16));
+    quantize_nvfp4_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(in_bf16), static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales), scale2, n, k);
+    return launch_status();
+}
+
+int atlas_b200_nvfp4_lora_linear(const atlas_b200_linear_desc* desc, void* stream) {
+    if (!desc) return ATLAS_B200_ERR_NULL;
+    return ops::nvfp4_lora_linear(*desc, static_cast<cudaStream_t>(stream));
+}
+
+int atlas_b200_device_status(uint32_t* out_word, int clear) {
+    if (!out_word) return ATLAS_B200_ERR_NULL;
+    cudaError_t e = cudaMemcpyFromSymbol(out_word, g_status_word, sizeof(uint32_t));
+    if (e != cudaSuccess) return cuda_status(e);
+    if (clear) {
+        const uint32_t zero = 0;
+        e = cudaMemcpyToSymbol(g_status_word, &zero, sizeof(uint32_t));
+    }
+    return cuda_status(e);
+}
+
+int atlas_b200_last_variant(void) { return t_last_variant; }
+
+const char* atlas_b200_version(void) { return "atlas_b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

@@ -1,0 +1,493 @@
+// The fused NVFP4 + multi-LoRA linear for sm_100a: TMA-staged tiles, in-kernel E2M1 x E4M3 ->
+// BF16 expansion, tcgen05.mma (kind::f16, BF16 x BF16 -> FP32) into a TMEM accumulator, and the
+// LoRA expand appended as extra K-steps of the same accumulator so y is written exactly once.
+//
+// Orientation ("swap-AB"): the MMA's M dimension (128 TMEM lanes) is a block of 128 OUTPUT
+// FEATURES, its N dimension (TMEM columns) a tile of MT TOKENS, MT in {16..256}.  A decode batch
+// of 16-64 tokens therefore still fills the 128-lane datapath, and a 256-token tile gives the
+// 128 x 256 x 16 instruction shape.
+//
+//   acc[f, m]  = sum_k  W'[f,k] * x[m,k]                      base: W' = E2M1*E4M3*2^-8 (exact BF16)
+//              + sum_g  B_{s_g}[f, j_g..j_g+16) * T_g[m, :]   LoRA: one 16-wide K-step per granule
+//   y[m, f]    = bf16(acc[f,m] * scale2 * 2^8)
+//
+// A granule g is 16 consecutive ranks of one adapter slot that occurs in the token tile; T_g[m,:]
+// is row m of the pre-scaled shrink result t (see lora_shrink_grouped_kernel) where seq_slot[m]
+// equals the granule's slot and zero elsewhere, so adapters never mix across tokens.  Granules
+// are ordered by slot, four to a 64-wide K block; zeros add exactly, so a token's result does not
+// depend on which other tokens share its tile.
+//
+// Warp roles (14 warps, 448 threads):
+//   warp 0        TMA producer: x tiles (SWIZZLE_128B) and raw weight stages (packed codes with
+//                 SWIZZLE_128B + scale bytes) through mbarrier rings
+//   warp 1        TMEM allocation, tcgen05.mma issue, tcgen05.commit
+//   warps 2-5     build the tile's granule list while the main loop runs; then the epilogue:
+//                 tcgen05.ld -> scale -> BF16 -> global
+//   warps 6-13    expand raw NVFP4 into the BF16 MMA operand tile; build the LoRA operand tiles
+//
+// Every wait is bounded: on expiry the waiter records a status code, raises the CTA's abort
+// flag, and all roles fall through to a common teardown that frees TMEM.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace atlas {
+namespace tc {
+
+constexpr int FT = 128;              // features per CTA = UMMA M
+constexpr int KB = 64;               // K elements per MMA stage (one 128-byte swizzle row of BF16)
+constexpr int KRAW = 256;            // K elements per raw weight stage
+constexpr int RAW_STAGES = 2;
+constexpr int RAW_PACKED_BYTES = FT * (KRAW / 2);    // 16 KiB
+constexpr int RAW_SCALE_BYTES = FT * (KRAW / 16);    // 2 KiB
+constexpr int W_TILE_BYTES = FT * KB * 2;            // 16 KiB
+constexpr int NUM_THREADS = 448;
+constexpr int DEQ_WARP0 = 6, DEQ_WARPS = 8, DEQ_THREADS = 256;
+constexpr int EPI_WARP0 = 2, EPI_THREADS = 128;
+constexpr int MAX_LORAS_TC = 4096;
+constexpr int MAX_RANK_TC = 64;
+constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;    // 1 s
+
+template <int MT> struct Cfg {
+    static constexpr int X_TILE_BYTES = MT * KB * 2;
+    static constexpr int STAGES = MT >= 256 ? 3 : (MT >= 128 ? 4 : 6);
+    static constexpr int TMEM_COLS = MT < 32 ? 32 : MT;
+    static constexpr int MAX_GRANULES = MT * (MAX_RANK_TC / 16);
+    // shared memory map (offsets from a 1024-byte aligned base)
+    static constexpr int OFF_X = 0;
+    static constexpr int OFF_W = OFF_X + STAGES * X_TILE_BYTES;
+    static constexpr int OFF_RAWP = OFF_W + STAGES * W_TILE_BYTES;
+    static constexpr int OFF_RAWS = OFF_RAWP + RAW_STAGES * RAW_PACKED_BYTES;
+    static constexpr int OFF_SLOT = OFF_RAWS + RAW_STAGES * RAW_SCALE_BYTES;     // int32[MT]
+    static constexpr int OFF_GRAN = OFF_SLOT + MT * 4;                           // uint16[MAX_GRANULES]
+    static constexpr int OFF_BITMAP = OFF_GRAN + MAX_GRANULES * 2;               // uint32[128]
+    static constexpr int OFF_SCAN = OFF_BITMAP + (MAX_LORAS_TC / 32) * 4;        // uint32[8]
+    static constexpr int OFF_BAR = OFF_SCAN + 64;                                // mbarriers
+    static constexpr int NUM_BARS = 3 * STAGES + 2 * RAW_STAGES + 2;
+    static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;                      // tmem ptr, n_gran, abort
+    static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;                      // + alignment slack
+};
+
+struct Params {
+    const int32_t* seq_slot;       // nullable: base only
+    const uint64_t* a_table;
+    const uint64_t* b_table;
+    const uint32_t* rank_table;    // nullable
+    const uint16_t* t;             // [M, max_rank] pre-scaled shrink result
+    uint16_t* y;
+    uint32_t M, N, K, out_row_stride, max_loras, max_rank;
+    float out_scale;               // scale2 * 2^8
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (this waiter's limit expired, or
+// another role raised the flag).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+                record_status(code);
+                *abort_flag = 1u;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T, BF16 inputs, FP32 accumulate; one thread issues.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrive on an mbarrier once all tcgen05.mma issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 16 consecutive columns of 32-bit TMEM -> 16 registers per thread.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// K-major operand tile, 128-byte rows, SWIZZLE_128B: 8-row groups are 1024 bytes apart.
+// start address >> 4 | LBO (unused for swizzled K-major, 1) | SBO = 1024 B | version 1 | SWIZZLE_128B.
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
+           (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// kind::f16 instruction descriptor: D = F32, A = B = BF16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t make_idesc_bf16(uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// byte offset of logical 16-byte chunk `c` (0..7) of row `r` in a SWIZZLE_128B tile of 128-byte rows
+__device__ __forceinline__ uint32_t sw128_off(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
+
+// ---------------------------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------------------------
+template <int MT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
+                            const __grid_constant__ CUtensorMap map_w,
+                            const __grid_constant__ CUtensorMap map_s,
+                            const Params p) {
+    using C = Cfg<MT>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t x_tile0 = smem_base + C::OFF_X;
+    const uint32_t w_tile0 = smem_base + C::OFF_W;
+    const uint32_t rawp0 = smem_base + C::OFF_RAWP;
+    const uint32_t raws0 = smem_base + C::OFF_RAWS;
+    int32_t* slot_arr = reinterpret_cast<int32_t*>(smem_gen + C::OFF_SLOT);
+    uint16_t* gran = reinterpret_cast<uint16_t*>(smem_gen + C::OFF_GRAN);
+    uint32_t* bitmap = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_BITMAP);
+    uint32_t* scan = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_SCAN);
+    const uint32_t bar0 = smem_base + C::OFF_BAR;
+    // barrier indices
+    const uint32_t BAR_FULL_X = bar0;                                  // [STAGES] TMA -> MMA
+    const uint32_t BAR_FULL_W = bar0 + 8 * C::STAGES;                  // [STAGES] expand warps -> MMA
+    const uint32_t BAR_EMPTY = bar0 + 16 * C::STAGES;                  // [STAGES] MMA -> producers
+    const uint32_t BAR_FULL_RAW = bar0 + 24 * C::STAGES;               // [RAW_STAGES]
+    const uint32_t BAR_EMPTY_RAW = BAR_FULL_RAW + 8 * RAW_STAGES;      // [RAW_STAGES]
+    const uint32_t BAR_ACC = BAR_EMPTY_RAW + 8 * RAW_STAGES;           // accumulator complete
+    const uint32_t BAR_LIST = BAR_ACC + 8;                             // granule list ready
+    volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + C::OFF_MISC);
+    // misc[0] = TMEM base address, misc[1] = granule count, misc[2] = abort flag
+    volatile uint32_t* abort_flag = misc + 2;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t f0 = blockIdx.x * FT;
+    const uint32_t m0 = blockIdx.y * MT;
+    const uint32_t num_kb = (p.K + KB - 1) / KB;
+
+    if (tid == 0) {
+        for (int i = 0; i < C::STAGES; ++i) {
+            mbar_init(BAR_FULL_X + 8 * i, 1);
+            mbar_init(BAR_FULL_W + 8 * i, DEQ_WARPS);
+            mbar_init(BAR_EMPTY + 8 * i, 1);
+        }
+        for (int i = 0; i < RAW_STAGES; ++i) {
+            mbar_init(BAR_FULL_RAW + 8 * i, 1);
+            mbar_init(BAR_EMPTY_RAW + 8 * i, DEQ_WARPS);
+        }
+        mbar_init(BAR_ACC, 1);
+        mbar_init(BAR_LIST, 1);
+        misc[1] = 0;
+        misc[2] = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_base + C::OFF_MISC, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&map_x);
+        tma_prefetch_desc(&map_w);
+        tma_prefetch_desc(&map_s);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_acc = misc[0];
+
+    if (warp == 0) {
+        // ===================================== TMA producer =====================================
+        if (lane == 0) {
+            // activation tiles, one per K block
+            for (uint32_t it = 0; it < num_kb; ++it) {
+                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+                if (!mbar_wait(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER)) break;
+                mbar_arrive_expect_tx(BAR_FULL_X + 8 * s, C::X_TILE_BYTES);
+                tma_load_2d(x_tile0 + s * C::X_TILE_BYTES, &map_x, int32_t(it * KB), int32_t(m0), BAR_FULL_X + 8 * s);
+            }
+        } else if (lane == 1) {
+            // raw weight stages (codes + scale bytes), one per four K blocks, on their own ring so
+            // that they run ahead of the activation tiles
+            const uint32_t num_raw = (num_kb + 3u) / 4u;
+            for (uint32_t ri = 0; ri < num_raw; ++ri) {
+                const uint32_t rs = ri % RAW_STAGES, rph = (ri / RAW_STAGES) & 1u;
+                if (!mbar_wait(BAR_EMPTY_RAW + 8 * rs, rph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER)) break;
+                mbar_arrive_expect_tx(BAR_FULL_RAW + 8 * rs, RAW_PACKED_BYTES + RAW_SCALE_BYTES);
+                tma_load_2d(rawp0 + rs * RAW_PACKED_BYTES, &map_w, int32_t(ri * (KRAW / 2)), int32_t(f0), BAR_FULL_RAW + 8 * rs);
+                tma_load_2d(raws0 + rs * RAW_SCALE_BYTES, &map_s, int32_t(ri * (KRAW / 16)), int32_t(f0), BAR_FULL_RAW + 8 * rs);
+            }
+        }
+    } else if (warp == 1) {
+        // ===================================== MMA issuer =======================================
+        constexpr uint32_t idesc = make_idesc_bf16(MT);
+        uint32_t total_blocks = num_kb;
+        bool ok = true;
+        for (uint32_t it = 0; ok && it < total_blocks; ++it) {
+            const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+            uint32_t ksteps = KB / 16;
+            if (it >= num_kb) {
+                const uint32_t left = misc[1] - (it - num_kb) * 4u;
+                ksteps = left < 4u ? left : 4u;
+            }
+            ok = mbar_wait(BAR_FULL_W + 8 * s, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA);
+            if (ok && it < num_kb) ok = mbar_wait(BAR_FULL_X + 8 * s, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA);
+            if (!ok) break;
+            tcgen05_fence_after();
+            if (lane == 0) {
+                const uint64_t a_desc = make_kmajor_sw128_desc(w_tile0 + s * W_TILE_BYTES);
+                const uint64_t b_desc = make_kmajor_sw128_desc(x_tile0 + s * C::X_TILE_BYTES);
+                for (uint32_t k = 0; k < ksteps; ++k)   // +32 bytes (16 BF16) along K inside the swizzle row
+                    umma_bf16(tmem_acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (it | k) != 0u);
+                umma_commit(BAR_EMPTY + 8 * s);
+            }
+            __syncwarp();
+            if (it + 1 == num_kb) {
+                // base K blocks issued; the LoRA K blocks follow once the granule list is known
+                ok = mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_MMA);
+                if (ok) total_blocks = num_kb + (misc[1] + 3u) / 4u;
+            }
+        }
+        if (ok && lane == 0) umma_commit(BAR_ACC);
+        __syncwarp();
+    } else if (warp < DEQ_WARP0) {
+        // ============================ granule list, then the epilogue ===========================
+        const uint32_t te = tid - EPI_WARP0 * 32;          // 0..127
+        uint32_t n_gran = 0;
+        if (p.seq_slot) {
+            bitmap[te] = 0;                                 // 128 words = 4096 slots
+            named_bar_sync(1, EPI_THREADS);
+            for (uint32_t r = te; r < uint32_t(MT); r += EPI_THREADS) {
+                const uint32_t m = m0 + r;
+                int32_t s = (m < p.M) ? p.seq_slot[m] : -1;
+                if (s >= 0) {
+                    if (uint32_t(s) >= p.max_loras) { record_status(STATUS_SLOT_OUT_OF_RANGE); s = -1; }
+                    else if (p.a_table[s] == 0ull || p.b_table[s] == 0ull) s = -1;
+                }
+                slot_arr[r] = s;
+                if (s >= 0) atomicOr(&bitmap[uint32_t(s) >> 5], 1u << (uint32_t(s) & 31u));
+            }
+            named_bar_sync(1, EPI_THREADS);
+            // thread te owns slots [32 te, 32 te + 32): count its granules, scan, emit in slot order
+            uint32_t word = bitmap[te], cnt = 0;
+            for (uint32_t w = word; w; w &= w - 1) {
+                const uint32_t s = te * 32 + (__ffs(w) - 1);
+                const uint32_t r = p.rank_table ? min(p.rank_table[s], p.max_rank) : p.max_rank;
+                cnt += (r + 15u) / 16u;
+            }
+            uint32_t incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= uint32_t(o)) incl += v;
+            }
+            if (lane == 31) scan[warp - EPI_WARP0] = incl;
+            named_bar_sync(1, EPI_THREADS);
+            uint32_t base = 0;
+            for (uint32_t w = 0; w < warp - EPI_WARP0; ++w) base += scan[w];
+            n_gran = scan[0] + scan[1] + scan[2] + scan[3];
+            uint32_t pos = base + incl - cnt;
+            for (uint32_t w = word; w; w &= w - 1) {
+                const uint32_t s = te * 32 + (__ffs(w) - 1);
+                const uint32_t r = p.rank_table ? min(p.rank_table[s], p.max_rank) : p.max_rank;
+                for (uint32_t g = 0; g < (r + 15u) / 16u; ++g) gran[pos++] = uint16_t((s << 2) | g);
+            }
+            if (te == 0) misc[1] = n_gran;
+            named_bar_sync(1, EPI_THREADS);
+        }
+        if (te == 0) mbar_arrive(BAR_LIST);
+
+        // ---- epilogue: TMEM lane = feature, column = token ----
+        const uint32_t q = warp & 3u;                       // TMEM lane quadrant this warp may read
+        if (mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE)) {
+            tcgen05_fence_after();
+            const uint32_t f = f0 + q * 32 + lane;
+            const float osc = p.out_scale;
+#pragma unroll 1
+            for (uint32_t c0 = 0; c0 < uint32_t(MT); c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem_acc + ((q * 32u) << 16) + c0, v);
+                tmem_ld_wait();
+                if (f < p.N) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t m = m0 + c0 + i;
+                        if (m < p.M) p.y[size_t(m) * p.out_row_stride + f] = f32_to_bf16_bits(__uint_as_float(v[i]) * osc);
+                    }
+                }
+            }
+        }
+    } else {
+        // ========================== NVFP4 -> BF16 operand expansion =============================
+        const uint32_t td = tid - DEQ_WARP0 * 32;           // 0..255
+        const uint32_t row = td & 127u, half = td >> 7;
+        bool ok = true;
+        const uint32_t num_raw = (num_kb + 3u) / 4u;
+        for (uint32_t ri = 0; ok && ri < num_raw; ++ri) {
+            const uint32_t rs = ri % RAW_STAGES, rph = (ri / RAW_STAGES) & 1u;
+            ok = mbar_wait(BAR_FULL_RAW + 8 * rs, rph, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
+            if (!ok) break;
+            const uint4 sc4 = lds128(raws0 + rs * RAW_SCALE_BYTES + row * 16);
+            const uint32_t scw[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                const uint32_t it = ri * 4 + j;
+                if (it >= num_kb) break;
+                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+                ok = mbar_wait(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
+                if (!ok) break;
+                // 32 codes of this row: logical chunk 2j + half of the swizzled 128-byte raw row
+                const uint4 pk = lds128(rawp0 + rs * RAW_PACKED_BYTES + sw128_off(row, 2 * j + half));
+                const uint32_t pw[4] = {pk.x, pk.y, pk.z, pk.w};
+                const uint32_t sbytes = scw[j] >> (16 * half);      // scale bytes 2*half, 2*half+1 of word j
+                const uint32_t mul0 = e4m3_to_bf16x2_shifted(sbytes & 0xFFu);
+                const uint32_t mul1 = e4m3_to_bf16x2_shifted((sbytes >> 8) & 0xFFu);
+                const uint32_t wt = w_tile0 + s * W_TILE_BYTES;
+#pragma unroll
+                for (uint32_t qd = 0; qd < 4; ++qd) {
+                    uint32_t o[4];
+                    e2m1x8_to_bf16x8(pw[qd], qd < 2 ? mul0 : mul1, o);
+                    sts128(wt + sw128_off(row, 4 * half + qd), o[0], o[1], o[2], o[3]);
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR_FULL_W + 8 * s);
+            }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR_EMPTY_RAW + 8 * rs);
+        }
+
+        // ---- LoRA K blocks: A operand = B_s rows, B operand = masked rows of t ----
+        if (ok) ok = mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
+        if (ok) {
+            const uint32_t n_gran = misc[1];
+            const uint32_t f = f0 + row;
+            for (uint32_t lb = 0; ok && lb * 4 < n_gran; ++lb) {
+                const uint32_t it = num_kb + lb;
+                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+                ok = mbar_wait(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
+                if (!ok) break;
+                const uint32_t wt = w_tile0 + s * W_TILE_BYTES;
+                const uint32_t xt = x_tile0 + s * C::X_TILE_BYTES;
+                const uint32_t ng = min(4u, n_gran - lb * 4);
+                for (uint32_t g = 0; g < ng; ++g) {
+                    const uint32_t e = gran[lb * 4 + g];
+                    const uint32_t slot = e >> 2, j0 = (e & 3u) * 16u;
+                    {   // B_s[f, j0 + 8 half .. +8)
+                        uint4 bv = make_uint4(0, 0, 0, 0);
+                        const uint32_t j = j0 + 8 * half;
+                        if (f < p.N && j < p.max_rank)
+                            bv = __ldg(reinterpret_cast<const uint4*>(
+                                reinterpret_cast<const uint16_t*>(p.b_table[slot]) + size_t(f) * p.max_rank + j));
+                        sts128(wt + sw128_off(row, 2 * g + half), bv.x, bv.y, bv.z, bv.w);
+                    }
+                    for (uint32_t task = td; task < uint32_t(MT) * 2; task += DEQ_THREADS) {
+                        const uint32_t r = task >> 1, hh = task & 1u;
+                        uint4 tv = make_uint4(0, 0, 0, 0);
+                        const uint32_t j = j0 + 8 * hh;
+                        if (slot_arr[r] == int32_t(slot) && j < p.max_rank)
+                            tv = *reinterpret_cast<const uint4*>(p.t + size_t(m0 + r) * p.max_rank + j);
+                        sts128(xt + sw128_off(r, 2 * g + hh), tv.x, tv.y, tv.z, tv.w);
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR_FULL_W + 8 * s);
+            }
+        }
+    }
+
+    // ========================================= teardown ==========================================
+    if (*abort_flag) {
+        // give copies that may still be in flight time to land before shared memory is released
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_acc, C::TMEM_COLS);
+    }
+}
+
+}  // namespace tc
+}  // namespace atlas

@@ -1,0 +1,199 @@
+/*
+ * atlas_b200 — C ABI of the B200 (sm_100a) NVFP4 + multi-LoRA linear path.
+ *
+ * Every entry point follows the reference's static-library launcher convention
+ * (crates/spark-runtime/src/cutlass.rs:33-168, cuda/cutlass_nvfp4_gemm.cu:242-343):
+ * plain pointers and sizes, the CUDA stream as `void*` (0 = legacy default stream),
+ * return 0 on success and a negative status otherwise.  All device memory is owned by
+ * the caller and must outlive the call; launchers allocate nothing, never synchronise
+ * and never read device memory on the host, so they can be captured into a CUDA graph
+ * like the reference's launches (crates/spark-model/src/layers/ops/lora_delta.rs:132-137).
+ *
+ * Status codes
+ *      0            success
+ *     -1            bad dimensions / unsupported shape
+ *     -2            workspace too small
+ *     -3            misaligned pointer or stride
+ *     -4            null pointer where one is required
+ *     -5            limit exceeded (max_loras, max_rank, scratch capacity)
+ *     -10 - e       CUDA runtime error e at launch
+ *     -120          library was not built for this GPU architecture
+ */
+#ifndef ATLAS_B200_H
+#define ATLAS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define ATLAS_B200_API __attribute__((visibility("default")))
+#else
+#define ATLAS_B200_API
+#endif
+
+#define ATLAS_B200_OK             0
+#define ATLAS_B200_ERR_DIMS      (-1)
+#define ATLAS_B200_ERR_WORKSPACE (-2)
+#define ATLAS_B200_ERR_ALIGN     (-3)
+#define ATLAS_B200_ERR_NULL      (-4)
+#define ATLAS_B200_ERR_LIMIT     (-5)
+#define ATLAS_B200_ERR_CUDA_BASE (-10)
+#define ATLAS_B200_ERR_ARCH      (-120)
+
+/* which kernel family a call dispatched to (launcher audit; see atlas_b200_last_variant) */
+#define ATLAS_B200_VARIANT_NONE     0
+#define ATLAS_B200_VARIANT_SIMT     1   /* CUDA-core tiles, any shape */
+#define ATLAS_B200_VARIANT_TCGEN05  2   /* TMA + tcgen05.mma + TMEM, LoRA expand in the accumulator */
+
+/* flags of atlas_b200_linear_desc.flags */
+#define ATLAS_B200_FLAG_FORCE_SIMT     1u   /* always take the CUDA-core path */
+#define ATLAS_B200_FLAG_FORCE_TCGEN05  2u   /* fail with -1 instead of falling back */
+#define ATLAS_B200_FLAG_STAGED_LORA    4u   /* reference rounding: base->bf16, then shrink/expand/fold in place */
+
+/* ---------------------------------------------------------------------------------------
+ * Routed multi-adapter LoRA delta over n rows:  out[i,:] += scale_s * (x[i,:] A_s^T) B_s^T,
+ * s = seq_slot[i]; rows with s < 0, or whose slot has a null A/B table entry, are untouched.
+ * Replaces `apply_lora_bgmv` (crates/spark-model/src/layers/ops/lora_delta.rs:269-314) and
+ * its two kernels (kernels/gb10/common/lora_bgmv.cu:50-126, :139-225); argument meaning and
+ * order follow them, strides are in elements.  Rounding boundaries are the reference's:
+ * lora_xa is BF16, the expand result is rounded to BF16 before the scaled fold.
+ *   x [n, x_row_stride] bf16   seq_slot [n] i32   a_table/b_table [max_loras] u64 device addresses
+ *   scale_table [max_loras] f32   base_out [n, out_row_stride] bf16 (in place)
+ *   lora_xa [n, max_rank] bf16 scratch
+ * `max_loras` is the length of the three tables; a slot index >= max_loras is treated as
+ * "no adapter" and recorded in the device status word. */
+ATLAS_B200_API int atlas_b200_lora_bgmv(const void* x, const int32_t* seq_slot,
+                         const uint64_t* a_table, const uint64_t* b_table, const float* scale_table,
+                         void* base_out, void* lora_xa,
+                         uint32_t n, uint32_t k_in, uint32_t n_out, uint32_t max_rank,
+                         uint32_t x_row_stride, uint32_t out_row_stride, uint32_t max_loras,
+                         void* stream);
+
+/* Single adapter on m contiguous rows: base_out += scale * (x a^T) b^T.
+ * Replaces `apply_lora_delta` (crates/spark-model/src/layers/ops/lora_delta.rs:145-235).
+ *   a [max_rank, k_in] bf16, b [n_out, max_rank] bf16 (pool layout, zero padded)
+ *   lora_xa [m, max_rank] bf16 scratch; lora_delta [m, n_out] bf16 scratch (may be null: the
+ *   fold is fused, the buffer is only written when given). */
+ATLAS_B200_API int atlas_b200_lora_delta(const void* x, const void* a, const void* b, float scale,
+                          void* base_out, void* lora_xa, void* lora_delta,
+                          uint32_t m, uint32_t k_in, uint32_t n_out, uint32_t max_rank,
+                          void* stream);
+
+/* Base NVFP4 linear  C[M,N] = A[M,K] * dequant(B)^T * scale2  (BF16 in/out, FP32 accumulate).
+ * Replaces `w4a16_gemm` / `w4a16_gemv` launchers
+ * (crates/spark-model/src/layers/ops/gemm_dense.rs:258-281, quant_dispatch.rs:94-115; kernels
+ * kernels/gb10/common/w4a16_gemm.cu:87-180, w4a16_gemv.cu:62-161).
+ *   b_packed [N, K/2] u8, low nibble = even k;  b_scale [N, K/16] E4M3;  scale2 by value.
+ * `ws` is unused by the current kernels and may be null. */
+ATLAS_B200_API int atlas_b200_w4a16_gemm(const void* a_bf16, const void* b_packed, const void* b_scale,
+                          float scale2, void* c_bf16, uint32_t m, uint32_t n, uint32_t k,
+                          void* ws, size_t ws_bytes, void* stream);
+
+/* Standalone NVFP4 -> BF16 decode, out[n,k] = bf16(E2M1[nib] * (e4m3(scale) * combined_global)).
+ * Replaces `dequant_nvfp4_to_bf16` (kernels/gb10/common/dequant_nvfp4_bf16.cu:50-73). */
+ATLAS_B200_API int atlas_b200_dequant_nvfp4_to_bf16(const void* packed, const void* scales, void* out_bf16,
+                                     float combined_global, uint32_t n, uint32_t k, void* stream);
+
+/* BF16 -> NVFP4 quantiser (per-16 E4M3 scales, E2M1 codes) with a caller-given scale2.
+ * Replaces `quantize_bf16_to_nvfp4` (kernels/gb10/common/quantize_bf16_to_nvfp4.cu:176-243). */
+ATLAS_B200_API int atlas_b200_quantize_bf16_to_nvfp4(const void* in_bf16, void* packed, void* scales,
+                                      float scale2, uint32_t n, uint32_t k, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * The fused layer:  y = dequant_NVFP4(W) x + scale_s B_s (A_s x),  y written once.
+ * New relative to the reference, which issues the base GEMM
+ * (crates/spark-model/src/layers/ops/gemm_dense.rs:258-453) and then apply_lora_bgmv
+ * (lora_delta.rs:269-314) as separate launches over the same tensors; the descriptor
+ * carries exactly their arguments.
+ */
+typedef struct atlas_b200_linear_desc {
+    /* activations */
+    const void*     x;              /* [m, x_row_stride] bf16 */
+    uint32_t        m, k, x_row_stride;
+    /* base weight: NVFP4 (w_packed, w_scale, scale2) or, when w_bf16 != NULL, dense bf16 [n, k] */
+    uint32_t        n;
+    const void*     w_packed;       /* [n, k/2] u8 */
+    const void*     w_scale;        /* [n, k/16] e4m3 */
+    const void*     w_bf16;         /* [n, k] bf16 or NULL */
+    float           scale2;
+    uint32_t        flags;
+    /* routing (seq_slot == NULL: base linear only) */
+    const int32_t*  seq_slot;       /* [m] i32, < 0 = no adapter */
+    const uint64_t* a_table;        /* [max_loras] device addresses of A_s [max_rank, k] bf16, 0 = none */
+    const uint64_t* b_table;        /* [max_loras] device addresses of B_s [n, max_rank] bf16, 0 = none */
+    const float*    scale_table;    /* [max_loras] */
+    const uint32_t* rank_table;     /* [max_loras] true ranks, or NULL (= max_rank everywhere) */
+    uint32_t        max_loras, max_rank;
+    /* output */
+    void*           y;              /* [m, out_row_stride] bf16 */
+    uint32_t        out_row_stride;
+    uint32_t        reserved0;
+    /* scratch: shrink result, [m, max_rank] bf16 */
+    void*           lora_t;
+    void*           ws;             /* reserved, may be NULL */
+    size_t          ws_bytes;
+} atlas_b200_linear_desc;
+
+ATLAS_B200_API int atlas_b200_nvfp4_lora_linear(const atlas_b200_linear_desc* desc, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Column-parallel sharding (split of N over `tp` ranks), as `shard_quantized_nvfp4`
+ * ColumnParallel (crates/spark-model/src/tp_shard/quant_shard.rs:57-90): rank r owns output
+ * rows [r*n/tp, (r+1)*n/tp) of W, of its scales, and of every B_s; scale2, A_s, x are
+ * replicated.  Returns the row range; -1 when n is not divisible as required. */
+ATLAS_B200_API int atlas_b200_column_shard(uint32_t n, uint32_t tp, uint32_t rank, uint32_t* row_begin, uint32_t* row_count);
+
+/* ---------------------------------------------------------------------------------------
+ * LoRA registry: slot math and pool layout (host only, no GPU).
+ */
+typedef struct atlas_b200_model_dims {
+    uint32_t hidden_size, intermediate_size, num_attention_heads, num_key_value_heads, head_dim;
+    uint32_t attn_gated;                 /* q_proj output is [Q|gate] when set */
+    uint32_t num_full_attention_layers;  /* layers that carry LoRA modules */
+} atlas_b200_model_dims;
+
+enum { ATLAS_B200_Q = 0, ATLAS_B200_K, ATLAS_B200_V, ATLAS_B200_O, ATLAS_B200_GATE, ATLAS_B200_UP, ATLAS_B200_DOWN,
+       ATLAS_B200_NUM_MODULES };
+
+/* `build_seq_slot_host` (crates/spark-model/src/lora/slot_math.rs:50-62) */
+ATLAS_B200_API int atlas_b200_build_seq_slot(const int32_t* adapter_slots, size_t n, size_t padded_n, int32_t active, int32_t* out);
+/* `routed_prefill_slot_of` (slot_math.rs:83-90); returns the slot or -1 for None */
+ATLAS_B200_API int32_t atlas_b200_routed_prefill_slot_of(int32_t adapter_slot, size_t active, size_t num_slots);
+/* `PeftAdapterConfig::scaling` (crates/atlas-core/src/config/parsers/lora.rs:70-77) */
+ATLAS_B200_API float atlas_b200_peft_scaling(double lora_alpha, size_t r, int use_rslora);
+/* `LoraModule::dims` (crates/spark-model/src/lora/types.rs:62-74) */
+ATLAS_B200_API int atlas_b200_module_dims(const atlas_b200_model_dims* cfg, int module, size_t* out_dim, size_t* in_dim);
+/* `pool_slot_bytes`, `slot_base_offset`, `module_slot_offsets` (slot_math.rs:109-162) */
+ATLAS_B200_API size_t atlas_b200_pool_slot_bytes(const atlas_b200_model_dims* cfg, size_t max_rank);
+ATLAS_B200_API size_t atlas_b200_slot_base_offset(size_t slot, const atlas_b200_model_dims* cfg, size_t max_rank);
+ATLAS_B200_API int atlas_b200_module_slot_offsets(const atlas_b200_model_dims* cfg, size_t max_rank, size_t layer_ordinal,
+                                   int module, size_t* a_off, size_t* b_off);
+/* One module of `pack_slot` (crates/spark-model/src/lora/loading.rs:160-186) into a host image of
+ * the slot: A [r, in] copied to the head of its [max_rank, in] region, B [out, r] row-repacked
+ * to stride max_rank; pads zeroed. `slot_image` is the slot's byte image (pool_slot_bytes long). */
+ATLAS_B200_API int atlas_b200_pack_module(const atlas_b200_model_dims* cfg, size_t max_rank, size_t layer_ordinal, int module,
+                           const void* a_bf16, const void* b_bf16, size_t r, void* slot_image);
+/* `select_victim_slot` (slot_math.rs:25-38): free-first, else least-recently-used idle slot,
+ * else -1 (pool full).  Arrays describe the cache region only. */
+ATLAS_B200_API int atlas_b200_select_victim_slot(const size_t* slot_index, const uint8_t* filled, const size_t* ref_count,
+                                  const uint64_t* last_used, size_t count);
+
+/* ---------------------------------------------------------------------------------------
+ * Diagnostics.
+ */
+/* Device status word: 0 = clean; otherwise the first problem a kernel recorded (out-of-range
+ * slot index, a bounded wait that expired).  Synchronises the device; not for use during
+ * stream capture.  `clear` != 0 resets it. */
+ATLAS_B200_API int atlas_b200_device_status(uint32_t* out_word, int clear);
+/* Kernel family chosen by the most recent fused / base call on this thread. */
+ATLAS_B200_API int atlas_b200_last_variant(void);
+ATLAS_B200_API const char* atlas_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATLAS_B200_H */
