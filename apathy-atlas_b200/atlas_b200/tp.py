@@ -1,0 +1,78 @@
+"""Column-parallel split of the layer over `tp` ranks (one GPU each).
+
+Rank r owns output rows [r*N/tp, (r+1)*N/tp) of the packed weight, of its block scales and of every
+B_s (contiguous slices, as `shard_quantized_nvfp4` ColumnParallel does for the base weight,
+crates/spark-model/src/tp_shard/quant_shard.rs:57-90); scale2, x, seq_slot, every A_s and the scale
+table are replicated, so the shrink is recomputed on every rank and the only exchange is one
+all-gather of the [M, N/tp] output shards.  The gathered tensor is laid out [tp, M, N/tp]
+(`gathered_to_row_major` gives the [M, N] view).
+"""
+from __future__ import annotations
+
+import copy
+
+import numpy as np
+
+from . import synth
+
+
+def shard_case(case: synth.Case, tp: int, rank: int) -> synth.Case:
+    """Host-side shard of a synthetic case (numpy slices; A and x are shared, not copied)."""
+    if case.N % tp != 0:
+        raise ValueError(f"N={case.N} is not divisible by tp={tp}")
+    n_loc = case.N // tp
+    lo, hi = rank * n_loc, (rank + 1) * n_loc
+    c = copy.copy(case)
+    c.N = n_loc
+    c.name = f"{case.name}/tp{tp}r{rank}"
+    if case.packed is not None:
+        c.packed, c.scales = case.packed[lo:hi], case.scales[lo:hi]
+    if case.w_bf16 is not None:
+        c.w_bf16 = case.w_bf16[lo:hi]
+    c.adapters = [None if a is None else synth.Adapter(a.a, a.b[lo:hi], a.scale, a.rank) for a in case.adapters]
+    return c
+
+
+def gathered_to_row_major(y_all: np.ndarray) -> np.ndarray:
+    """[tp, M, N/tp] (all-gather order) -> [M, N]."""
+    tp, M, n_loc = y_all.shape
+    return np.ascontiguousarray(y_all.transpose(1, 0, 2)).reshape(M, tp * n_loc)
+
+
+class DeviceShard:
+    """This rank's tensors resident on the current CUDA device, and the call descriptor over them."""
+
+    def __init__(self, torch, ab, case: synth.Case, tp: int, rank: int):
+        self.ab, self.torch = ab, torch
+        self.local_case = lc = shard_case(case, tp, rank) if tp > 1 else case
+        self.n_local = lc.N
+
+        def dev(a):
+            if a is None:
+                return None
+            if a.dtype == np.uint16:
+                return torch.from_numpy(a.view(np.int16).copy()).cuda()
+            return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+        self.x = dev(lc.x)
+        self.seq_slot = dev(lc.seq_slot.astype(np.int32))
+        self.packed, self.scales, self.w_bf16 = dev(lc.packed), dev(lc.scales), dev(lc.w_bf16)
+        self.pool = ab.LoraPool(lc.K, lc.N, lc.max_rank, lc.max_loras)
+        for s, ad in enumerate(lc.adapters):
+            if ad is None:
+                continue
+            self.pool.a_pool[s, :ad.rank].copy_(dev(ad.a).view(torch.bfloat16))
+            self.pool.b_pool[s, :, :ad.rank].copy_(dev(np.ascontiguousarray(ad.b)).view(torch.bfloat16))
+            self.pool._a_host[s] = self.pool.a_pool[s].data_ptr()
+            self.pool._b_host[s] = self.pool.b_pool[s].data_ptr()
+            self.pool._scale_host[s] = ad.scale
+            self.pool._rank_host[s] = ad.rank
+        self.pool.refresh_tables()
+        self.lora_t = torch.zeros((lc.M, lc.max_rank), dtype=torch.int16, device="cuda")
+
+    def desc(self, y, extra_flags: int = 0, out_row_stride=None):
+        lc = self.local_case
+        return self.ab.make_linear_desc(
+            x=self.x, m=lc.M, k=lc.K, n=lc.N, y=y, w_packed=self.packed, w_scale=self.scales, scale2=lc.scale2,
+            w_bf16=self.w_bf16, seq_slot=self.seq_slot, route=self.pool.route(), lora_t=self.lora_t,
+            flags=extra_flags, out_row_stride=out_row_stride)

@@ -248,7 +248,7 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
     if (!use_tc && (d.flags & ATLAS_B200_FLAG_FORCE_TCGEN05)) return ATLAS_B200_ERR_DIMS;
 
     if (use_tc) {
-        if (d.seq_slot) {
+        if (d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK)) {
             // shrink first: t = scale_s / (scale2 * 2^8) * (A_s x), the unit of the MMA accumulator
             ShrinkParams sp{};
             sp.x = static_cast<const uint16_t*>(d.x);

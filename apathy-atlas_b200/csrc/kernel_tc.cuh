@@ -276,23 +276,46 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     if (warp == 0) {
         // ===================================== TMA producer =====================================
         if (lane == 0) {
-            // activation tiles, one per K block
-            for (uint32_t it = 0; it < num_kb; ++it) {
-                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-                if (!mbar_wait(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER)) break;
-                mbar_arrive_expect_tx(BAR_FULL_X + 8 * s, C::X_TILE_BYTES);
-                tma_load_2d(x_tile0 + s * C::X_TILE_BYTES, &map_x, int32_t(it * KB), int32_t(m0), BAR_FULL_X + 8 * s);
-            }
-        } else if (lane == 1) {
-            // raw weight stages (codes + scale bytes), one per four K blocks, on their own ring so
-            // that they run ahead of the activation tiles
+            // One thread feeds two rings without blocking on either: activation tiles (one per K
+            // block) and raw weight stages (codes + scale bytes, one per four K blocks), so the
+            // weight stream runs ahead of the activation stream.
             const uint32_t num_raw = (num_kb + 3u) / 4u;
-            for (uint32_t ri = 0; ri < num_raw; ++ri) {
-                const uint32_t rs = ri % RAW_STAGES, rph = (ri / RAW_STAGES) & 1u;
-                if (!mbar_wait(BAR_EMPTY_RAW + 8 * rs, rph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER)) break;
-                mbar_arrive_expect_tx(BAR_FULL_RAW + 8 * rs, RAW_PACKED_BYTES + RAW_SCALE_BYTES);
-                tma_load_2d(rawp0 + rs * RAW_PACKED_BYTES, &map_w, int32_t(ri * (KRAW / 2)), int32_t(f0), BAR_FULL_RAW + 8 * rs);
-                tma_load_2d(raws0 + rs * RAW_SCALE_BYTES, &map_s, int32_t(ri * (KRAW / 16)), int32_t(f0), BAR_FULL_RAW + 8 * rs);
+            uint32_t it = 0, ri = 0, spins = 0;
+            uint64_t t0 = 0;
+            while (it < num_kb || ri < num_raw) {
+                bool progressed = false;
+                if (ri < num_raw) {
+                    const uint32_t rs = ri % RAW_STAGES, rph = (ri / RAW_STAGES) & 1u;
+                    if (mbar_try_wait(BAR_EMPTY_RAW + 8 * rs, rph ^ 1u)) {
+                        mbar_arrive_expect_tx(BAR_FULL_RAW + 8 * rs, RAW_PACKED_BYTES + RAW_SCALE_BYTES);
+                        tma_load_2d(rawp0 + rs * RAW_PACKED_BYTES, &map_w, int32_t(ri * (KRAW / 2)), int32_t(f0), BAR_FULL_RAW + 8 * rs);
+                        tma_load_2d(raws0 + rs * RAW_SCALE_BYTES, &map_s, int32_t(ri * (KRAW / 16)), int32_t(f0), BAR_FULL_RAW + 8 * rs);
+                        ++ri;
+                        progressed = true;
+                    }
+                }
+                if (it < num_kb) {
+                    const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+                    if (mbar_try_wait(BAR_EMPTY + 8 * s, ph ^ 1u)) {
+                        mbar_arrive_expect_tx(BAR_FULL_X + 8 * s, C::X_TILE_BYTES);
+                        tma_load_2d(x_tile0 + s * C::X_TILE_BYTES, &map_x, int32_t(it * KB), int32_t(m0), BAR_FULL_X + 8 * s);
+                        ++it;
+                        progressed = true;
+                    }
+                }
+                if (progressed) {
+                    spins = 0;
+                    t0 = 0;
+                } else if ((++spins & 63u) == 0u) {
+                    if (*abort_flag) break;
+                    const uint64_t now = global_timer_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > WAIT_LIMIT_NS) {
+                        record_status(STATUS_WAIT_EXPIRED_PRODUCER);
+                        *abort_flag = 1u;
+                        break;
+                    }
+                }
             }
         }
     } else if (warp == 1) {

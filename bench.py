@@ -1,0 +1,307 @@
+#!/usr/bin/env python
+"""Benchmark of the fused NVFP4 + multi-LoRA linear layer.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload config1] [--impl reference]
+
+One step = one pass of the layer over one synthetic batch.  The default workload is benchmark
+configuration 1 (NVFP4 base K=5120 N=17408, 256 tokens, 16 adapters of rank 32, 10 % of the tokens
+adapter-less).  With N > 1 (launched by torch.distributed.run, one rank per GPU) the same layer is
+split column-parallel over the ranks — W, its scales and every B_s by output rows; x and A_s
+replicated — and the shards are collected by one NCCL all-gather: strong scaling.
+
+Rank 0 prints one JSON line.  `value` is device-timed (CUDA events on the launching stream, L2
+flushed between steps, inputs resident in HBM); `e2e` runs the same call with host buffers, with the
+H2D copy of the step's inputs and the D2H copy of its result inside the timed region.
+`--impl reference` times the CPU oracle (a scalar restatement of the reference's arithmetic — the
+reference itself is Rust + GB10 CUDA and has no CPU build of this path) on a bounded sample.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "apathy-atlas_b200"))
+
+import numpy as np
+
+METRIC = "NVFP4+multi-LoRA linear tokens/s"
+FP4_PEAK_TFLOPS = 9000.0          # B200 dense NVFP4, nominal (no measured figure on this pool)
+WORKLOADS = {"config0": 0, "config1": 1, "config2": 2, "config3": 3, "config4": 4}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def algorithmic_work(case):
+    """Bytes and flops of one pass, each tensor counted once (adapters at their true rank)."""
+    M, N, K = case.M, case.N, case.K
+    w_bytes = N * K * 2 if case.w_bf16 is not None else N * K * (0.5 + 1.0 / 16.0)
+    hit = sorted(set(int(s) for s in case.seq_slot if s >= 0))
+    a_bytes = sum(case.adapters[s].rank * K * 2 for s in hit)
+    b_bytes = sum(case.adapters[s].rank * N * 2 for s in hit)
+    x_bytes, y_bytes, slot_bytes = M * K * 2, M * N * 2, 4 * M
+    flops = 2.0 * M * N * K + 2.0 * sum(case.adapters[int(s)].rank * (K + N) for s in case.seq_slot if s >= 0)
+    return dict(w=w_bytes, a=a_bytes, b=b_bytes, x=x_bytes, y=y_bytes, slot=slot_bytes,
+                total=w_bytes + a_bytes + b_bytes + x_bytes + y_bytes + slot_bytes, flops=flops,
+                main_kernel=w_bytes + b_bytes + x_bytes + y_bytes + slot_bytes)
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.rows, self._stop_evt = index, [], threading.Event()
+
+    def run(self):
+        while not self._stop_evt.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                self.rows.append([c.strip() for c in out.strip().split(",")])
+            except Exception:
+                pass
+            self._stop_evt.wait(0.2)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=6)
+        sm, mx, reasons = [], 0.0, set()
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])); mx = max(mx, float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU arm: the oracle on host cores
+# --------------------------------------------------------------------------------------------------
+def cpu_sample(case, budget_rows=None):
+    """Time the reference's launch sequence (base linear, then staged routed LoRA) on a row sample."""
+    from oracle import oracle_ctypes as oc
+    import copy
+    rows = budget_rows or max(1, min(case.M, int(2.0e9 / (case.N * case.K))))   # ~ a few seconds per step
+    sub = copy.copy(case)
+    sub.M, sub.x, sub.seq_slot = rows, case.x[:rows].copy(), case.seq_slot[:rows].copy()
+    pool = oc.HostPool(case.K, case.N, case.max_rank, case.max_loras)
+    for s, ad in enumerate(case.adapters):
+        if ad is not None:
+            pool.pack(s, ad.a, ad.b, ad.scale)
+    kw = dict(packed=case.packed, scales=case.scales, scale2=case.scale2, w_bf16=case.w_bf16,
+              seq_slot=sub.seq_slot, pool=pool)
+
+    def step():
+        t0 = time.perf_counter()
+        oc.reference_sequence(sub.x, rows, case.N, case.K, **kw)
+        return time.perf_counter() - t0
+    return step, rows, oc.num_threads()
+
+
+def run_reference_arm(args, case):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    step, rows, cores = cpu_sample(case)
+    for _ in range(min(args.warmup, 1)):
+        step()
+    times = [step() for _ in range(args.steps)]
+    t = float(np.mean(times))
+    tok_s = rows / t
+    sample = f"first {rows} of {case.M} tokens x all {case.N} outputs, every step"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": t * 1e3 * case.M / rows,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args, case, 1),
+        "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, case, tp):
+    hit = len(set(int(s) for s in case.seq_slot if s >= 0))
+    return {"workload": args.workload, "M": case.M, "K": case.K, "N": case.N, "base": "nvfp4" if case.packed is not None else "bf16",
+            "adapters": sum(a is not None for a in case.adapters), "adapters_hit": hit, "max_rank": case.max_rank,
+            "adapter_less_rows": int((case.seq_slot < 0).sum()), "activation_mode": "A16 (exact BF16 x)",
+            "parallelism": f"column-parallel tp{tp} + all-gather" if tp > 1 else "single GPU",
+            "l2": "flushed between timed steps"}
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="config1", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="atlas_b200", choices=["atlas_b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    from atlas_b200 import synth
+    case = synth.baseline_config(WORKLOADS[args.workload])
+
+    if args.impl == "reference":
+        run_reference_arm(args, case)
+        return
+
+    import torch
+    import atlas_b200 as ab
+    ab.lib()                                      # fail loudly when the CUDA library is missing
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    else:
+        dist = None
+        torch.cuda.set_device(0)
+    assert args.warmup >= 3, "at least 3 warm-up steps"
+    tp = world
+    dev = torch.device("cuda", local_rank)
+
+    # ---- this rank's column shard, resident in HBM ----
+    from atlas_b200 import tp as tpmod
+    shard = tpmod.DeviceShard(torch, ab, case, tp, rank)
+    M, N, K, n_loc = case.M, case.N, case.K, shard.n_local
+    y_loc = torch.empty((M, n_loc), dtype=torch.bfloat16, device=dev)
+    y_all = torch.empty((tp, M, n_loc), dtype=torch.bfloat16, device=dev) if tp > 1 else None
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > L2 (126 MB)
+    desc = shard.desc(y_loc)
+    desc_main_only = shard.desc(y_loc, extra_flags=ab.FLAG_REUSE_SHRINK)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        v = ab.nvfp4_lora_linear(desc, stream)
+        if tp > 1:
+            dist.all_gather_into_tensor(y_all, y_loc)
+        return v
+
+    def barrier():
+        if tp > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    variant = None
+    for _ in range(args.warmup):
+        flush.fill_(1)
+        variant = step()
+    barrier()
+    status = ab.device_status()
+    if status != 0:
+        raise RuntimeError(f"device status word {status:#x} after warm-up")
+    if variant != ab.VARIANT_TCGEN05 and case.packed is not None:
+        raise RuntimeError("the tcgen05 path did not run for this workload")
+
+    # ---- device-timed steps ----
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for a, b in ev:
+        flush.fill_(1)
+        a.record(stream)
+        step()
+        b.record(stream)
+    barrier()
+    step_ms = float(np.mean([a.elapsed_time(b) for a, b in ev]))
+
+    # ---- the dominant kernel alone (shrink result reused), for the roofline ----
+    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in ev2:
+        flush.fill_(1)
+        a.record(stream)
+        ab.nvfp4_lora_linear(desc_main_only, stream)
+        b.record(stream)
+    barrier()
+    main_ms = float(np.mean([a.elapsed_time(b) for a, b in ev2]))
+
+    # ---- end to end through the C ABI with host buffers ----
+    x_host = torch.from_numpy(case.x.view(np.int16).copy()).pin_memory()
+    slot_host = torch.from_numpy(case.seq_slot.copy()).pin_memory()
+    y_host = torch.empty((tp, M, n_loc) if tp > 1 else (M, n_loc), dtype=torch.int16).pin_memory()
+    e2e_steps = max(3, min(args.steps, 20))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        shard.x.view(torch.int16).copy_(x_host, non_blocking=True)
+        shard.seq_slot.copy_(slot_host, non_blocking=True)
+        step()
+        if rank == 0:
+            y_host.copy_((y_all if tp > 1 else y_loc).view(torch.int16), non_blocking=True)
+        barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    clocks = sampler.stop()
+
+    t = torch.tensor([step_ms, main_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if tp > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    step_ms, main_ms, e2e_ms = [float(v) for v in t.tolist()]
+
+    if rank == 0:
+        hbm_gbs, peak_kind = peaks()
+        work = algorithmic_work(case)
+        shard_work = algorithmic_work(shard.local_case)
+        achieved = shard_work["main_kernel"] / (main_ms * 1e-3) / 1e9
+        t_roof = max(work["flops"] / (FP4_PEAK_TFLOPS * 1e12), work["total"] / (hbm_gbs * 1e9))
+        line = {
+            "metric": METRIC, "value": M / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": tp,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(args, case, tp),
+            "tflops": work["flops"] / (step_ms * 1e-3) / 1e12,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
+                         "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "nvfp4_lora_linear_tc_kernel (per rank)", "kernel_ms": main_ms,
+                         "algorithmic_bytes": shard_work["main_kernel"]},
+            "layer_roofline": {"time_us": t_roof * 1e6, "frac": t_roof / (step_ms * 1e-3),
+                               "rule": "max(flops / 9 PFLOP/s nominal NVFP4, algorithmic bytes / measured HBM GB/s), single GPU",
+                               "algorithmic_bytes": work["total"], "flops": work["flops"]},
+            "e2e": {"value": M / (e2e_ms * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": int(x_host.numel() * 2 + slot_host.numel() * 4),
+                    "d2h_bytes_per_step": int(y_host.numel() * 2), "ms_per_step": e2e_ms},
+            "gpu_launches": args.steps * 2 + args.steps,
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline and tp == 1:
+            cstep, rows, cores = cpu_sample(case)
+            ct = cstep()
+            line["cpu_baseline"] = {"value": rows / ct, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                    "sample": f"first {rows} of {M} tokens x all {N} outputs, one pass ({ct:.1f} s)"}
+        print(json.dumps(line), flush=True)
+    if tp > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

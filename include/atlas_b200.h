@@ -53,6 +53,8 @@ extern "C" {
 #define ATLAS_B200_FLAG_FORCE_SIMT     1u   /* always take the CUDA-core path */
 #define ATLAS_B200_FLAG_FORCE_TCGEN05  2u   /* fail with -1 instead of falling back */
 #define ATLAS_B200_FLAG_STAGED_LORA    4u   /* reference rounding: base->bf16, then shrink/expand/fold in place */
+#define ATLAS_B200_FLAG_REUSE_SHRINK   8u   /* tcgen05 path only: lora_t already holds this call's shrink result (same x,
+                                               seq_slot, tables and scale2 as the call that wrote it); skip the shrink launch */
 
 /* ---------------------------------------------------------------------------------------
  * Routed multi-adapter LoRA delta over n rows:  out[i,:] += scale_s * (x[i,:] A_s^T) B_s^T,

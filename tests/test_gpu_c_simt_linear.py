@@ -1,0 +1,41 @@
+"""The CUDA-core path of the fused layer (any shape, dense-BF16 base, reference rounding mode)."""
+import numpy as np
+import pytest
+
+from gpu_util import DeviceCase, assert_close, ideal
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M,K,N,ranks,max_rank", [
+    (5, 48, 70, [4, 8], 8),
+    (16, 512, 192, [16] * 4, 16),
+    (70, 272, 130, [8, 16, 32], 32),
+])
+def test_simt_nvfp4_fused(cuda, atlas, oracle, M, K, N, ranks, max_rank):
+    from atlas_b200 import synth
+    case = synth.make_case("simt", M=M, K=K, N=N, ranks=ranks, max_rank=max_rank, none_frac=0.2,
+                           scale2=0.02, b_std=0.3, seed=K)
+    dc = DeviceCase(cuda, atlas, case, out_row_stride=N + 6)
+    y, variant = dc.run(flags=atlas.FLAG_FORCE_SIMT)
+    assert variant == atlas.VARIANT_SIMT
+    assert_close(oracle, y[:, :N], ideal(oracle, case), "fused")
+    assert (y[:, N:] == 0x7FC0).all()                       # padding columns of the output are untouched
+    yb, _ = dc.run(lora=False, flags=atlas.FLAG_FORCE_SIMT)
+    assert_close(oracle, yb[:, :N], ideal(oracle, case, lora=False), "base")
+    none = case.seq_slot < 0
+    assert np.array_equal(y[none], yb[none])                # un-adapted rows are the base result, bit for bit
+    assert atlas.device_status() == 0
+
+
+def test_config0_dense_bf16_base(cuda, atlas, oracle):
+    """Benchmark configuration 0: M=16, K=N=4096, BF16 base, 4 adapters of rank 16, alpha 32."""
+    from atlas_b200 import synth
+    case = synth.baseline_config(0)
+    dc = DeviceCase(cuda, atlas, case)
+    y, variant = dc.run()
+    assert variant == atlas.VARIANT_SIMT
+    assert_close(oracle, y, ideal(oracle, case), "config0")
+    want_seq, _ = oracle.reference_sequence(case.x, case.M, case.N, case.K, w_bf16=case.w_bf16,
+                                            seq_slot=case.seq_slot, pool=__import__("gpu_util").host_pool(oracle, case))
+    assert_close(oracle, y, oracle.bf16_to_f32(want_seq), "config0 vs reference launch sequence")

@@ -1,0 +1,80 @@
+"""The reference's own CUDA kernels (compiled unchanged for sm_100a under oracle/_ref) run on this GPU,
+against the oracle — this pins the oracle to outputs of the reference itself — and against this
+library's replacements for them."""
+import numpy as np
+import pytest
+
+from gpu_util import RefModule, assert_close, bits_from_dev, device_pool, host_pool, ref_available, to_dev
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not ref_available(), reason="oracle/_ref cubins not built")]
+
+
+def u32(v):
+    return ("u32", v)
+
+
+def test_reference_dequant_equals_oracle(cuda, oracle):
+    torch = cuda
+    from atlas_b200 import synth
+    N, K = 128, 512
+    packed, scales = synth.make_nvfp4_weight(21, N, K)
+    scales[0, :] = np.arange(32, dtype=np.uint8)                       # subnormal scale bytes too
+    out = torch.zeros((N, K), dtype=torch.int16, device="cuda")
+    dp, ds = to_dev(torch, packed), to_dev(torch, scales)
+    RefModule("dequant_nvfp4_bf16").launch("dequant_nvfp4_to_bf16", (N, 1, 1), (256, 1, 1),
+                                           [dp.data_ptr(), ds.data_ptr(), out.data_ptr(), 0.5, u32(N), u32(K)])
+    torch.cuda.synchronize()
+    assert np.array_equal(bits_from_dev(out), oracle.dequant_nvfp4_to_bf16(packed, scales, 0.5, N, K))
+
+
+def test_reference_bgmv_equals_oracle_and_library(cuda, atlas, oracle):
+    torch = cuda
+    from atlas_b200 import synth
+    M, K, N, max_rank = 24, 1024, 512, 16
+    case = synth.make_case("ref", M=M, K=K, N=N, ranks=[8, 16, 4], max_rank=max_rank, max_loras=4,
+                           none_frac=0.2, b_std=0.3, seed=9)
+    pool = device_pool(torch, atlas, case)
+    base = oracle.f32_to_bf16(np.random.default_rng(2).standard_normal((M, N)).astype(np.float32))
+    x, slot = to_dev(torch, case.x), to_dev(torch, case.seq_slot)
+    out_ref, xa_ref = to_dev(torch, base), torch.zeros((M, max_rank), dtype=torch.int16, device="cuda")
+    mod = RefModule("lora_bgmv")
+    mod.launch("lora_bgmv_shrink", ((max_rank + 3) // 4, M, 1), (256, 1, 1),
+               [x.data_ptr(), slot.data_ptr(), pool.a_table.data_ptr(), xa_ref.data_ptr(), u32(M), u32(max_rank), u32(K), u32(K)])
+    mod.launch("lora_bgmv_expand_fold", ((N + 3) // 4, M, 1), (256, 1, 1),
+               [xa_ref.data_ptr(), slot.data_ptr(), pool.b_table.data_ptr(), pool.scale_table.data_ptr(),
+                out_ref.data_ptr(), u32(M), u32(N), u32(max_rank), u32(N)])
+    torch.cuda.synchronize()
+    want = base.copy()
+    want_xa = oracle.lora_bgmv_staged(case.x, case.seq_slot, host_pool(oracle, case), want, M)
+    ref_out, ref_xa = bits_from_dev(out_ref), bits_from_dev(xa_ref)
+    routed = case.seq_slot >= 0
+    assert np.array_equal(ref_out[~routed], base[~routed])
+    # same rounding boundaries, different FP32 summation order: equal up to the last BF16 bit
+    assert_close(oracle, ref_xa, oracle.bf16_to_f32(want_xa), "reference xa vs oracle")
+    assert_close(oracle, ref_out, oracle.bf16_to_f32(want), "reference out vs oracle")
+    same = (ref_out == want).mean()
+    assert same > 0.95, f"only {same:.3f} of outputs bit-identical to the oracle"
+    # this library's replacement against the reference kernel
+    out_lib, xa_lib = to_dev(torch, base), torch.zeros((M, max_rank), dtype=torch.int16, device="cuda")
+    atlas.apply_lora_bgmv(pool.route(), x, out_lib, slot, M, K, N, xa_lib)
+    torch.cuda.synchronize()
+    assert_close(oracle, bits_from_dev(out_lib), oracle.bf16_to_f32(ref_out), "library vs reference kernel")
+    assert (bits_from_dev(out_lib) == ref_out).mean() > 0.95
+
+
+def test_reference_w4a16_gemm_equals_oracle_and_library(cuda, atlas, oracle):
+    torch = cuda
+    from atlas_b200 import synth
+    M, K, N = 48, 512, 256
+    case = synth.make_case("ref", M=M, K=K, N=N, ranks=[8], max_rank=8, scale2=0.01, seed=4)
+    x, dp, ds = to_dev(torch, case.x), to_dev(torch, case.packed), to_dev(torch, case.scales)
+    c_ref = torch.zeros((M, N), dtype=torch.int16, device="cuda")
+    RefModule("w4a16_gemm").launch("w4a16_gemm", ((N + 63) // 64, (M + 63) // 64, 1), (128, 1, 1),
+                                   [x.data_ptr(), dp.data_ptr(), ds.data_ptr(), 0.01, c_ref.data_ptr(), u32(M), u32(N), u32(K)])
+    torch.cuda.synchronize()
+    want = oracle.w4a16_gemm_bf16w(case.x, case.packed, case.scales, float(np.float32(0.01)), M, N, K)
+    assert_close(oracle, bits_from_dev(c_ref), oracle.bf16_to_f32(want), "reference gemm vs oracle")
+    c_lib = torch.zeros((M, N), dtype=torch.int16, device="cuda")
+    atlas.w4a16_gemm(x, dp, ds, float(np.float32(0.01)), c_lib, M, N, K)
+    torch.cuda.synchronize()
+    assert_close(oracle, bits_from_dev(c_lib), oracle.bf16_to_f32(bits_from_dev(c_ref)), "library vs reference gemm")
