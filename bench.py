@@ -101,7 +101,7 @@ def cpu_sample(case, budget_rows=None):
     """Time the reference's launch sequence (base linear, then staged routed LoRA) on a row sample."""
     from oracle import oracle_ctypes as oc
     import copy
-    rows = budget_rows or max(1, min(case.M, int(2.0e9 / (case.N * case.K))))   # ~ a few seconds per step
+    rows = budget_rows or max(1, min(case.M, int(2.5e10 / (case.N * case.K))))  # ~ 5-20 s of host work per pass
     sub = copy.copy(case)
     sub.M, sub.x, sub.seq_slot = rows, case.x[:rows].copy(), case.seq_slot[:rows].copy()
     pool = oc.HostPool(case.K, case.N, case.max_rank, case.max_loras)
@@ -156,7 +156,7 @@ def workload_config(args, case, tp):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="config1", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="atlas_b200", choices=["atlas_b200", "reference"])

@@ -55,7 +55,7 @@ def test_base_linear(cuda, atlas, oracle, M, K, N):
 def test_fused_lora(cuda, atlas, oracle, M, K, N, ranks, max_rank, with_ranks):
     from atlas_b200 import synth
     case = synth.make_case("fused", M=M, K=K, N=N, ranks=ranks, max_rank=max_rank, max_loras=len(ranks) + 3,
-                           none_frac=0.15, scale2=0.02, b_std=0.3, seed=M + N)
+                           none_frac=0.15, scale2=0.02, b_std=0.1, seed=M + N)
     dc = DeviceCase(cuda, atlas, case)
     y, variant = dc.run(with_ranks=with_ranks, flags=_tc(atlas))
     assert variant == atlas.VARIANT_TCGEN05
@@ -66,7 +66,7 @@ def test_fused_lora(cuda, atlas, oracle, M, K, N, ranks, max_rank, with_ranks):
     assert none.any() and np.array_equal(y[none], yb[none])            # routing is exact
     # the LoRA term is visible at this scale, and the device result tracks it
     base = ideal(oracle, case, lora=False)
-    assert np.abs(want - base)[~none].mean() > 0.02
+    assert np.abs(want - base)[~none].mean() > 0.05
     got = oracle.bf16_to_f32(y)
     num = ((got - base)[~none] * (want - base)[~none]).sum()
     den = np.linalg.norm((got - base)[~none]) * np.linalg.norm((want - base)[~none])
