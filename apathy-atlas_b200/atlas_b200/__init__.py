@@ -33,7 +33,7 @@ EXPORTS = (
     "atlas_b200_build_seq_slot", "atlas_b200_routed_prefill_slot_of", "atlas_b200_peft_scaling",
     "atlas_b200_module_dims", "atlas_b200_pool_slot_bytes", "atlas_b200_slot_base_offset",
     "atlas_b200_module_slot_offsets", "atlas_b200_pack_module", "atlas_b200_select_victim_slot",
-    "atlas_b200_device_status", "atlas_b200_last_variant", "atlas_b200_version",
+    "atlas_b200_device_status", "atlas_b200_last_variant", "atlas_b200_set_profile_buffer", "atlas_b200_version",
 )
 
 
@@ -99,6 +99,7 @@ def lib() -> C.CDLL:
     L.atlas_b200_select_victim_slot.argtypes = [C.POINTER(sz), C.POINTER(C.c_uint8), C.POINTER(sz),
                                                 C.POINTER(C.c_uint64), sz]
     L.atlas_b200_device_status.argtypes = [C.POINTER(u32), C.c_int]
+    L.atlas_b200_set_profile_buffer.argtypes = [vp, sz]
     L.atlas_b200_version.restype = C.c_char_p
     _lib = L
     return L

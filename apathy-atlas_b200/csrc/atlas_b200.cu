@@ -24,6 +24,8 @@
 namespace atlas {
 
 static thread_local int t_last_variant = ATLAS_B200_VARIANT_NONE;
+static unsigned long long* g_profile_buf = nullptr;   // device buffer for per-CTA cycle counters (diagnostics)
+static size_t g_profile_words = 0;
 
 static inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? ATLAS_B200_OK : ATLAS_B200_ERR_CUDA_BASE - int(e); }
 static inline int launch_status() { return cuda_status(cudaGetLastError()); }
@@ -217,6 +219,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, cudaStream_t
     p.max_loras = d.max_loras; p.max_rank = d.max_rank;
     p.out_scale = d.scale2 * kWeightPreScale;
     dim3 grid((d.n + tc::FT - 1) / tc::FT, (d.m + MT - 1) / MT);
+    p.profile = (g_profile_buf && size_t(grid.x) * grid.y * tc::PROFILE_WORDS <= g_profile_words) ? g_profile_buf : nullptr;
     if (grid.y > 65535) return ATLAS_B200_ERR_LIMIT;
     tc::nvfp4_lora_linear_tc_kernel<MT><<<grid, tc::NUM_THREADS, C::SMEM_BYTES, st>>>(map_x, map_w, map_s, p);
     return launch_status();
@@ -378,6 +381,12 @@ int atlas_b200_device_status(uint32_t* out_word, int clear) {
 }
 
 int atlas_b200_last_variant(void) { return t_last_variant; }
+
+int atlas_b200_set_profile_buffer(void* device_buffer, size_t n_words) {
+    g_profile_buf = static_cast<unsigned long long*>(device_buffer);
+    g_profile_words = device_buffer ? n_words : 0;
+    return ATLAS_B200_OK;
+}
 
 const char* atlas_b200_version(void) { return "atlas_b200 0.1 (sm_100a)"; }
 

@@ -17,13 +17,19 @@
 // are ordered by slot, four to a 64-wide K block; zeros add exactly, so a token's result does not
 // depend on which other tokens share its tile.
 //
+// Operand placement: the weight operand (MMA "A", 128 features x 16 k per instruction) is written
+// by the expansion warps straight into TENSOR MEMORY (tcgen05.st) and read from there by the MMA;
+// only the activation operand lives in shared memory.  Shared-memory bandwidth is what bounds this
+// kernel (TMA writes + MMA operand reads + raw-code reads all share it), and a BF16 weight tile
+// that is written to and read back from shared memory every K block costs a third of it.
+//
 // Warp roles (14 warps, 448 threads):
 //   warp 0        TMA producer: x tiles (SWIZZLE_128B) and raw weight stages (packed codes with
 //                 SWIZZLE_128B + scale bytes) through mbarrier rings
 //   warp 1        TMEM allocation, tcgen05.mma issue, tcgen05.commit
-//   warps 2-5     build the tile's granule list while the main loop runs; then the epilogue:
-//                 tcgen05.ld -> scale -> BF16 -> global
-//   warps 6-13    expand raw NVFP4 into the BF16 MMA operand tile; build the LoRA operand tiles
+//   warps 2-5     build the tile's granule list while the main loop runs; then the epilogue
+//   warps 6-13    expand raw NVFP4 into the BF16 weight operand (TMEM); build the LoRA operands;
+//                 then join the epilogue: tcgen05.ld -> scale -> BF16 -> global
 //
 // Every wait is bounded: on expiry the waiter records a status code, raises the CTA's abort
 // flag, and all roles fall through to a common teardown that frees TMEM.
@@ -39,35 +45,39 @@ namespace tc {
 constexpr int FT = 128;              // features per CTA = UMMA M
 constexpr int KB = 64;               // K elements per MMA stage (one 128-byte swizzle row of BF16)
 constexpr int KRAW = 256;            // K elements per raw weight stage
-constexpr int RAW_STAGES = 2;
+constexpr int RAW_STAGES = 3;
 constexpr int RAW_PACKED_BYTES = FT * (KRAW / 2);    // 16 KiB
 constexpr int RAW_SCALE_BYTES = FT * (KRAW / 16);    // 2 KiB
-constexpr int W_TILE_BYTES = FT * KB * 2;            // 16 KiB
 constexpr int NUM_THREADS = 448;
 constexpr int DEQ_WARP0 = 6, DEQ_WARPS = 8, DEQ_THREADS = 256;
 constexpr int EPI_WARP0 = 2, EPI_THREADS = 128;
 constexpr int MAX_LORAS_TC = 4096;
 constexpr int MAX_RANK_TC = 64;
 constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;    // 1 s
+constexpr int PROFILE_WORDS = 10;                    // u64 words per CTA in the optional profile buffer
 
 template <int MT> struct Cfg {
     static constexpr int X_TILE_BYTES = MT * KB * 2;
-    static constexpr int STAGES = MT >= 256 ? 3 : (MT >= 128 ? 4 : 6);
-    static constexpr int TMEM_COLS = MT < 32 ? 32 : MT;
+    static constexpr int STAGES = MT >= 256 ? 5 : (MT >= 128 ? 6 : 8);
+    static constexpr int A_COLS = KB / 2;                                  // TMEM columns of one weight-operand stage
+    static constexpr int TMEM_A_BASE = MT < 32 ? 32 : MT;                  // accumulator occupies [0, MT)
+    static constexpr int TMEM_NEEDED = TMEM_A_BASE + STAGES * A_COLS;
+    static constexpr int TMEM_COLS = TMEM_NEEDED <= 64 ? 64 : TMEM_NEEDED <= 128 ? 128 : TMEM_NEEDED <= 256 ? 256 : 512;
     static constexpr int MAX_GRANULES = MT * (MAX_RANK_TC / 16);
     // shared memory map (offsets from a 1024-byte aligned base)
     static constexpr int OFF_X = 0;
-    static constexpr int OFF_W = OFF_X + STAGES * X_TILE_BYTES;
-    static constexpr int OFF_RAWP = OFF_W + STAGES * W_TILE_BYTES;
+    static constexpr int OFF_RAWP = OFF_X + STAGES * X_TILE_BYTES;
     static constexpr int OFF_RAWS = OFF_RAWP + RAW_STAGES * RAW_PACKED_BYTES;
     static constexpr int OFF_SLOT = OFF_RAWS + RAW_STAGES * RAW_SCALE_BYTES;     // int32[MT]
     static constexpr int OFF_GRAN = OFF_SLOT + MT * 4;                           // uint16[MAX_GRANULES]
     static constexpr int OFF_BITMAP = OFF_GRAN + MAX_GRANULES * 2;               // uint32[128]
     static constexpr int OFF_SCAN = OFF_BITMAP + (MAX_LORAS_TC / 32) * 4;        // uint32[8]
     static constexpr int OFF_BAR = OFF_SCAN + 64;                                // mbarriers
-    static constexpr int NUM_BARS = 3 * STAGES + 2 * RAW_STAGES + 2;
+    static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_STAGES + 2;
     static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;                      // tmem ptr, n_gran, abort
     static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;                      // + alignment slack
+    static_assert(TMEM_NEEDED <= 512, "tensor memory budget");
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
 struct Params {
@@ -79,6 +89,7 @@ struct Params {
     uint16_t* y;
     uint32_t M, N, K, out_row_stride, max_loras, max_rank;
     float out_scale;               // scale2 * 2^8
+    unsigned long long* profile;   // nullable: per-CTA wait/busy cycle counters (PROFILE_WORDS per CTA)
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -129,6 +140,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// mbar_wait that also adds the cycles spent waiting to `acc` (profiling builds of a launch only)
+__device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code,
+                                                bool timed, unsigned long long& acc) {
+    if (!timed) return mbar_wait(bar, parity, abort_flag, code);
+    const long long t0 = clock64();
+    const bool ok = mbar_wait(bar, parity, abort_flag, code);
+    acc += (unsigned long long)(clock64() - t0);
+    return ok;
+}
+
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -153,14 +174,26 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 
-// D[tmem] (+)= A[smem] * B[smem]^T, BF16 inputs, FP32 accumulate; one thread issues.
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem]^T, BF16 inputs, FP32 accumulate; one thread issues.
+// A: 128 lanes x 8 columns (16 BF16 per lane, two per 32-bit column, even k in the low half).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// registers -> 32 lanes x N consecutive 32-bit TMEM columns (lane = this warp's quadrant base + laneid)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // Arrive on an mbarrier once all tcgen05.mma issued so far by this thread have completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -206,6 +239,45 @@ __device__ __forceinline__ uint32_t sw128_off(uint32_t r, uint32_t c) { return r
 // ---------------------------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------------------------
+// Epilogue for one participant: `q` = TMEM lane quadrant of this warp, chunks of 16 token columns
+// c = part, part + nparts, ...  Lane pairs exchange values so every thread stores two adjacent
+// features (4 bytes) of one token.
+template <int MT>
+__device__ __forceinline__ void epilogue_columns(const Params& p, uint32_t tmem_acc, uint32_t q, uint32_t lane,
+                                                 uint32_t f0, uint32_t m0, uint32_t part, uint32_t nparts) {
+    const uint32_t f = f0 + q * 32 + lane;
+    const float osc = p.out_scale;
+    const bool pair_ok = (p.out_row_stride % 2u == 0u) && ((reinterpret_cast<uintptr_t>(p.y) & 3u) == 0u);
+    const bool odd = lane & 1u;
+#pragma unroll 1
+    for (uint32_t c0 = part * 16; c0 < uint32_t(MT); c0 += nparts * 16) {
+        uint32_t v[16];
+        tmem_ld16(tmem_acc + ((q * 32u) << 16) + c0, v);
+        tmem_ld_wait();
+        if (pair_ok) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float a = __uint_as_float(v[2 * i]) * osc, b = __uint_as_float(v[2 * i + 1]) * osc;
+                const float got = __shfl_xor_sync(0xFFFFFFFFu, odd ? a : b, 1);
+                // even lane: token 2i, features (f, f+1); odd lane: token 2i+1, features (f-1, f)
+                const uint32_t m = m0 + c0 + 2 * i + (odd ? 1u : 0u);
+                const uint32_t fe = f & ~1u;
+                const uint32_t w = odd ? pack_bf16x2(got, b) : pack_bf16x2(a, got);
+                if (m < p.M) {
+                    if (fe + 1 < p.N) *reinterpret_cast<uint32_t*>(p.y + size_t(m) * p.out_row_stride + fe) = w;
+                    else if (fe < p.N) p.y[size_t(m) * p.out_row_stride + fe] = uint16_t(w & 0xFFFFu);
+                }
+            }
+        } else if (f < p.N) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint32_t m = m0 + c0 + i;
+                if (m < p.M) p.y[size_t(m) * p.out_row_stride + f] = f32_to_bf16_bits(__uint_as_float(v[i]) * osc);
+            }
+        }
+    }
+}
+
 template <int MT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
@@ -218,7 +290,6 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
     const uint32_t x_tile0 = smem_base + C::OFF_X;
-    const uint32_t w_tile0 = smem_base + C::OFF_W;
     const uint32_t rawp0 = smem_base + C::OFF_RAWP;
     const uint32_t raws0 = smem_base + C::OFF_RAWS;
     int32_t* slot_arr = reinterpret_cast<int32_t*>(smem_gen + C::OFF_SLOT);
@@ -226,11 +297,12 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     uint32_t* bitmap = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_BITMAP);
     uint32_t* scan = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_SCAN);
     const uint32_t bar0 = smem_base + C::OFF_BAR;
-    // barrier indices
-    const uint32_t BAR_FULL_X = bar0;                                  // [STAGES] TMA -> MMA
-    const uint32_t BAR_FULL_W = bar0 + 8 * C::STAGES;                  // [STAGES] expand warps -> MMA
-    const uint32_t BAR_EMPTY = bar0 + 16 * C::STAGES;                  // [STAGES] MMA -> producers
-    const uint32_t BAR_FULL_RAW = bar0 + 24 * C::STAGES;               // [RAW_STAGES]
+    // FULL[s]: both operands of stage s are in place.  DEQ_WARPS + 1 arrivals per phase: the eight
+    // expansion warps, plus the TMA producer (with the tile's byte count) for a base K block or one
+    // extra arrival by an expansion thread for a LoRA K block, whose activation tile they build.
+    const uint32_t BAR_FULL = bar0;                                    // [STAGES] operands -> MMA
+    const uint32_t BAR_EMPTY = bar0 + 8 * C::STAGES;                   // [STAGES] MMA -> producers
+    const uint32_t BAR_FULL_RAW = bar0 + 16 * C::STAGES;               // [RAW_STAGES]
     const uint32_t BAR_EMPTY_RAW = BAR_FULL_RAW + 8 * RAW_STAGES;      // [RAW_STAGES]
     const uint32_t BAR_ACC = BAR_EMPTY_RAW + 8 * RAW_STAGES;           // accumulator complete
     const uint32_t BAR_LIST = BAR_ACC + 8;                             // granule list ready
@@ -242,11 +314,14 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     const uint32_t f0 = blockIdx.x * FT;
     const uint32_t m0 = blockIdx.y * MT;
     const uint32_t num_kb = (p.K + KB - 1) / KB;
+    const bool prof = p.profile != nullptr;
+    const long long t_entry = clock64();
+    const uint64_t t_entry_ns = prof ? global_timer_ns() : 0;
+    unsigned long long* prof_row = prof ? p.profile + (size_t(blockIdx.y) * gridDim.x + blockIdx.x) * PROFILE_WORDS : nullptr;
 
     if (tid == 0) {
         for (int i = 0; i < C::STAGES; ++i) {
-            mbar_init(BAR_FULL_X + 8 * i, 1);
-            mbar_init(BAR_FULL_W + 8 * i, DEQ_WARPS);
+            mbar_init(BAR_FULL + 8 * i, DEQ_WARPS + 1);
             mbar_init(BAR_EMPTY + 8 * i, 1);
         }
         for (int i = 0; i < RAW_STAGES; ++i) {
@@ -272,6 +347,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_acc = misc[0];
+    const uint32_t tmem_a0 = tmem_acc + C::TMEM_A_BASE;   // weight-operand stages: [tmem_a0 + s * A_COLS, + A_COLS)
 
     if (warp == 0) {
         // ===================================== TMA producer =====================================
@@ -279,7 +355,10 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             // One thread feeds two rings without blocking on either: activation tiles (one per K
             // block) and raw weight stages (codes + scale bytes, one per four K blocks), so the
             // weight stream runs ahead of the activation stream.
+            // CTAs start their K loop at different K offsets (a rotation in units of one raw stage),
+            // so concurrently running CTAs do not all pull the same activation lines at one moment.
             const uint32_t num_raw = (num_kb + 3u) / 4u;
+            const uint32_t rot_raw = (num_kb % 4u == 0u) ? (blockIdx.x % num_raw) : 0u;
             uint32_t it = 0, ri = 0, spins = 0;
             uint64_t t0 = 0;
             while (it < num_kb || ri < num_raw) {
@@ -288,8 +367,9 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     const uint32_t rs = ri % RAW_STAGES, rph = (ri / RAW_STAGES) & 1u;
                     if (mbar_try_wait(BAR_EMPTY_RAW + 8 * rs, rph ^ 1u)) {
                         mbar_arrive_expect_tx(BAR_FULL_RAW + 8 * rs, RAW_PACKED_BYTES + RAW_SCALE_BYTES);
-                        tma_load_2d(rawp0 + rs * RAW_PACKED_BYTES, &map_w, int32_t(ri * (KRAW / 2)), int32_t(f0), BAR_FULL_RAW + 8 * rs);
-                        tma_load_2d(raws0 + rs * RAW_SCALE_BYTES, &map_s, int32_t(ri * (KRAW / 16)), int32_t(f0), BAR_FULL_RAW + 8 * rs);
+                        const uint32_t rk = (ri + rot_raw) % num_raw;
+                        tma_load_2d(rawp0 + rs * RAW_PACKED_BYTES, &map_w, int32_t(rk * (KRAW / 2)), int32_t(f0), BAR_FULL_RAW + 8 * rs);
+                        tma_load_2d(raws0 + rs * RAW_SCALE_BYTES, &map_s, int32_t(rk * (KRAW / 16)), int32_t(f0), BAR_FULL_RAW + 8 * rs);
                         ++ri;
                         progressed = true;
                     }
@@ -297,8 +377,9 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 if (it < num_kb) {
                     const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
                     if (mbar_try_wait(BAR_EMPTY + 8 * s, ph ^ 1u)) {
-                        mbar_arrive_expect_tx(BAR_FULL_X + 8 * s, C::X_TILE_BYTES);
-                        tma_load_2d(x_tile0 + s * C::X_TILE_BYTES, &map_x, int32_t(it * KB), int32_t(m0), BAR_FULL_X + 8 * s);
+                        mbar_arrive_expect_tx(BAR_FULL + 8 * s, C::X_TILE_BYTES);
+                        const uint32_t kb = (it + 4u * rot_raw) % num_kb;
+                        tma_load_2d(x_tile0 + s * C::X_TILE_BYTES, &map_x, int32_t(kb * KB), int32_t(m0), BAR_FULL + 8 * s);
                         ++it;
                         progressed = true;
                     }
@@ -320,35 +401,60 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         }
     } else if (warp == 1) {
         // ===================================== MMA issuer =======================================
-        constexpr uint32_t idesc = make_idesc_bf16(MT);
-        uint32_t total_blocks = num_kb;
-        bool ok = true;
-        for (uint32_t it = 0; ok && it < total_blocks; ++it) {
-            const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-            uint32_t ksteps = KB / 16;
-            if (it >= num_kb) {
-                const uint32_t left = misc[1] - (it - num_kb) * 4u;
-                ksteps = left < 4u ? left : 4u;
+        // One thread runs this role.  tcgen05.mma issue blocks once a couple of instructions are
+        // queued, so whatever this thread executes between the last MMA of one K block and the
+        // first of the next must fit inside that short queue or the tensor pipe drains: the loop
+        // carries its stage/phase/operand addresses incrementally and waits on ONE barrier per block.
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16(MT);
+            unsigned long long w_full = 0;
+            const long long t_begin = prof ? clock64() : 0;
+            bool ok = true;
+            uint32_t s = 0, ph = 0, acc = 0;
+            uint32_t bar_full = BAR_FULL, bar_empty = BAR_EMPTY, a_tmem = tmem_a0;
+            uint64_t b_desc = make_kmajor_sw128_desc(x_tile0);
+            constexpr uint64_t b_desc_step = uint64_t(C::X_TILE_BYTES >> 4);
+            for (uint32_t it = 0; it < num_kb; ++it) {
+                ok = mbar_wait_timed(bar_full, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full);
+                if (!ok) break;
+                tcgen05_fence_after();
+                // 16 k per instruction: 8 TMEM columns of A, 32 bytes along the swizzled row of B
+                umma_bf16_ts(tmem_acc, a_tmem, b_desc, idesc, acc);
+                umma_bf16_ts(tmem_acc, a_tmem + 8, b_desc + 2, idesc, 1u);
+                umma_bf16_ts(tmem_acc, a_tmem + 16, b_desc + 4, idesc, 1u);
+                umma_bf16_ts(tmem_acc, a_tmem + 24, b_desc + 6, idesc, 1u);
+                umma_commit(bar_empty);
+                acc = 1u;
+                if (++s == uint32_t(C::STAGES)) {
+                    s = 0; ph ^= 1u;
+                    bar_full = BAR_FULL; bar_empty = BAR_EMPTY; a_tmem = tmem_a0; b_desc -= b_desc_step * (C::STAGES - 1);
+                } else {
+                    bar_full += 8; bar_empty += 8; a_tmem += C::A_COLS; b_desc += b_desc_step;
+                }
             }
-            ok = mbar_wait(BAR_FULL_W + 8 * s, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA);
-            if (ok && it < num_kb) ok = mbar_wait(BAR_FULL_X + 8 * s, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA);
-            if (!ok) break;
-            tcgen05_fence_after();
-            if (lane == 0) {
-                const uint64_t a_desc = make_kmajor_sw128_desc(w_tile0 + s * W_TILE_BYTES);
-                const uint64_t b_desc = make_kmajor_sw128_desc(x_tile0 + s * C::X_TILE_BYTES);
-                for (uint32_t k = 0; k < ksteps; ++k)   // +32 bytes (16 BF16) along K inside the swizzle row
-                    umma_bf16(tmem_acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (it | k) != 0u);
-                umma_commit(BAR_EMPTY + 8 * s);
+            // base K blocks issued; the LoRA K blocks follow once the granule list is known
+            if (ok) ok = mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_MMA);
+            if (ok) {
+                const uint32_t n_gran = misc[1];
+                for (uint32_t g0 = 0; g0 < n_gran; g0 += 4) {
+                    ok = mbar_wait_timed(bar_full, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t ksteps = min(4u, n_gran - g0);
+                    for (uint32_t k = 0; k < ksteps; ++k)
+                        umma_bf16_ts(tmem_acc, a_tmem + 8 * k, b_desc + 2 * k, idesc, 1u);
+                    umma_commit(bar_empty);
+                    if (++s == uint32_t(C::STAGES)) {
+                        s = 0; ph ^= 1u;
+                        bar_full = BAR_FULL; bar_empty = BAR_EMPTY; a_tmem = tmem_a0; b_desc -= b_desc_step * (C::STAGES - 1);
+                    } else {
+                        bar_full += 8; bar_empty += 8; a_tmem += C::A_COLS; b_desc += b_desc_step;
+                    }
+                }
             }
-            __syncwarp();
-            if (it + 1 == num_kb) {
-                // base K blocks issued; the LoRA K blocks follow once the granule list is known
-                ok = mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_MMA);
-                if (ok) total_blocks = num_kb + (misc[1] + 3u) / 4u;
-            }
+            if (ok) umma_commit(BAR_ACC);
+            if (prof) { prof_row[0] = w_full + ((unsigned long long)(t_begin - t_entry) << 32); prof_row[2] = (unsigned long long)(clock64() - t_begin); }
         }
-        if (ok && lane == 0) umma_commit(BAR_ACC);
         __syncwarp();
     } else if (warp < DEQ_WARP0) {
         // ============================ granule list, then the epilogue ===========================
@@ -397,35 +503,29 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         }
         if (te == 0) mbar_arrive(BAR_LIST);
 
-        // ---- epilogue: TMEM lane = feature, column = token ----
-        const uint32_t q = warp & 3u;                       // TMEM lane quadrant this warp may read
+        // ---- epilogue, shared with the expansion warps: TMEM lane = feature, column = token ----
         if (mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE)) {
+            const long long t_epi = clock64();
             tcgen05_fence_after();
-            const uint32_t f = f0 + q * 32 + lane;
-            const float osc = p.out_scale;
-#pragma unroll 1
-            for (uint32_t c0 = 0; c0 < uint32_t(MT); c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(tmem_acc + ((q * 32u) << 16) + c0, v);
-                tmem_ld_wait();
-                if (f < p.N) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const uint32_t m = m0 + c0 + i;
-                        if (m < p.M) p.y[size_t(m) * p.out_row_stride + f] = f32_to_bf16_bits(__uint_as_float(v[i]) * osc);
-                    }
-                }
-            }
+            epilogue_columns<MT>(p, tmem_acc, warp & 3u, lane, f0, m0, 0, 3);
+            if (prof && te == 0) prof_row[7] = (unsigned long long)(clock64() - t_epi);
         }
     } else {
-        // ========================== NVFP4 -> BF16 operand expansion =============================
-        const uint32_t td = tid - DEQ_WARP0 * 32;           // 0..255
-        const uint32_t row = td & 127u, half = td >> 7;
+        // ========================== NVFP4 -> BF16 weight operand, into TMEM ======================
+        // warp w may touch TMEM lanes [32 (w % 4), +32): it owns those 32 features; the two warps
+        // of a quadrant split each K block in halves of 32.
+        const uint32_t q = warp & 3u;
+        const uint32_t half = (warp - DEQ_WARP0) >> 2;
+        const uint32_t row = q * 32 + lane;
+        const uint32_t td = tid - DEQ_WARP0 * 32;
+        const uint32_t lane_base = (q * 32u) << 16;
         bool ok = true;
+        unsigned long long w_raw = 0, w_empty = 0;
+        const long long t_begin = clock64();
         const uint32_t num_raw = (num_kb + 3u) / 4u;
         for (uint32_t ri = 0; ok && ri < num_raw; ++ri) {
             const uint32_t rs = ri % RAW_STAGES, rph = (ri / RAW_STAGES) & 1u;
-            ok = mbar_wait(BAR_FULL_RAW + 8 * rs, rph, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
+            ok = mbar_wait_timed(BAR_FULL_RAW + 8 * rs, rph, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_raw);
             if (!ok) break;
             const uint4 sc4 = lds128(raws0 + rs * RAW_SCALE_BYTES + row * 16);
             const uint32_t scw[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
@@ -433,68 +533,104 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             for (uint32_t j = 0; j < 4; ++j) {
                 const uint32_t it = ri * 4 + j;
                 if (it >= num_kb) break;
-                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-                ok = mbar_wait(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
-                if (!ok) break;
                 // 32 codes of this row: logical chunk 2j + half of the swizzled 128-byte raw row
                 const uint4 pk = lds128(rawp0 + rs * RAW_PACKED_BYTES + sw128_off(row, 2 * j + half));
                 const uint32_t pw[4] = {pk.x, pk.y, pk.z, pk.w};
                 const uint32_t sbytes = scw[j] >> (16 * half);      // scale bytes 2*half, 2*half+1 of word j
                 const uint32_t mul0 = e4m3_to_bf16x2_shifted(sbytes & 0xFFu);
                 const uint32_t mul1 = e4m3_to_bf16x2_shifted((sbytes >> 8) & 0xFFu);
-                const uint32_t wt = w_tile0 + s * W_TILE_BYTES;
+                uint32_t o[16];
 #pragma unroll
                 for (uint32_t qd = 0; qd < 4; ++qd) {
-                    uint32_t o[4];
-                    e2m1x8_to_bf16x8(pw[qd], qd < 2 ? mul0 : mul1, o);
-                    sts128(wt + sw128_off(row, 4 * half + qd), o[0], o[1], o[2], o[3]);
+                    uint32_t o4[4];
+                    e2m1x8_to_bf16x8(pw[qd], qd < 2 ? mul0 : mul1, o4);
+                    o[4 * qd] = o4[0]; o[4 * qd + 1] = o4[1]; o[4 * qd + 2] = o4[2]; o[4 * qd + 3] = o4[3];
                 }
-                fence_proxy_async();
+                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+                ok = mbar_wait_timed(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_empty);
+                if (!ok) break;
+                tcgen05_fence_after();
+                // this thread's 32 k of its feature row: 16 columns at 16 * half of the stage
+                tmem_st16(tmem_a0 + lane_base + s * C::A_COLS + 16 * half, o);
+                tmem_st_wait();
+                tcgen05_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(BAR_FULL_W + 8 * s);
+                if (lane == 0) mbar_arrive(BAR_FULL + 8 * s);
             }
             if (!ok) break;
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR_EMPTY_RAW + 8 * rs);
         }
+        if (prof && td == 0) {
+            prof_row[3] = w_raw; prof_row[4] = w_empty; prof_row[5] = (unsigned long long)(clock64() - t_begin);
+        }
+        const long long t_lora = clock64();
 
-        // ---- LoRA K blocks: A operand = B_s rows, B operand = masked rows of t ----
+        // ---- LoRA K blocks: weight operand = rows of B_s (TMEM), activation operand = masked rows
+        //      of t (shared memory, written here with generic stores) ----
         if (ok) ok = mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
         if (ok) {
             const uint32_t n_gran = misc[1];
             const uint32_t f = f0 + row;
+            constexpr uint32_t T_TASKS = (uint32_t(MT) * 2 + DEQ_THREADS - 1) / DEQ_THREADS;   // per granule
             for (uint32_t lb = 0; ok && lb * 4 < n_gran; ++lb) {
                 const uint32_t it = num_kb + lb;
                 const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-                ok = mbar_wait(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
-                if (!ok) break;
-                const uint32_t wt = w_tile0 + s * W_TILE_BYTES;
-                const uint32_t xt = x_tile0 + s * C::X_TILE_BYTES;
                 const uint32_t ng = min(4u, n_gran - lb * 4);
-                for (uint32_t g = 0; g < ng; ++g) {
-                    const uint32_t e = gran[lb * 4 + g];
-                    const uint32_t slot = e >> 2, j0 = (e & 3u) * 16u;
-                    {   // B_s[f, j0 + 8 half .. +8)
-                        uint4 bv = make_uint4(0, 0, 0, 0);
+                // issue every global load of the block before the first use
+                uint4 bv[4], tv[4][T_TASKS];
+#pragma unroll
+                for (uint32_t g = 0; g < 4; ++g) {
+                    bv[g] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (uint32_t u = 0; u < T_TASKS; ++u) tv[g][u] = make_uint4(0, 0, 0, 0);
+                    if (g < ng) {
+                        const uint32_t e = gran[lb * 4 + g];
+                        const uint32_t slot = e >> 2, j0 = (e & 3u) * 16u;
                         const uint32_t j = j0 + 8 * half;
                         if (f < p.N && j < p.max_rank)
-                            bv = __ldg(reinterpret_cast<const uint4*>(
+                            bv[g] = __ldg(reinterpret_cast<const uint4*>(
                                 reinterpret_cast<const uint16_t*>(p.b_table[slot]) + size_t(f) * p.max_rank + j));
-                        sts128(wt + sw128_off(row, 2 * g + half), bv.x, bv.y, bv.z, bv.w);
-                    }
-                    for (uint32_t task = td; task < uint32_t(MT) * 2; task += DEQ_THREADS) {
-                        const uint32_t r = task >> 1, hh = task & 1u;
-                        uint4 tv = make_uint4(0, 0, 0, 0);
-                        const uint32_t j = j0 + 8 * hh;
-                        if (slot_arr[r] == int32_t(slot) && j < p.max_rank)
-                            tv = *reinterpret_cast<const uint4*>(p.t + size_t(m0 + r) * p.max_rank + j);
-                        sts128(xt + sw128_off(r, 2 * g + hh), tv.x, tv.y, tv.z, tv.w);
+#pragma unroll
+                        for (uint32_t u = 0; u < T_TASKS; ++u) {
+                            const uint32_t task = td + u * DEQ_THREADS;
+                            const uint32_t r = task >> 1, jj = j0 + 8 * (task & 1u);
+                            if (task < uint32_t(MT) * 2 && slot_arr[r] == int32_t(slot) && jj < p.max_rank)
+                                tv[g][u] = *reinterpret_cast<const uint4*>(p.t + size_t(m0 + r) * p.max_rank + jj);
+                        }
                     }
                 }
+                ok = mbar_wait(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t xt = x_tile0 + s * C::X_TILE_BYTES;
+#pragma unroll
+                for (uint32_t g = 0; g < 4; ++g) {
+                    if (g < ng) {
+                        // B_s[f, j0 + 8 half .. +8): 4 columns at 8 g + 4 half
+                        tmem_st4(tmem_a0 + lane_base + s * C::A_COLS + 8 * g + 4 * half, bv[g].x, bv[g].y, bv[g].z, bv[g].w);
+#pragma unroll
+                        for (uint32_t u = 0; u < T_TASKS; ++u) {
+                            const uint32_t task = td + u * DEQ_THREADS;
+                            if (task < uint32_t(MT) * 2)
+                                sts128(xt + sw128_off(task >> 1, 2 * g + (task & 1u)), tv[g][u].x, tv[g][u].y, tv[g][u].z, tv[g][u].w);
+                        }
+                    }
+                }
+                tmem_st_wait();
+                tcgen05_fence_before();
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(BAR_FULL_W + 8 * s);
+                if (lane == 0) mbar_arrive(BAR_FULL + 8 * s);
+                if (td == 0) mbar_arrive(BAR_FULL + 8 * s);     // stands in for the TMA producer's arrival
             }
+        }
+        if (prof && td == 0) prof_row[6] = (unsigned long long)(clock64() - t_lora);
+
+        // ---- join the epilogue ----
+        if (ok && mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE)) {
+            tcgen05_fence_after();
+            epilogue_columns<MT>(p, tmem_acc, q, lane, f0, m0, 1 + half, 3);
         }
     }
 
@@ -509,6 +645,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_acc, C::TMEM_COLS);
+        if (prof && lane == 0) { prof_row[1] = (unsigned long long)(clock64() - t_entry); prof_row[8] = t_entry_ns; prof_row[9] = global_timer_ns(); }
     }
 }
 

@@ -193,6 +193,14 @@ ATLAS_B200_API int atlas_b200_select_victim_slot(const size_t* slot_index, const
 ATLAS_B200_API int atlas_b200_device_status(uint32_t* out_word, int clear);
 /* Kernel family chosen by the most recent fused / base call on this thread. */
 ATLAS_B200_API int atlas_b200_last_variant(void);
+/* Per-CTA cycle counters of the tcgen05 kernel, the counterpart of the reference's per-phase timers
+ * (crates/spark-model/src/layers/qwen3_attention/trait_impl/multi_seq/mod.rs:125-141).  While a device
+ * buffer of `n_words` u64 is set (10 words per CTA, CTA index = blockIdx.y * gridDim.x + blockIdx.x) each
+ * launch that fits writes, in SM cycles unless noted: [0] low 32 bits: MMA thread waiting for operands,
+ * high 32 bits: kernel entry to first MMA wait; [1] CTA lifetime; [2] MMA role total; [3] expansion warps
+ * waiting for raw weights; [4] waiting for a free stage; [5] expansion total; [6] LoRA operand build;
+ * [7] epilogue; [8]/[9] %globaltimer (ns) at CTA entry / exit.  Pass NULL to switch it off (default). */
+ATLAS_B200_API int atlas_b200_set_profile_buffer(void* device_buffer, size_t n_words);
 ATLAS_B200_API const char* atlas_b200_version(void);
 
 #ifdef __cplusplus
