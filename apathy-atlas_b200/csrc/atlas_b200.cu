@@ -80,7 +80,15 @@ static bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem, con
 // ---------------------------------------------------------------------------------------------
 namespace ops {
 
-static int launch_shrink(const ShrinkParams& p, uint32_t n_slots, cudaStream_t st) {
+static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool release_dependents = false) {
+    p.release_dependents = release_dependents ? 1u : 0u;
+    // Same shared-memory carve-out as the tcgen05 kernel, so that kernel's CTAs can become resident
+    // next to this grid's instead of waiting for the SMs to drain and be reconfigured.
+    static bool carveout_set = false;
+    if (!carveout_set) {
+        cudaFuncSetAttribute(lora_shrink_grouped_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        carveout_set = true;
+    }
     if (p.M == 0 || p.max_rank == 0) return ATLAS_B200_OK;
     dim3 grid(n_slots, (p.max_rank + SHRINK_RT - 1) / SHRINK_RT, (p.M + SHRINK_TC - 1) / SHRINK_TC);
     if (grid.y > 65535 || grid.z > 65535) return ATLAS_B200_ERR_LIMIT;
@@ -188,7 +196,7 @@ static bool tc_eligible(const atlas_b200_linear_desc& d) {
 }
 
 template <int MT>
-static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, cudaStream_t st) {
+static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_shrink, cudaStream_t st) {
     using C = tc::Cfg<MT>;
     Runtime& rt = runtime();
     if (!rt.tc_attr_set[slot_idx]) {
@@ -221,8 +229,21 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, cudaStream_t
     dim3 grid((d.n + tc::FT - 1) / tc::FT, (d.m + MT - 1) / MT);
     p.profile = (g_profile_buf && size_t(grid.x) * grid.y * tc::PROFILE_WORDS <= g_profile_words) ? g_profile_buf : nullptr;
     if (grid.y > 65535) return ATLAS_B200_ERR_LIMIT;
-    tc::nvfp4_lora_linear_tc_kernel<MT><<<grid, tc::NUM_THREADS, C::SMEM_BYTES, st>>>(map_x, map_w, map_s, p);
-    return launch_status();
+    // Launched as a programmatic dependent of the shrink that precedes it in the stream: its CTAs
+    // may start while the shrink still runs (the shrink releases them as soon as it is resident) and
+    // wait for the shrink's completion only where they first read t, after the base K loop.
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(tc::NUM_THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = after_shrink ? 1 : 0;
+    p.wait_for_shrink = after_shrink ? 1u : 0u;
+    return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_kernel<MT>, map_x, map_w, map_s, p));
 }
 
 static int validate_linear(const atlas_b200_linear_desc& d) {
@@ -263,14 +284,15 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
             sp.out = static_cast<uint16_t*>(d.lora_t);
             sp.M = d.m; sp.k_in = d.k; sp.max_rank = d.max_rank; sp.x_row_stride = d.x_row_stride; sp.max_loras = d.max_loras;
             sp.post = 1.0f / (d.scale2 * kWeightPreScale);
-            rc = launch_shrink(sp, d.max_loras, st);
+            rc = launch_shrink(sp, d.max_loras, st, true);
             if (rc) return rc;
         }
-        if (d.m <= 16) rc = launch_tc<16>(d, 0, st);
-        else if (d.m <= 32) rc = launch_tc<32>(d, 1, st);
-        else if (d.m <= 64) rc = launch_tc<64>(d, 2, st);
-        else if (d.m <= 128) rc = launch_tc<128>(d, 3, st);
-        else rc = launch_tc<256>(d, 4, st);
+        const bool after_shrink = d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK);
+        if (d.m <= 16) rc = launch_tc<16>(d, 0, after_shrink, st);
+        else if (d.m <= 32) rc = launch_tc<32>(d, 1, after_shrink, st);
+        else if (d.m <= 64) rc = launch_tc<64>(d, 2, after_shrink, st);
+        else if (d.m <= 128) rc = launch_tc<128>(d, 3, after_shrink, st);
+        else rc = launch_tc<256>(d, 4, after_shrink, st);
         if (rc == ATLAS_B200_OK) t_last_variant = ATLAS_B200_VARIANT_TCGEN05;
         return rc;
     }

@@ -89,6 +89,7 @@ struct Params {
     uint16_t* y;
     uint32_t M, N, K, out_row_stride, max_loras, max_rank;
     float out_scale;               // scale2 * 2^8
+    uint32_t wait_for_shrink;      // launched as a programmatic dependent of the shrink: wait before reading t
     unsigned long long* profile;   // nullable: per-CTA wait/busy cycle counters (PROFILE_WORDS per CTA)
 };
 
@@ -122,12 +123,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 
 // Bounded wait.  Returns false when the CTA is aborting (this waiter's limit expired, or
-// another role raised the flag).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code) {
+// another role raised the flag).  `backoff_ns` > 0 makes a waiter that expects to wait long (the
+// epilogue warps during the main loop) sleep between polls: a polling warp otherwise takes issue
+// slots and shared-memory bandwidth from the warps that feed the tensor pipe.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code,
+                                          uint32_t backoff_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     uint32_t spins = 0;
     while (true) {
+        if (backoff_ns) __nanosleep(backoff_ns);
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63u) == 0u) {
             if (*abort_flag) return false;
@@ -232,6 +237,13 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+
+// 16-byte global -> shared copy; src_bytes < 16 zero-fills the remainder (0 = all zeros, nothing read)
+__device__ __forceinline__ void cp_async_16_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // byte offset of logical 16-byte chunk `c` (0..7) of row `r` in a SWIZZLE_128B tile of 128-byte rows
 __device__ __forceinline__ uint32_t sw128_off(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
@@ -387,7 +399,9 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 if (progressed) {
                     spins = 0;
                     t0 = 0;
-                } else if ((++spins & 63u) == 0u) {
+                } else {
+                    __nanosleep(64);
+                    if ((++spins & 63u) != 0u) continue;
                     if (*abort_flag) break;
                     const uint64_t now = global_timer_ns();
                     if (t0 == 0) t0 = now;
@@ -414,26 +428,34 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             uint32_t bar_full = BAR_FULL, bar_empty = BAR_EMPTY, a_tmem = tmem_a0;
             uint64_t b_desc = make_kmajor_sw128_desc(x_tile0);
             constexpr uint64_t b_desc_step = uint64_t(C::X_TILE_BYTES >> 4);
+            bool ready = false;                              // result of an early look at this block's barrier
             for (uint32_t it = 0; it < num_kb; ++it) {
-                ok = mbar_wait_timed(bar_full, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full);
-                if (!ok) break;
+                if (!ready) {
+                    ok = mbar_wait_timed(bar_full, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full);
+                    if (!ok) break;
+                }
                 tcgen05_fence_after();
+                // next block's stage / phase / operands
+                uint32_t n_full = bar_full + 8, n_empty = bar_empty + 8, n_a = a_tmem + C::A_COLS, n_ph = ph;
+                uint64_t n_b = b_desc + b_desc_step;
+                if (++s == uint32_t(C::STAGES)) {
+                    s = 0; n_ph ^= 1u;
+                    n_full = BAR_FULL; n_empty = BAR_EMPTY; n_a = tmem_a0; n_b = b_desc - b_desc_step * (C::STAGES - 1);
+                }
                 // 16 k per instruction: 8 TMEM columns of A, 32 bytes along the swizzled row of B
                 umma_bf16_ts(tmem_acc, a_tmem, b_desc, idesc, acc);
                 umma_bf16_ts(tmem_acc, a_tmem + 8, b_desc + 2, idesc, 1u);
+                // look at the next block's barrier while the tensor pipe still holds queued work
+                ready = mbar_try_wait(n_full, n_ph);
                 umma_bf16_ts(tmem_acc, a_tmem + 16, b_desc + 4, idesc, 1u);
                 umma_bf16_ts(tmem_acc, a_tmem + 24, b_desc + 6, idesc, 1u);
                 umma_commit(bar_empty);
                 acc = 1u;
-                if (++s == uint32_t(C::STAGES)) {
-                    s = 0; ph ^= 1u;
-                    bar_full = BAR_FULL; bar_empty = BAR_EMPTY; a_tmem = tmem_a0; b_desc -= b_desc_step * (C::STAGES - 1);
-                } else {
-                    bar_full += 8; bar_empty += 8; a_tmem += C::A_COLS; b_desc += b_desc_step;
-                }
+                bar_full = n_full; bar_empty = n_empty; a_tmem = n_a; b_desc = n_b; ph = n_ph;
             }
+            ready = false;
             // base K blocks issued; the LoRA K blocks follow once the granule list is known
-            if (ok) ok = mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_MMA);
+            if (ok) ok = mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_MMA, 32);
             if (ok) {
                 const uint32_t n_gran = misc[1];
                 for (uint32_t g0 = 0; g0 < n_gran; g0 += 4) {
@@ -504,7 +526,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         if (te == 0) mbar_arrive(BAR_LIST);
 
         // ---- epilogue, shared with the expansion warps: TMEM lane = feature, column = token ----
-        if (mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE)) {
+        if (mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 512)) {
             const long long t_epi = clock64();
             tcgen05_fence_after();
             epilogue_columns<MT>(p, tmem_acc, warp & 3u, lane, f0, m0, 0, 3);
@@ -513,7 +535,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     } else {
         // ========================== NVFP4 -> BF16 weight operand, into TMEM ======================
         // warp w may touch TMEM lanes [32 (w % 4), +32): it owns those 32 features; the two warps
-        // of a quadrant split each K block in halves of 32.
+        // of a quadrant split each K block in halves of 32.  K blocks are expanded two at a time so
+        // that each warp has two independent dependency chains in flight.
         const uint32_t q = warp & 3u;
         const uint32_t half = (warp - DEQ_WARP0) >> 2;
         const uint32_t row = q * 32 + lane;
@@ -523,112 +546,144 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         unsigned long long w_raw = 0, w_empty = 0;
         const long long t_begin = clock64();
         const uint32_t num_raw = (num_kb + 3u) / 4u;
+        uint32_t s = 0, ph = 0;                              // stage / phase of the next K block to fill
+        uint32_t rs = 0, rph = 0;
         for (uint32_t ri = 0; ok && ri < num_raw; ++ri) {
-            const uint32_t rs = ri % RAW_STAGES, rph = (ri / RAW_STAGES) & 1u;
             ok = mbar_wait_timed(BAR_FULL_RAW + 8 * rs, rph, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_raw);
             if (!ok) break;
             const uint4 sc4 = lds128(raws0 + rs * RAW_SCALE_BYTES + row * 16);
             const uint32_t scw[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) {
-                const uint32_t it = ri * 4 + j;
-                if (it >= num_kb) break;
-                // 32 codes of this row: logical chunk 2j + half of the swizzled 128-byte raw row
-                const uint4 pk = lds128(rawp0 + rs * RAW_PACKED_BYTES + sw128_off(row, 2 * j + half));
-                const uint32_t pw[4] = {pk.x, pk.y, pk.z, pk.w};
-                const uint32_t sbytes = scw[j] >> (16 * half);      // scale bytes 2*half, 2*half+1 of word j
-                const uint32_t mul0 = e4m3_to_bf16x2_shifted(sbytes & 0xFFu);
-                const uint32_t mul1 = e4m3_to_bf16x2_shifted((sbytes >> 8) & 0xFFu);
-                uint32_t o[16];
+            for (uint32_t jp = 0; jp < 4; jp += 2) {
+                if (ri * 4 + jp >= num_kb) break;
+                const bool two = ri * 4 + jp + 1 < num_kb;
+                uint32_t o[2][16];
 #pragma unroll
-                for (uint32_t qd = 0; qd < 4; ++qd) {
-                    uint32_t o4[4];
-                    e2m1x8_to_bf16x8(pw[qd], qd < 2 ? mul0 : mul1, o4);
-                    o[4 * qd] = o4[0]; o[4 * qd + 1] = o4[1]; o[4 * qd + 2] = o4[2]; o[4 * qd + 3] = o4[3];
+                for (uint32_t u = 0; u < 2; ++u) {
+                    const uint32_t j = jp + u;
+                    // 32 codes of this row: logical chunk 2j + half of the swizzled 128-byte raw row
+                    const uint4 pk = lds128(rawp0 + rs * RAW_PACKED_BYTES + sw128_off(row, 2 * j + half));
+                    const uint32_t pw[4] = {pk.x, pk.y, pk.z, pk.w};
+                    const uint32_t sbytes = scw[j] >> (16 * half);      // scale bytes 2*half, 2*half+1 of word j
+                    const uint32_t mul0 = e4m3_to_bf16x2_shifted(sbytes & 0xFFu);
+                    const uint32_t mul1 = e4m3_to_bf16x2_shifted((sbytes >> 8) & 0xFFu);
+#pragma unroll
+                    for (uint32_t qd = 0; qd < 4; ++qd) {
+                        uint32_t o4[4];
+                        e2m1x8_to_bf16x8(pw[qd], qd < 2 ? mul0 : mul1, o4);
+                        o[u][4 * qd] = o4[0]; o[u][4 * qd + 1] = o4[1]; o[u][4 * qd + 2] = o4[2]; o[u][4 * qd + 3] = o4[3];
+                    }
                 }
-                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-                ok = mbar_wait_timed(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_empty);
+                const uint32_t s0 = s, ph0 = ph;
+                uint32_t s1 = s0 + 1, ph1 = ph0;
+                if (s1 == uint32_t(C::STAGES)) { s1 = 0; ph1 ^= 1u; }
+                ok = mbar_wait_timed(BAR_EMPTY + 8 * s0, ph0 ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_empty);
                 if (!ok) break;
                 tcgen05_fence_after();
                 // this thread's 32 k of its feature row: 16 columns at 16 * half of the stage
-                tmem_st16(tmem_a0 + lane_base + s * C::A_COLS + 16 * half, o);
+                tmem_st16(tmem_a0 + lane_base + s0 * C::A_COLS + 16 * half, o[0]);
+                if (two) {
+                    ok = mbar_wait_timed(BAR_EMPTY + 8 * s1, ph1 ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_empty);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    tmem_st16(tmem_a0 + lane_base + s1 * C::A_COLS + 16 * half, o[1]);
+                }
                 tmem_st_wait();
                 tcgen05_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(BAR_FULL + 8 * s);
+                if (lane == 0) {
+                    mbar_arrive(BAR_FULL + 8 * s0);
+                    if (two) mbar_arrive(BAR_FULL + 8 * s1);
+                }
+                if (two) { s = s1 + 1; ph = ph1; } else { s = s1; ph = ph1; }
+                if (s == uint32_t(C::STAGES)) { s = 0; ph ^= 1u; }
             }
             if (!ok) break;
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR_EMPTY_RAW + 8 * rs);
+            if (++rs == uint32_t(RAW_STAGES)) { rs = 0; rph ^= 1u; }
         }
         if (prof && td == 0) {
             prof_row[3] = w_raw; prof_row[4] = w_empty; prof_row[5] = (unsigned long long)(clock64() - t_begin);
         }
         const long long t_lora = clock64();
 
-        // ---- LoRA K blocks: weight operand = rows of B_s (TMEM), activation operand = masked rows
-        //      of t (shared memory, written here with generic stores) ----
-        if (ok) ok = mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
+        // ---- LoRA K blocks: weight operand = rows of B_s (registers -> TMEM), activation operand =
+        //      masked rows of t, copied global -> shared with cp.async (zero-filled where the token
+        //      is routed elsewhere).  Loads of block lb+1 are in flight while block lb is handed over.
+        if (ok) ok = mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, 32);
+        // t is produced by the shrink grid this kernel may have overtaken: everything above ran
+        // without it; from here on its writes must be complete and visible.
+        if (p.wait_for_shrink) asm volatile("griddepcontrol.wait;" ::: "memory");
         if (ok) {
             const uint32_t n_gran = misc[1];
+            const uint32_t n_lb = (n_gran + 3u) / 4u;
             const uint32_t f = f0 + row;
             constexpr uint32_t T_TASKS = (uint32_t(MT) * 2 + DEQ_THREADS - 1) / DEQ_THREADS;   // per granule
-            for (uint32_t lb = 0; ok && lb * 4 < n_gran; ++lb) {
-                const uint32_t it = num_kb + lb;
-                const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+            uint4 bcur[4], bnext[4];
+            uint32_t ls = s, lph = ph;                       // stage / phase of the block being LOADED
+            auto issue_loads = [&](uint32_t lb, uint4 (&bvv)[4]) -> bool {
+                // the activation tile of this stage is rewritten: wait until the MMA has released it
+                if (!mbar_wait(BAR_EMPTY + 8 * ls, lph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT)) return false;
+                const uint32_t xt = x_tile0 + ls * C::X_TILE_BYTES;
                 const uint32_t ng = min(4u, n_gran - lb * 4);
-                // issue every global load of the block before the first use
-                uint4 bv[4], tv[4][T_TASKS];
 #pragma unroll
                 for (uint32_t g = 0; g < 4; ++g) {
-                    bv[g] = make_uint4(0, 0, 0, 0);
-#pragma unroll
-                    for (uint32_t u = 0; u < T_TASKS; ++u) tv[g][u] = make_uint4(0, 0, 0, 0);
+                    bvv[g] = make_uint4(0, 0, 0, 0);
                     if (g < ng) {
                         const uint32_t e = gran[lb * 4 + g];
                         const uint32_t slot = e >> 2, j0 = (e & 3u) * 16u;
                         const uint32_t j = j0 + 8 * half;
                         if (f < p.N && j < p.max_rank)
-                            bv[g] = __ldg(reinterpret_cast<const uint4*>(
+                            bvv[g] = __ldg(reinterpret_cast<const uint4*>(
                                 reinterpret_cast<const uint16_t*>(p.b_table[slot]) + size_t(f) * p.max_rank + j));
 #pragma unroll
                         for (uint32_t u = 0; u < T_TASKS; ++u) {
                             const uint32_t task = td + u * DEQ_THREADS;
-                            const uint32_t r = task >> 1, jj = j0 + 8 * (task & 1u);
-                            if (task < uint32_t(MT) * 2 && slot_arr[r] == int32_t(slot) && jj < p.max_rank)
-                                tv[g][u] = *reinterpret_cast<const uint4*>(p.t + size_t(m0 + r) * p.max_rank + jj);
+                            if (task < uint32_t(MT) * 2) {
+                                const uint32_t r = task >> 1, jj = j0 + 8 * (task & 1u);
+                                const bool hit = slot_arr[r] == int32_t(slot) && jj < p.max_rank;
+                                // a miss copies 0 bytes and zero-fills the 16-byte destination
+                                const uint16_t* src = hit ? p.t + size_t(m0 + r) * p.max_rank + jj : p.t;
+                                cp_async_16_zfill(xt + sw128_off(r, 2 * g + (task & 1u)), src, hit ? 16u : 0u);
+                            }
                         }
                     }
                 }
-                ok = mbar_wait(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
-                if (!ok) break;
+                cp_async_commit();
+                if (++ls == uint32_t(C::STAGES)) { ls = 0; lph ^= 1u; }
+                return true;
+            };
+            if (n_lb > 0) ok = issue_loads(0, bcur);
+            for (uint32_t lb = 0; ok && lb < n_lb; ++lb) {
+                if (lb + 1 < n_lb) {
+                    ok = issue_loads(lb + 1, bnext);
+                    if (!ok) break;
+                    cp_async_wait_group<1>();
+                } else {
+                    cp_async_wait_group<0>();
+                }
+                const uint32_t ng = min(4u, n_gran - lb * 4);
                 tcgen05_fence_after();
-                const uint32_t xt = x_tile0 + s * C::X_TILE_BYTES;
 #pragma unroll
-                for (uint32_t g = 0; g < 4; ++g) {
-                    if (g < ng) {
-                        // B_s[f, j0 + 8 half .. +8): 4 columns at 8 g + 4 half
-                        tmem_st4(tmem_a0 + lane_base + s * C::A_COLS + 8 * g + 4 * half, bv[g].x, bv[g].y, bv[g].z, bv[g].w);
-#pragma unroll
-                        for (uint32_t u = 0; u < T_TASKS; ++u) {
-                            const uint32_t task = td + u * DEQ_THREADS;
-                            if (task < uint32_t(MT) * 2)
-                                sts128(xt + sw128_off(task >> 1, 2 * g + (task & 1u)), tv[g][u].x, tv[g][u].y, tv[g][u].z, tv[g][u].w);
-                        }
-                    }
-                }
+                for (uint32_t g = 0; g < 4; ++g)   // B_s[f, j0 + 8 half .. +8): 4 columns at 8 g + 4 half
+                    if (g < ng) tmem_st4(tmem_a0 + lane_base + s * C::A_COLS + 8 * g + 4 * half,
+                                         bcur[g].x, bcur[g].y, bcur[g].z, bcur[g].w);
                 tmem_st_wait();
                 tcgen05_fence_before();
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(BAR_FULL + 8 * s);
                 if (td == 0) mbar_arrive(BAR_FULL + 8 * s);     // stands in for the TMA producer's arrival
+                if (++s == uint32_t(C::STAGES)) { s = 0; ph ^= 1u; }
+#pragma unroll
+                for (uint32_t g = 0; g < 4; ++g) bcur[g] = bnext[g];
             }
         }
         if (prof && td == 0) prof_row[6] = (unsigned long long)(clock64() - t_lora);
 
         // ---- join the epilogue ----
-        if (ok && mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE)) {
+        if (ok && mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 64)) {
             tcgen05_fence_after();
             epilogue_columns<MT>(p, tmem_acc, q, lane, f0, m0, 1 + half, 3);
         }

@@ -126,6 +126,7 @@ struct ShrinkParams {
     uint16_t* out;                  // [M, max_rank]
     uint32_t M, k_in, max_rank, x_row_stride, max_loras;
     float post;                     // 0 => unscaled output
+    uint32_t release_dependents;    // let a programmatic dependent launch start while this grid runs
 };
 
 __global__ void __launch_bounds__(SHRINK_THREADS)
@@ -134,6 +135,9 @@ lora_shrink_grouped_kernel(const ShrinkParams p) {
     __shared__ uint32_t warp_count[SHRINK_THREADS / 32];
     __shared__ float red[SHRINK_THREADS / 32][SHRINK_TG * SHRINK_RT];
 
+    // The fused layer launches its main kernel as a programmatic dependent of this grid; it reads
+    // this grid's output only behind its own griddepcontrol.wait, so it may start right away.
+    if (p.release_dependents) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t s = blockIdx.x;
     const uint32_t j0 = blockIdx.y * SHRINK_RT;
