@@ -70,7 +70,8 @@ template <int MT> struct Cfg {
     static constexpr int OFF_RAWS = OFF_RAWP + RAW_STAGES * RAW_PACKED_BYTES;
     static constexpr int OFF_SLOT = OFF_RAWS + RAW_STAGES * RAW_SCALE_BYTES;     // int32[MT]
     static constexpr int OFF_GRAN = OFF_SLOT + MT * 4;                           // uint16[MAX_GRANULES]
-    static constexpr int OFF_BITMAP = OFF_GRAN + MAX_GRANULES * 2;               // uint32[128]
+    static constexpr int OFF_GRANB = OFF_GRAN + MAX_GRANULES * 2;                // uint64[MAX_GRANULES]: B_s address of the granule
+    static constexpr int OFF_BITMAP = OFF_GRANB + MAX_GRANULES * 8;              // uint32[128]
     static constexpr int OFF_SCAN = OFF_BITMAP + (MAX_LORAS_TC / 32) * 4;        // uint32[8]
     static constexpr int OFF_BAR = OFF_SCAN + 64;                                // mbarriers
     static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_STAGES + 2;
@@ -306,6 +307,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     const uint32_t raws0 = smem_base + C::OFF_RAWS;
     int32_t* slot_arr = reinterpret_cast<int32_t*>(smem_gen + C::OFF_SLOT);
     uint16_t* gran = reinterpret_cast<uint16_t*>(smem_gen + C::OFF_GRAN);
+    unsigned long long* gran_b = reinterpret_cast<unsigned long long*>(smem_gen + C::OFF_GRANB);
     uint32_t* bitmap = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_BITMAP);
     uint32_t* scan = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_SCAN);
     const uint32_t bar0 = smem_base + C::OFF_BAR;
@@ -518,12 +520,25 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             for (uint32_t w = word; w; w &= w - 1) {
                 const uint32_t s = te * 32 + (__ffs(w) - 1);
                 const uint32_t r = p.rank_table ? min(p.rank_table[s], p.max_rank) : p.max_rank;
-                for (uint32_t g = 0; g < (r + 15u) / 16u; ++g) gran[pos++] = uint16_t((s << 2) | g);
+                const unsigned long long b_addr = p.b_table[s];
+                for (uint32_t g = 0; g < (r + 15u) / 16u; ++g) { gran_b[pos] = b_addr; gran[pos++] = uint16_t((s << 2) | g); }
             }
             if (te == 0) misc[1] = n_gran;
             named_bar_sync(1, EPI_THREADS);
         }
         if (te == 0) mbar_arrive(BAR_LIST);
+        // Pull this CTA's rows of every B_s it will need into L2 now, while the base K loop runs:
+        // the LoRA K blocks at the end then see L2 latency instead of HBM latency.
+        if (n_gran) {
+            const uint32_t f = f0 + te;
+            if (f < p.N) {
+                for (uint32_t g = 0; g < n_gran; ++g) {
+                    const uint32_t e = gran[g];
+                    const uint16_t* src = reinterpret_cast<const uint16_t*>(gran_b[g]) + size_t(f) * p.max_rank + (e & 3u) * 16u;
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+                }
+            }
+        }
 
         // ---- epilogue, shared with the expansion warps: TMEM lane = feature, column = token ----
         if (mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 512)) {
@@ -636,7 +651,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                         const uint32_t j = j0 + 8 * half;
                         if (f < p.N && j < p.max_rank)
                             bvv[g] = __ldg(reinterpret_cast<const uint4*>(
-                                reinterpret_cast<const uint16_t*>(p.b_table[slot]) + size_t(f) * p.max_rank + j));
+                                reinterpret_cast<const uint16_t*>(gran_b[lb * 4 + g]) + size_t(f) * p.max_rank + j));
 #pragma unroll
                         for (uint32_t u = 0; u < T_TASKS; ++u) {
                             const uint32_t task = td + u * DEQ_THREADS;
