@@ -29,7 +29,7 @@ MODULES = ("q", "k", "v", "o", "gate", "up", "down")
 EXPORTS = (
     "atlas_b200_lora_bgmv", "atlas_b200_lora_delta", "atlas_b200_w4a16_gemm",
     "atlas_b200_dequant_nvfp4_to_bf16", "atlas_b200_quantize_bf16_to_nvfp4",
-    "atlas_b200_nvfp4_lora_linear", "atlas_b200_column_shard",
+    "atlas_b200_nvfp4_lora_linear", "atlas_b200_nvfp4_lora_linear_noalloc", "atlas_b200_column_shard",
     "atlas_b200_build_seq_slot", "atlas_b200_routed_prefill_slot_of", "atlas_b200_peft_scaling",
     "atlas_b200_module_dims", "atlas_b200_pool_slot_bytes", "atlas_b200_slot_base_offset",
     "atlas_b200_module_slot_offsets", "atlas_b200_pack_module", "atlas_b200_select_victim_slot",
@@ -83,6 +83,7 @@ def lib() -> C.CDLL:
     L.atlas_b200_dequant_nvfp4_to_bf16.argtypes = [vp, vp, vp, f32, u32, u32, vp]
     L.atlas_b200_quantize_bf16_to_nvfp4.argtypes = [vp, vp, vp, f32, u32, u32, vp]
     L.atlas_b200_nvfp4_lora_linear.argtypes = [C.POINTER(LinearDesc), vp]
+    L.atlas_b200_nvfp4_lora_linear_noalloc.argtypes = [C.POINTER(LinearDesc), vp]
     L.atlas_b200_column_shard.argtypes = [u32, u32, u32, C.POINTER(u32), C.POINTER(u32)]
     L.atlas_b200_build_seq_slot.argtypes = [C.POINTER(i32), sz, sz, i32, C.POINTER(i32)]
     L.atlas_b200_routed_prefill_slot_of.argtypes = [i32, sz, sz]
@@ -257,6 +258,21 @@ def make_linear_desc(*, x, m, k, n, y, w_packed=None, w_scale=None, scale2=1.0, 
 def nvfp4_lora_linear(desc: LinearDesc, stream=None) -> int:
     """Launch the fused layer; returns the kernel family that ran (VARIANT_*)."""
     _check("atlas_b200_nvfp4_lora_linear", lib().atlas_b200_nvfp4_lora_linear(C.byref(desc), _stream_ptr(stream)))
+    return lib().atlas_b200_last_variant()
+
+
+STATIC_SCRATCH_ELEMS = 512 * 1024
+
+
+def nvfp4_lora_linear_noalloc(desc: LinearDesc, stream=None) -> int:
+    """The fused layer without a caller-provided shrink scratch (`desc.lora_t` is ignored).
+
+    For callers that may launch kernels but may not allocate device memory: the scratch is a fixed
+    1 MiB array inside the library (m * max_rank <= STATIC_SCRATCH_ELEMS, else AtlasError -5).  Calls
+    share that array, so calls that could overlap on the GPU must be serialised by the caller.
+    Returns the kernel family that ran (VARIANT_*)."""
+    _check("atlas_b200_nvfp4_lora_linear_noalloc",
+           lib().atlas_b200_nvfp4_lora_linear_noalloc(C.byref(desc), _stream_ptr(stream)))
     return lib().atlas_b200_last_variant()
 
 

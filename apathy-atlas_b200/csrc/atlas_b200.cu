@@ -391,6 +391,64 @@ int atlas_b200_nvfp4_lora_linear(const atlas_b200_linear_desc* desc, void* strea
     return ops::nvfp4_lora_linear(*desc, static_cast<cudaStream_t>(stream));
 }
 
+// ---------------------------------------------------------------------------------------------
+// Fused layer for callers that cannot allocate device memory.
+//
+// Some hosts of this library may launch kernels but may not call cudaMalloc: a plug-in that is
+// handed tensors by an engine which owns every byte of device memory, or code running inside a
+// region (a captured serving step, a real-time loop) where the allocator must not be entered.
+// Such a caller has nowhere to get the shrink scratch `lora_t` from.  This entry point keeps that
+// scratch in a fixed array inside the library image instead, so the caller passes inputs and the
+// output only.
+//
+// The array holds ATLAS_B200_STATIC_SCRATCH_ELEMS BF16 values (1 MiB) on every GPU that loads the
+// library, for the life of the process.  A call needs m * max_rank of them; more is refused.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) uint16_t g_static_lora_t[ATLAS_B200_STATIC_SCRATCH_ELEMS];
+
+namespace atlas {
+// In host code `g_static_lora_t` names a host-side shadow of the symbol, not device memory, so the
+// device address is asked for once per device, with that device current, and cached.
+static constexpr int kMaxDevices = 64;
+static void* g_static_scratch_addr[kMaxDevices] = {};
+static std::mutex g_static_scratch_mutex;
+
+static int static_scratch_for_current_device(void** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_status(e);
+    if (dev < 0 || dev >= kMaxDevices) return ATLAS_B200_ERR_LIMIT;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (!g_static_scratch_addr[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_lora_t);
+        if (e != cudaSuccess) return cuda_status(e);
+        if (!ptr) return ATLAS_B200_ERR_NULL;
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return ATLAS_B200_OK;
+}
+}  // namespace atlas
+
+extern "C" int atlas_b200_nvfp4_lora_linear_noalloc(const atlas_b200_linear_desc* desc, void* stream) {
+    if (!desc) return ATLAS_B200_ERR_NULL;
+    atlas_b200_linear_desc d = *desc;
+    if (d.seq_slot) {
+        // validate the size before anything else so that an oversized call never touches the array
+        if (d.max_rank == 0 || d.max_loras == 0) return ATLAS_B200_ERR_DIMS;
+        if (uint64_t(d.m) * uint64_t(d.max_rank) > uint64_t(ATLAS_B200_STATIC_SCRATCH_ELEMS)) return ATLAS_B200_ERR_LIMIT;
+        void* scratch = nullptr;
+        const int rc = static_scratch_for_current_device(&scratch);
+        if (rc) return rc;
+        // Nothing in the scratch has to start at zero: the shrink writes every element of every routed
+        // row (pad ranks as zeros) and un-routed rows are never read, so leftovers of an earlier call
+        // are harmless and no clearing pass is launched.
+        d.lora_t = scratch;
+    }
+    return ops::nvfp4_lora_linear(d, static_cast<cudaStream_t>(stream));
+}
+
 int atlas_b200_device_status(uint32_t* out_word, int clear) {
     if (!out_word) return ATLAS_B200_ERR_NULL;
     cudaError_t e = cudaMemcpyFromSymbol(out_word, g_status_word, sizeof(uint32_t));

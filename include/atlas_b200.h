@@ -142,6 +142,23 @@ typedef struct atlas_b200_linear_desc {
 
 ATLAS_B200_API int atlas_b200_nvfp4_lora_linear(const atlas_b200_linear_desc* desc, void* stream);
 
+/* The fused layer for a caller that must not allocate device memory (no counterpart in the
+ * reference, whose callers size their scratch from a buffer arena).  Identical to
+ * atlas_b200_nvfp4_lora_linear except that `desc->lora_t` is ignored: the shrink scratch is a fixed
+ * array of ATLAS_B200_STATIC_SCRATCH_ELEMS BF16 values (1 MiB) that the library keeps on every GPU
+ * it is loaded on until the process exits.  Meant for plug-ins whose host engine owns all device
+ * memory, and for call sites where entering the CUDA allocator is forbidden.
+ *   - m * max_rank must not exceed ATLAS_B200_STATIC_SCRATCH_ELEMS, else -5 and nothing is launched.
+ *   - The first call on each device looks the array's device address up (with that device current);
+ *     make that first call outside any stream capture.  Later calls only launch kernels.
+ *   - The call itself never calls cudaMalloc / cudaFree or any allocating routine.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  The
+ *     kernels overwrite every element they later read, so nothing is cleared between calls; but two
+ *     calls whose kernels overlap on the GPU (different streams, or concurrent graph branches) race
+ *     on it.  Serialise such calls, or use atlas_b200_nvfp4_lora_linear with a scratch per stream. */
+#define ATLAS_B200_STATIC_SCRATCH_ELEMS (512u * 1024u)
+ATLAS_B200_API int atlas_b200_nvfp4_lora_linear_noalloc(const atlas_b200_linear_desc* desc, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Column-parallel sharding (split of N over `tp` ranks), as `shard_quantized_nvfp4`
  * ColumnParallel (crates/spark-model/src/tp_shard/quant_shard.rs:57-90): rank r owns output
