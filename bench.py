@@ -203,7 +203,7 @@ def main():
     def step():
         v = ab.nvfp4_lora_linear(desc, stream)
         if tp > 1:
-            dist.all_gather_into_tensor(y_all, y_loc)
+            dist.all_gather_into_tensor(y_all.view(tp * M, n_loc), y_loc)
         return v
 
     def barrier():
