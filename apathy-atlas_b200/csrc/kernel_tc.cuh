@@ -45,7 +45,7 @@ namespace tc {
 constexpr int FT = 128;              // features per CTA = UMMA M
 constexpr int KB = 64;               // K elements per MMA stage (one 128-byte swizzle row of BF16)
 constexpr int KRAW = 256;            // K elements per raw weight stage
-constexpr int RAW_STAGES = 3;
+constexpr int RAW_STAGES = 2;
 constexpr int RAW_PACKED_BYTES = FT * (KRAW / 2);    // 16 KiB
 constexpr int RAW_SCALE_BYTES = FT * (KRAW / 16);    // 2 KiB
 constexpr int NUM_THREADS = 448;
@@ -634,7 +634,23 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             const uint32_t n_gran = misc[1];
             const uint32_t n_lb = (n_gran + 3u) / 4u;
             const uint32_t f = f0 + row;
+            // Activation side of a granule: MT rows x 2 chunks of 16 bytes.  Task -> (row = task % MT,
+            // chunk = task / MT), so eight neighbouring lanes write eight different swizzled chunks.
+            // Everything that does not depend on the granule is computed once per thread.
             constexpr uint32_t T_TASKS = (uint32_t(MT) * 2 + DEQ_THREADS - 1) / DEQ_THREADS;   // per granule
+            int32_t t_slot[T_TASKS];
+            const uint16_t* t_src[T_TASKS];
+            uint32_t t_dst[T_TASKS], t_xor[T_TASKS], t_hh[T_TASKS];
+#pragma unroll
+            for (uint32_t u = 0; u < T_TASKS; ++u) {
+                const uint32_t task = td + u * DEQ_THREADS;
+                const uint32_t r = task & (uint32_t(MT) - 1u), hh = task / uint32_t(MT);
+                t_hh[u] = hh;
+                t_slot[u] = (task < uint32_t(MT) * 2) ? slot_arr[r] : -2;     // -2 never matches: no task
+                t_src[u] = p.t + size_t(m0 + r) * p.max_rank + 8 * hh;
+                t_dst[u] = r * 128u;
+                t_xor[u] = r & 7u;
+            }
             uint4 bcur[4], bnext[4];
             uint32_t ls = s, lph = ph;                       // stage / phase of the block being LOADED
             auto issue_loads = [&](uint32_t lb, uint4 (&bvv)[4]) -> bool {
@@ -647,20 +663,18 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     bvv[g] = make_uint4(0, 0, 0, 0);
                     if (g < ng) {
                         const uint32_t e = gran[lb * 4 + g];
-                        const uint32_t slot = e >> 2, j0 = (e & 3u) * 16u;
+                        const int32_t slot = int32_t(e >> 2);
+                        const uint32_t j0 = (e & 3u) * 16u;
                         const uint32_t j = j0 + 8 * half;
                         if (f < p.N && j < p.max_rank)
                             bvv[g] = __ldg(reinterpret_cast<const uint4*>(
                                 reinterpret_cast<const uint16_t*>(gran_b[lb * 4 + g]) + size_t(f) * p.max_rank + j));
 #pragma unroll
                         for (uint32_t u = 0; u < T_TASKS; ++u) {
-                            const uint32_t task = td + u * DEQ_THREADS;
-                            if (task < uint32_t(MT) * 2) {
-                                const uint32_t r = task >> 1, jj = j0 + 8 * (task & 1u);
-                                const bool hit = slot_arr[r] == int32_t(slot) && jj < p.max_rank;
+                            if (t_slot[u] != -2) {
                                 // a miss copies 0 bytes and zero-fills the 16-byte destination
-                                const uint16_t* src = hit ? p.t + size_t(m0 + r) * p.max_rank + jj : p.t;
-                                cp_async_16_zfill(xt + sw128_off(r, 2 * g + (task & 1u)), src, hit ? 16u : 0u);
+                                const bool hit = t_slot[u] == slot && j0 + 8 * t_hh[u] < p.max_rank;
+                                cp_async_16_zfill(xt + t_dst[u] + (((2 * g + t_hh[u]) ^ t_xor[u]) << 4), hit ? t_src[u] + j0 : p.t, hit ? 16u : 0u);
                             }
                         }
                     }

@@ -122,7 +122,11 @@ def run_reference_arm(args, case):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    step, rows, cores = cpu_sample(case)
+    # size the per-step sample so that the whole run stays near two minutes on this host
+    probe, probe_rows, _ = cpu_sample(case, budget_rows=min(4, case.M))
+    per_row = probe() / probe_rows
+    budget_rows = int(120.0 / max(args.steps + min(args.warmup, 1), 1) / max(per_row, 1e-9))
+    step, rows, cores = cpu_sample(case, budget_rows=max(1, min(case.M, budget_rows)))
     for _ in range(min(args.warmup, 1)):
         step()
     times = [step() for _ in range(args.steps)]
