@@ -54,6 +54,7 @@ class LinearDesc(C.Structure):
         ("max_loras", C.c_uint32), ("max_rank", C.c_uint32),
         ("y", C.c_void_p), ("out_row_stride", C.c_uint32), ("reserved0", C.c_uint32),
         ("lora_t", C.c_void_p), ("ws", C.c_void_p), ("ws_bytes", C.c_size_t),
+        ("b_pool_base", C.c_void_p), ("b_slot_stride", C.c_size_t),
     ]
 
 
@@ -202,6 +203,8 @@ class LoraRoute:
     max_rank: int
     max_loras: int
     rank_table: object = None   # optional [max_loras] u32 true ranks (not in the reference)
+    b_pool_base: object = None  # optional: B side of the pool as a strided array (see atlas_b200.h)
+    b_slot_stride: int = 0
 
 
 def apply_lora_bgmv(route: LoraRoute, x, base_out, seq_slot, n: int, x_row_stride: int, out_row_stride: int,
@@ -250,6 +253,7 @@ def make_linear_desc(*, x, m, k, n, y, w_packed=None, w_scale=None, scale2=1.0, 
         d.rank_table = _ptr(route.rank_table)
         d.max_loras, d.max_rank = route.max_loras, route.max_rank
         d.lora_t = _ptr(lora_t)
+        d.b_pool_base, d.b_slot_stride = _ptr(route.b_pool_base), route.b_slot_stride
     d.y = _ptr(y)
     d.out_row_stride = out_row_stride if out_row_stride is not None else n
     return d
@@ -329,6 +333,9 @@ class LoraPool:
         self.scale_table.copy_(torch.tensor(self._scale_host, dtype=torch.float32))
         self.rank_table.copy_(torch.tensor(self._rank_host, dtype=torch.int32))
 
-    def route(self, with_ranks: bool = True) -> LoraRoute:
-        return LoraRoute(self.a_table, self.b_table, self.scale_table, self.k_in, self.n_out,
-                         self.max_rank, self.max_loras, self.rank_table if with_ranks else None)
+    def route(self, with_ranks: bool = True, strided: bool = True) -> LoraRoute:
+        r = LoraRoute(self.a_table, self.b_table, self.scale_table, self.k_in, self.n_out,
+                      self.max_rank, self.max_loras, self.rank_table if with_ranks else None)
+        if strided:     # slot s of b_pool starts s * n_out * max_rank * 2 bytes after slot 0
+            r.b_pool_base, r.b_slot_stride = self.b_pool.data_ptr(), self.n_out * self.max_rank * 2
+        return r

@@ -20,6 +20,7 @@
 #include "common.cuh"
 #include "kernel_tc.cuh"
 #include "kernels_simt.cuh"
+#include "kernel_shrink_mma.cuh"
 
 namespace atlas {
 
@@ -82,14 +83,34 @@ namespace ops {
 
 static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool release_dependents = false) {
     p.release_dependents = release_dependents ? 1u : 0u;
+    if (p.M == 0 || p.max_rank == 0) return ATLAS_B200_OK;
     // Same shared-memory carve-out as the tcgen05 kernel, so that kernel's CTAs can become resident
     // next to this grid's instead of waiting for the SMs to drain and be reconfigured.
     static bool carveout_set = false;
     if (!carveout_set) {
         cudaFuncSetAttribute(lora_shrink_grouped_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(lora_shrink_mma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         carveout_set = true;
     }
-    if (p.M == 0 || p.max_rank == 0) return ATLAS_B200_OK;
+    // tensor-core shrink where rows can be read with aligned 128-bit loads in whole 32-element chunks
+    const bool mma_ok = (p.k_in % 32 == 0) && (p.x_row_stride % 8 == 0) && aligned(p.x, 16) &&
+                        (p.seq_slot || aligned(p.a_uniform, 4));
+    if (mma_ok) {
+        dim3 grid(n_slots * SHM_KSPLIT, (p.max_rank + SHM_RANKS - 1) / SHM_RANKS, (p.M + SHM_CHUNK - 1) / SHM_CHUNK);
+        if (grid.y > 65535 || grid.z > 65535) return ATLAS_B200_ERR_LIMIT;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(SHM_THREADS);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;      // SHM_KSPLIT CTAs along x share one (slot, ranks, chunk)
+        attr[0].val.clusterDim.x = SHM_KSPLIT;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        return cuda_status(cudaLaunchKernelEx(&cfg, lora_shrink_mma_kernel, p));
+    }
     dim3 grid(n_slots, (p.max_rank + SHRINK_RT - 1) / SHRINK_RT, (p.M + SHRINK_TC - 1) / SHRINK_TC);
     if (grid.y > 65535 || grid.z > 65535) return ATLAS_B200_ERR_LIMIT;
     lora_shrink_grouped_kernel<<<grid, SHRINK_THREADS, 0, st>>>(p);
@@ -205,7 +226,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
         if (e != cudaSuccess) return cuda_status(e);
         rt.tc_attr_set[slot_idx] = true;
     }
-    CUtensorMap map_x, map_w, map_s;
+    CUtensorMap map_x, map_w, map_s, map_b;
     if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.x, d.k, d.m, uint64_t(d.x_row_stride) * 2, tc::KB, MT,
                    CU_TENSOR_MAP_SWIZZLE_128B))
         return ATLAS_B200_ERR_DIMS;
@@ -216,7 +237,24 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
                    CU_TENSOR_MAP_SWIZZLE_NONE))
         return ATLAS_B200_ERR_DIMS;
 
+    // B side of the adapter pool as one 3-D tensor [max_loras][n][max_rank]: box = one granule of one slot
+    const bool b_strided = d.seq_slot && d.b_pool_base && d.b_slot_stride && d.b_slot_stride % 16 == 0 &&
+                           aligned(d.b_pool_base, 16) && d.max_rank % 8 == 0;
+    if (b_strided) {
+        const cuuint64_t dims[3] = {d.max_rank, d.n, d.max_loras};
+        const cuuint64_t strides[2] = {uint64_t(d.max_rank) * 2, uint64_t(d.b_slot_stride)};
+        const cuuint32_t box[3] = {16, tc::FT, 1};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        if (rt.encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(d.b_pool_base), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return ATLAS_B200_ERR_DIMS;
+    } else {
+        map_b = map_s;   // never dereferenced
+    }
+
     tc::Params p{};
+    p.b_pool_strided = b_strided ? 1u : 0u;
     p.seq_slot = d.seq_slot;
     p.a_table = d.a_table;
     p.b_table = d.b_table;
@@ -243,7 +281,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     cfg.attrs = attr;
     cfg.numAttrs = after_shrink ? 1 : 0;
     p.wait_for_shrink = after_shrink ? 1u : 0u;
-    return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_kernel<MT>, map_x, map_w, map_s, p));
+    return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_kernel<MT>, map_x, map_w, map_s, map_b, p));
 }
 
 static int validate_linear(const atlas_b200_linear_desc& d) {
@@ -284,7 +322,9 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
             sp.out = static_cast<uint16_t*>(d.lora_t);
             sp.M = d.m; sp.k_in = d.k; sp.max_rank = d.max_rank; sp.x_row_stride = d.x_row_stride; sp.max_loras = d.max_loras;
             sp.post = 1.0f / (d.scale2 * kWeightPreScale);
-            rc = launch_shrink(sp, d.max_loras, st, true);
+            // A small batch: let the main kernel start under the shrink.  A large one: the shrink is a
+            // sizeable grid that should have the whole machine first; the main kernel then follows it.
+            rc = launch_shrink(sp, d.max_loras, st, d.m <= 1024);
             if (rc) return rc;
         }
         const bool after_shrink = d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK);

@@ -23,12 +23,12 @@
 // kernel (TMA writes + MMA operand reads + raw-code reads all share it), and a BF16 weight tile
 // that is written to and read back from shared memory every K block costs a third of it.
 //
-// Warp roles (14 warps, 448 threads):
+// Warp roles (22 warps, 704 threads):
 //   warp 0        TMA producer: x tiles (SWIZZLE_128B) and raw weight stages (packed codes with
 //                 SWIZZLE_128B + scale bytes) through mbarrier rings
 //   warp 1        TMEM allocation, tcgen05.mma issue, tcgen05.commit
 //   warps 2-5     build the tile's granule list while the main loop runs; then the epilogue
-//   warps 6-13    expand raw NVFP4 into the BF16 weight operand (TMEM); build the LoRA operands;
+//   warps 6-21    expand raw NVFP4 into the BF16 weight operand (TMEM); build the LoRA operands;
 //                 then join the epilogue: tcgen05.ld -> scale -> BF16 -> global
 //
 // Every wait is bounded: on expiry the waiter records a status code, raises the CTA's abort
@@ -45,20 +45,27 @@ namespace tc {
 constexpr int FT = 128;              // features per CTA = UMMA M
 constexpr int KB = 64;               // K elements per MMA stage (one 128-byte swizzle row of BF16)
 constexpr int KRAW = 256;            // K elements per raw weight stage
-constexpr int RAW_STAGES = 2;
 constexpr int RAW_PACKED_BYTES = FT * (KRAW / 2);    // 16 KiB
 constexpr int RAW_SCALE_BYTES = FT * (KRAW / 16);    // 2 KiB
-constexpr int NUM_THREADS = 448;
-constexpr int DEQ_WARP0 = 6, DEQ_WARPS = 8, DEQ_THREADS = 256;
+constexpr int NUM_THREADS = 704;
+// sixteen expansion warps in two groups of eight; a group expands every other K block, so that the
+// latency of one group's hand-over (TMEM store wait, fences, barrier traffic) hides under the other's work
+constexpr int DEQ_WARP0 = 6, DEQ_WARPS = 16, DEQ_GROUP_WARPS = 8, DEQ_THREADS = 512;
 constexpr int EPI_WARP0 = 2, EPI_THREADS = 128;
 constexpr int MAX_LORAS_TC = 4096;
 constexpr int MAX_RANK_TC = 64;
 constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;    // 1 s
-constexpr int PROFILE_WORDS = 10;                    // u64 words per CTA in the optional profile buffer
+constexpr int PROFILE_WORDS = 16;
+#ifndef MMA_BACKOFF_NS
+#define MMA_BACKOFF_NS 32
+#endif                    // u64 words per CTA in the optional profile buffer
 
 template <int MT> struct Cfg {
     static constexpr int X_TILE_BYTES = MT * KB * 2;
     static constexpr int STAGES = MT >= 256 ? 5 : (MT >= 128 ? 6 : 8);
+    // raw weight stages in flight: small token tiles leave shared memory free, and they are the
+    // HBM-bound shapes that need many bytes in flight per SM
+    static constexpr int RAW_STAGES = MT >= 256 ? 2 : (MT >= 128 ? 4 : 6);
     static constexpr int A_COLS = KB / 2;                                  // TMEM columns of one weight-operand stage
     static constexpr int TMEM_A_BASE = MT < 32 ? 32 : MT;                  // accumulator occupies [0, MT)
     static constexpr int TMEM_NEEDED = TMEM_A_BASE + STAGES * A_COLS;
@@ -68,13 +75,22 @@ template <int MT> struct Cfg {
     static constexpr int OFF_X = 0;
     static constexpr int OFF_RAWP = OFF_X + STAGES * X_TILE_BYTES;
     static constexpr int OFF_RAWS = OFF_RAWP + RAW_STAGES * RAW_PACKED_BYTES;
-    static constexpr int OFF_SLOT = OFF_RAWS + RAW_STAGES * RAW_SCALE_BYTES;     // int32[MT]
+    static constexpr int STAGING_BASE = OFF_RAWS + RAW_STAGES * RAW_SCALE_BYTES;
+    // After the base K loop the whole staging area is re-used for the LoRA K blocks: each block holds up
+    // to four granules, each a B_s tile [128 x 16] and a masked-t tile [MT x 16], BF16, K-major, SWIZZLE_32B.
+    static constexpr int L_GRAN_A = FT * 32;                                     // one granule of B_s: [128 x 16] BF16
+    static constexpr int L_GRAN_T = MT * 32;                                     // one granule of masked t: [MT x 16] BF16
+    static constexpr int L_TILE_A = 4 * L_GRAN_A;
+    static constexpr int L_BLOCK = L_TILE_A + 4 * L_GRAN_T;
+    static constexpr int L_STAGES = (STAGING_BASE / L_BLOCK) >= 4 ? 4 : ((STAGING_BASE / L_BLOCK) >= 3 ? 3 : 4);
+    static constexpr int STAGING_BYTES = STAGING_BASE > L_STAGES * L_BLOCK ? STAGING_BASE : L_STAGES * L_BLOCK;
+    static constexpr int OFF_SLOT = STAGING_BYTES;                               // int32[MT]
     static constexpr int OFF_GRAN = OFF_SLOT + MT * 4;                           // uint16[MAX_GRANULES]
     static constexpr int OFF_GRANB = OFF_GRAN + MAX_GRANULES * 2;                // uint64[MAX_GRANULES]: B_s address of the granule
     static constexpr int OFF_BITMAP = OFF_GRANB + MAX_GRANULES * 8;              // uint32[128]
     static constexpr int OFF_SCAN = OFF_BITMAP + (MAX_LORAS_TC / 32) * 4;        // uint32[8]
     static constexpr int OFF_BAR = OFF_SCAN + 64;                                // mbarriers
-    static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_STAGES + 2;
+    static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_STAGES + 3 + 2 * L_STAGES;
     static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;                      // tmem ptr, n_gran, abort
     static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;                      // + alignment slack
     static_assert(TMEM_NEEDED <= 512, "tensor memory budget");
@@ -90,6 +106,7 @@ struct Params {
     uint16_t* y;
     uint32_t M, N, K, out_row_stride, max_loras, max_rank;
     float out_scale;               // scale2 * 2^8
+    uint32_t b_pool_strided;       // B_s tiles can be fetched by TMA from a [max_loras][N][max_rank] strided pool
     uint32_t wait_for_shrink;      // launched as a programmatic dependent of the shrink: wait before reading t
     unsigned long long* profile;   // nullable: per-CTA wait/busy cycle counters (PROFILE_WORDS per CTA)
 };
@@ -148,10 +165,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 
 // mbar_wait that also adds the cycles spent waiting to `acc` (profiling builds of a launch only)
 __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code,
-                                                bool timed, unsigned long long& acc) {
-    if (!timed) return mbar_wait(bar, parity, abort_flag, code);
+                                                bool timed, unsigned long long& acc, uint32_t backoff_ns = 0) {
+    if (!timed) return mbar_wait(bar, parity, abort_flag, code, backoff_ns);
     const long long t0 = clock64();
-    const bool ok = mbar_wait(bar, parity, abort_flag, code);
+    const bool ok = mbar_wait(bar, parity, abort_flag, code, backoff_ns);
     acc += (unsigned long long)(clock64() - t0);
     return ok;
 }
@@ -165,6 +182,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1, int32_t c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -188,6 +210,14 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T (both operands K-major shared-memory tiles); one thread issues.
+__device__ __forceinline__ void umma_bf16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // registers -> 32 lanes x N consecutive 32-bit TMEM columns (lane = this warp's quadrant base + laneid)
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -225,6 +255,13 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
     return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
            (uint64_t(1) << 46) | (uint64_t(2) << 61);
 }
+// K-major operand tile of 16 BF16 (32-byte rows), SWIZZLE_32B: 8-row groups are 256 bytes apart.
+__device__ __forceinline__ uint64_t make_kmajor_sw32_desc(uint32_t smem_addr) {
+    return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(256 >> 4) << 32) |
+           (uint64_t(1) << 46) | (uint64_t(6) << 61);
+}
+// byte offset of 16-byte chunk `c` (0..1) of row `r` in a SWIZZLE_32B tile of 32-byte rows
+__device__ __forceinline__ uint32_t sw32_off(uint32_t r, uint32_t c) { return r * 32u + ((c ^ ((r >> 2) & 1u)) << 4); }
 // kind::f16 instruction descriptor: D = F32, A = B = BF16, both K-major, M = 128, N = n.
 __host__ __device__ constexpr uint32_t make_idesc_bf16(uint32_t n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
@@ -296,6 +333,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                             const __grid_constant__ CUtensorMap map_w,
                             const __grid_constant__ CUtensorMap map_s,
+                            const __grid_constant__ CUtensorMap map_b,
                             const Params p) {
     using C = Cfg<MT>;
     extern __shared__ uint8_t smem_raw[];
@@ -311,15 +349,18 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     uint32_t* bitmap = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_BITMAP);
     uint32_t* scan = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_SCAN);
     const uint32_t bar0 = smem_base + C::OFF_BAR;
-    // FULL[s]: both operands of stage s are in place.  DEQ_WARPS + 1 arrivals per phase: the eight
+    // FULL[s]: both operands of stage s are in place.  DEQ_GROUP_WARPS + 1 arrivals per phase: the eight
     // expansion warps, plus the TMA producer (with the tile's byte count) for a base K block or one
     // extra arrival by an expansion thread for a LoRA K block, whose activation tile they build.
     const uint32_t BAR_FULL = bar0;                                    // [STAGES] operands -> MMA
     const uint32_t BAR_EMPTY = bar0 + 8 * C::STAGES;                   // [STAGES] MMA -> producers
-    const uint32_t BAR_FULL_RAW = bar0 + 16 * C::STAGES;               // [RAW_STAGES]
-    const uint32_t BAR_EMPTY_RAW = BAR_FULL_RAW + 8 * RAW_STAGES;      // [RAW_STAGES]
-    const uint32_t BAR_ACC = BAR_EMPTY_RAW + 8 * RAW_STAGES;           // accumulator complete
+    const uint32_t BAR_FULL_RAW = bar0 + 16 * C::STAGES;               // [C::RAW_STAGES]
+    const uint32_t BAR_EMPTY_RAW = BAR_FULL_RAW + 8 * C::RAW_STAGES;      // [C::RAW_STAGES]
+    const uint32_t BAR_ACC = BAR_EMPTY_RAW + 8 * C::RAW_STAGES;           // accumulator complete
     const uint32_t BAR_LIST = BAR_ACC + 8;                             // granule list ready
+    const uint32_t BAR_LFULL = BAR_LIST + 8;                           // [L_STAGES] LoRA operands -> MMA
+    const uint32_t BAR_LEMPTY = BAR_LFULL + 8 * C::L_STAGES;           // [L_STAGES] MMA -> LoRA operand build
+    const uint32_t BAR_DRAINED = BAR_LEMPTY + 8 * C::L_STAGES;         // every expansion warp is done with the staging area
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + C::OFF_MISC);
     // misc[0] = TMEM base address, misc[1] = granule count, misc[2] = abort flag
     volatile uint32_t* abort_flag = misc + 2;
@@ -335,15 +376,20 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
 
     if (tid == 0) {
         for (int i = 0; i < C::STAGES; ++i) {
-            mbar_init(BAR_FULL + 8 * i, DEQ_WARPS + 1);
+            mbar_init(BAR_FULL + 8 * i, DEQ_GROUP_WARPS + 1);
             mbar_init(BAR_EMPTY + 8 * i, 1);
         }
-        for (int i = 0; i < RAW_STAGES; ++i) {
+        for (int i = 0; i < C::RAW_STAGES; ++i) {
             mbar_init(BAR_FULL_RAW + 8 * i, 1);
             mbar_init(BAR_EMPTY_RAW + 8 * i, DEQ_WARPS);
         }
         mbar_init(BAR_ACC, 1);
         mbar_init(BAR_LIST, 1);
+        mbar_init(BAR_DRAINED, DEQ_WARPS);
+        for (int i = 0; i < C::L_STAGES; ++i) {
+            mbar_init(BAR_LFULL + 8 * i, DEQ_WARPS + 1);
+            mbar_init(BAR_LEMPTY + 8 * i, 1);
+        }
         misc[1] = 0;
         misc[2] = 0;
         fence_barrier_init();
@@ -356,6 +402,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         tma_prefetch_desc(&map_x);
         tma_prefetch_desc(&map_w);
         tma_prefetch_desc(&map_s);
+        if (p.b_pool_strided) tma_prefetch_desc(&map_b);
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -378,7 +425,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             while (it < num_kb || ri < num_raw) {
                 bool progressed = false;
                 if (ri < num_raw) {
-                    const uint32_t rs = ri % RAW_STAGES, rph = (ri / RAW_STAGES) & 1u;
+                    const uint32_t rs = ri % C::RAW_STAGES, rph = (ri / C::RAW_STAGES) & 1u;
                     if (mbar_try_wait(BAR_EMPTY_RAW + 8 * rs, rph ^ 1u)) {
                         mbar_arrive_expect_tx(BAR_FULL_RAW + 8 * rs, RAW_PACKED_BYTES + RAW_SCALE_BYTES);
                         const uint32_t rk = (ri + rot_raw) % num_raw;
@@ -433,7 +480,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             bool ready = false;                              // result of an early look at this block's barrier
             for (uint32_t it = 0; it < num_kb; ++it) {
                 if (!ready) {
-                    ok = mbar_wait_timed(bar_full, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full);
+                    ok = mbar_wait_timed(bar_full, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full, MMA_BACKOFF_NS);
                     if (!ok) break;
                 }
                 tcgen05_fence_after();
@@ -459,21 +506,20 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             // base K blocks issued; the LoRA K blocks follow once the granule list is known
             if (ok) ok = mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_MMA, 32);
             if (ok) {
+                // LoRA K blocks: both operands are shared-memory tiles in their own ring
                 const uint32_t n_gran = misc[1];
+                uint32_t ls = 0, lph = 0;
                 for (uint32_t g0 = 0; g0 < n_gran; g0 += 4) {
-                    ok = mbar_wait_timed(bar_full, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full);
+                    ok = mbar_wait_timed(BAR_LFULL + 8 * ls, lph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full, MMA_BACKOFF_NS);
                     if (!ok) break;
                     tcgen05_fence_after();
                     const uint32_t ksteps = min(4u, n_gran - g0);
-                    for (uint32_t k = 0; k < ksteps; ++k)
-                        umma_bf16_ts(tmem_acc, a_tmem + 8 * k, b_desc + 2 * k, idesc, 1u);
-                    umma_commit(bar_empty);
-                    if (++s == uint32_t(C::STAGES)) {
-                        s = 0; ph ^= 1u;
-                        bar_full = BAR_FULL; bar_empty = BAR_EMPTY; a_tmem = tmem_a0; b_desc -= b_desc_step * (C::STAGES - 1);
-                    } else {
-                        bar_full += 8; bar_empty += 8; a_tmem += C::A_COLS; b_desc += b_desc_step;
-                    }
+                    const uint64_t la = make_kmajor_sw32_desc(x_tile0 + ls * C::L_BLOCK);
+                    const uint64_t lb_ = make_kmajor_sw32_desc(x_tile0 + ls * C::L_BLOCK + C::L_TILE_A);
+                    for (uint32_t k = 0; k < ksteps; ++k)   // one granule = one 16-wide K step with its own pair of tiles
+                        umma_bf16_ss(tmem_acc, la + k * (C::L_GRAN_A >> 4), lb_ + k * (C::L_GRAN_T >> 4), idesc, 1u);
+                    umma_commit(BAR_LEMPTY + 8 * ls);
+                    if (++ls == uint32_t(C::L_STAGES)) { ls = 0; lph ^= 1u; }
                 }
             }
             if (ok) umma_commit(BAR_ACC);
@@ -544,7 +590,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         if (mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 512)) {
             const long long t_epi = clock64();
             tcgen05_fence_after();
-            epilogue_columns<MT>(p, tmem_acc, warp & 3u, lane, f0, m0, 0, 3);
+            epilogue_columns<MT>(p, tmem_acc, warp & 3u, lane, f0, m0, 0, 5);
             if (prof && te == 0) prof_row[7] = (unsigned long long)(clock64() - t_epi);
         }
     } else {
@@ -553,7 +599,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         // of a quadrant split each K block in halves of 32.  K blocks are expanded two at a time so
         // that each warp has two independent dependency chains in flight.
         const uint32_t q = warp & 3u;
-        const uint32_t half = (warp - DEQ_WARP0) >> 2;
+        const uint32_t half = ((warp - DEQ_WARP0) >> 2) & 1u;
+        const uint32_t grp = (warp - DEQ_WARP0) >> 3;       // group 0 expands K blocks 0,2 of a raw stage, group 1 blocks 1,3
         const uint32_t row = q * 32 + lane;
         const uint32_t td = tid - DEQ_WARP0 * 32;
         const uint32_t lane_base = (q * 32u) << 16;
@@ -561,25 +608,23 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         unsigned long long w_raw = 0, w_empty = 0;
         const long long t_begin = clock64();
         const uint32_t num_raw = (num_kb + 3u) / 4u;
-        uint32_t s = 0, ph = 0;                              // stage / phase of the next K block to fill
+        uint32_t s = grp, ph = 0;                            // stage / phase of this group's next K block
         uint32_t rs = 0, rph = 0;
         for (uint32_t ri = 0; ok && ri < num_raw; ++ri) {
             ok = mbar_wait_timed(BAR_FULL_RAW + 8 * rs, rph, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_raw);
             if (!ok) break;
             const uint4 sc4 = lds128(raws0 + rs * RAW_SCALE_BYTES + row * 16);
             const uint32_t scw[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
-#pragma unroll
-            for (uint32_t jp = 0; jp < 4; jp += 2) {
-                if (ri * 4 + jp >= num_kb) break;
-                const bool two = ri * 4 + jp + 1 < num_kb;
+            if (ri * 4 + grp < num_kb) {
+                const bool two = ri * 4 + grp + 2 < num_kb;
                 uint32_t o[2][16];
 #pragma unroll
                 for (uint32_t u = 0; u < 2; ++u) {
-                    const uint32_t j = jp + u;
+                    const uint32_t j = grp + 2 * u;
                     // 32 codes of this row: logical chunk 2j + half of the swizzled 128-byte raw row
                     const uint4 pk = lds128(rawp0 + rs * RAW_PACKED_BYTES + sw128_off(row, 2 * j + half));
                     const uint32_t pw[4] = {pk.x, pk.y, pk.z, pk.w};
-                    const uint32_t sbytes = scw[j] >> (16 * half);      // scale bytes 2*half, 2*half+1 of word j
+                    const uint32_t sbytes = (grp ? (u ? scw[3] : scw[1]) : (u ? scw[2] : scw[0])) >> (16 * half);   // scale bytes 2*half, 2*half+1 of word j
                     const uint32_t mul0 = e4m3_to_bf16x2_shifted(sbytes & 0xFFu);
                     const uint32_t mul1 = e4m3_to_bf16x2_shifted((sbytes >> 8) & 0xFFu);
 #pragma unroll
@@ -590,8 +635,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     }
                 }
                 const uint32_t s0 = s, ph0 = ph;
-                uint32_t s1 = s0 + 1, ph1 = ph0;
-                if (s1 == uint32_t(C::STAGES)) { s1 = 0; ph1 ^= 1u; }
+                uint32_t s1 = s0 + 2, ph1 = ph0;
+                if (s1 >= uint32_t(C::STAGES)) { s1 -= C::STAGES; ph1 ^= 1u; }
                 ok = mbar_wait_timed(BAR_EMPTY + 8 * s0, ph0 ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_empty);
                 if (!ok) break;
                 tcgen05_fence_after();
@@ -610,37 +655,55 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     mbar_arrive(BAR_FULL + 8 * s0);
                     if (two) mbar_arrive(BAR_FULL + 8 * s1);
                 }
-                if (two) { s = s1 + 1; ph = ph1; } else { s = s1; ph = ph1; }
-                if (s == uint32_t(C::STAGES)) { s = 0; ph ^= 1u; }
+                s = s1 + 2; ph = ph1;                        // four K blocks per raw stage
+                if (s >= uint32_t(C::STAGES)) { s -= C::STAGES; ph ^= 1u; }
             }
             if (!ok) break;
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR_EMPTY_RAW + 8 * rs);
-            if (++rs == uint32_t(RAW_STAGES)) { rs = 0; rph ^= 1u; }
+            if (++rs == uint32_t(C::RAW_STAGES)) { rs = 0; rph ^= 1u; }
         }
         if (prof && td == 0) {
             prof_row[3] = w_raw; prof_row[4] = w_empty; prof_row[5] = (unsigned long long)(clock64() - t_begin);
         }
         const long long t_lora = clock64();
 
-        // ---- LoRA K blocks: weight operand = rows of B_s (registers -> TMEM), activation operand =
-        //      masked rows of t, copied global -> shared with cp.async (zero-filled where the token
-        //      is routed elsewhere).  Loads of block lb+1 are in flight while block lb is handed over.
+        // ---- LoRA K blocks.  Per granule: a B_s tile [128 features x 16 ranks] and a masked-t tile
+        //      [MT tokens x 16] (rows of t where the token is routed to the granule's slot, zero
+        //      elsewhere), both in the MMA's SWIZZLE_32B layout, four granules to a block, L_STAGES
+        //      blocks in flight.  B_s tiles come by 3-D TMA out of the strided adapter pool (one
+        //      tensor map covers every slot); without such a pool they are copied with cp.async like
+        //      the t tiles.  No registers hold data, so shared memory alone sets the pipeline depth.
         if (ok) ok = mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, 32);
         // t is produced by the shrink grid this kernel may have overtaken: everything above ran
         // without it; from here on its writes must be complete and visible.
         if (p.wait_for_shrink) asm volatile("griddepcontrol.wait;" ::: "memory");
-        if (ok) {
-            const uint32_t n_gran = misc[1];
-            const uint32_t n_lb = (n_gran + 3u) / 4u;
-            const uint32_t f = f0 + row;
-            // Activation side of a granule: MT rows x 2 chunks of 16 bytes.  Task -> (row = task % MT,
-            // chunk = task / MT), so eight neighbouring lanes write eight different swizzled chunks.
-            // Everything that does not depend on the granule is computed once per thread.
+        const uint32_t n_gran = ok ? misc[1] : 0u;
+        const uint32_t n_lb = (n_gran + 3u) / 4u;
+        s = num_kb % uint32_t(C::STAGES);                    // stage / phase the K block after the last one would take
+        ph = (num_kb / uint32_t(C::STAGES)) & 1u;
+        if (ok && n_lb > 0) {
+            // the staging area is about to be overwritten: every base MMA must have read its x tile,
+            // and every expansion warp must be done with the raw weight stages
+            {
+                uint32_t ss = s, pp = ph;
+                for (int i = 0; ok && i < C::STAGES; ++i) {
+                    ok = mbar_wait(BAR_EMPTY + 8 * ss, pp ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
+                    if (++ss == uint32_t(C::STAGES)) { ss = 0; pp ^= 1u; }
+                }
+            }
+            // (an mbarrier rather than bar.sync, so that this wait is bounded like every other one)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR_DRAINED);
+            if (ok) ok = mbar_wait(BAR_DRAINED, 0, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
+        }
+        if (ok && n_lb > 0) {
             constexpr uint32_t T_TASKS = (uint32_t(MT) * 2 + DEQ_THREADS - 1) / DEQ_THREADS;   // per granule
+            // task -> (row = task % MT, chunk = task / MT): eight neighbouring lanes write eight
+            // different swizzled chunks; everything independent of the granule is computed once
             int32_t t_slot[T_TASKS];
             const uint16_t* t_src[T_TASKS];
-            uint32_t t_dst[T_TASKS], t_xor[T_TASKS], t_hh[T_TASKS];
+            uint32_t t_dst[T_TASKS], t_hh[T_TASKS];
 #pragma unroll
             for (uint32_t u = 0; u < T_TASKS; ++u) {
                 const uint32_t task = td + u * DEQ_THREADS;
@@ -648,73 +711,81 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 t_hh[u] = hh;
                 t_slot[u] = (task < uint32_t(MT) * 2) ? slot_arr[r] : -2;     // -2 never matches: no task
                 t_src[u] = p.t + size_t(m0 + r) * p.max_rank + 8 * hh;
-                t_dst[u] = r * 128u;
-                t_xor[u] = r & 7u;
+                t_dst[u] = C::L_TILE_A + r * 32u + ((hh ^ ((r >> 2) & 1u)) << 4);
             }
-            uint4 bcur[4], bnext[4];
-            uint32_t ls = s, lph = ph;                       // stage / phase of the block being LOADED
-            auto issue_loads = [&](uint32_t lb, uint4 (&bvv)[4]) -> bool {
-                // the activation tile of this stage is rewritten: wait until the MMA has released it
-                if (!mbar_wait(BAR_EMPTY + 8 * ls, lph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT)) return false;
-                const uint32_t xt = x_tile0 + ls * C::X_TILE_BYTES;
+            // B_s side: this thread copies chunk (2 g + a_h) of feature row a_row
+            const uint32_t a_row = td & 127u, a_h = (td >> 7) & 1u;    // threads 0..255 copy B_s when it does not come by TMA
+            const uint32_t a_dst = sw32_off(a_row, a_h);
+            const uint32_t f = f0 + a_row;
+            const size_t a_src_off = size_t(f) * p.max_rank + 8 * a_h;
+            uint32_t ls = 0, lph = 0;
+            unsigned long long w_lempty = 0, w_issue = 0, w_group = 0;
+            auto issue_block = [&](uint32_t lb) -> bool {
+                if (!mbar_wait_timed(BAR_LEMPTY + 8 * ls, lph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_lempty)) return false;
+                const long long t_i0 = prof ? clock64() : 0;
+                const uint32_t base = x_tile0 + ls * C::L_BLOCK;
                 const uint32_t ng = min(4u, n_gran - lb * 4);
+                if (td == 0) {   // the block's ninth arrival: with the TMA byte count, or plain
+                    if (p.b_pool_strided) mbar_arrive_expect_tx(BAR_LFULL + 8 * ls, ng * C::L_GRAN_A);
+                    else mbar_arrive(BAR_LFULL + 8 * ls);
+                }
 #pragma unroll
                 for (uint32_t g = 0; g < 4; ++g) {
-                    bvv[g] = make_uint4(0, 0, 0, 0);
                     if (g < ng) {
                         const uint32_t e = gran[lb * 4 + g];
                         const int32_t slot = int32_t(e >> 2);
                         const uint32_t j0 = (e & 3u) * 16u;
-                        const uint32_t j = j0 + 8 * half;
-                        if (f < p.N && j < p.max_rank)
-                            bvv[g] = __ldg(reinterpret_cast<const uint4*>(
-                                reinterpret_cast<const uint16_t*>(gran_b[lb * 4 + g]) + size_t(f) * p.max_rank + j));
+                        if (p.b_pool_strided) {
+                            if (td == 0) tma_load_3d(base + g * C::L_GRAN_A, &map_b, int32_t(j0), int32_t(f0), slot, BAR_LFULL + 8 * ls);
+                        } else if (td < 256u) {
+                            const bool live = f < p.N && j0 + 8 * a_h < p.max_rank;
+                            const uint16_t* src = live ? reinterpret_cast<const uint16_t*>(gran_b[lb * 4 + g]) + a_src_off + j0 : p.t;
+                            cp_async_16_zfill(base + g * C::L_GRAN_A + a_dst, src, live ? 16u : 0u);
+                        }
 #pragma unroll
                         for (uint32_t u = 0; u < T_TASKS; ++u) {
                             if (t_slot[u] != -2) {
-                                // a miss copies 0 bytes and zero-fills the 16-byte destination
+                                // a hit copies 16 bytes of t; a miss stores zeros
                                 const bool hit = t_slot[u] == slot && j0 + 8 * t_hh[u] < p.max_rank;
-                                cp_async_16_zfill(xt + t_dst[u] + (((2 * g + t_hh[u]) ^ t_xor[u]) << 4), hit ? t_src[u] + j0 : p.t, hit ? 16u : 0u);
+                                if (hit) cp_async_16_zfill(base + g * C::L_GRAN_T + t_dst[u], t_src[u] + j0, 16u);
+                                else sts128(base + g * C::L_GRAN_T + t_dst[u], 0u, 0u, 0u, 0u);
                             }
                         }
                     }
                 }
-                cp_async_commit();
-                if (++ls == uint32_t(C::STAGES)) { ls = 0; lph ^= 1u; }
+                if (++ls == uint32_t(C::L_STAGES)) { ls = 0; lph ^= 1u; }
+                if (prof) w_issue += (unsigned long long)(clock64() - t_i0);
                 return true;
             };
-            if (n_lb > 0) ok = issue_loads(0, bcur);
+            // one cp.async group per block, issued L_STAGES - 1 blocks ahead (empty groups past the end
+            // keep "group index == block index")
+            for (uint32_t i = 0; ok && i + 1 < uint32_t(C::L_STAGES); ++i) {
+                if (i < n_lb) ok = issue_block(i);
+                cp_async_commit();
+            }
+            // Hand block lb over first, refill afterwards: the refill waits for the MMA to release a
+            // stage, and must not stand between finished copies and the MMA that is waiting for them.
+            uint32_t cs = 0;
             for (uint32_t lb = 0; ok && lb < n_lb; ++lb) {
-                if (lb + 1 < n_lb) {
-                    ok = issue_loads(lb + 1, bnext);
-                    if (!ok) break;
-                    cp_async_wait_group<1>();
-                } else {
-                    cp_async_wait_group<0>();
-                }
-                const uint32_t ng = min(4u, n_gran - lb * 4);
-                tcgen05_fence_after();
-#pragma unroll
-                for (uint32_t g = 0; g < 4; ++g)   // B_s[f, j0 + 8 half .. +8): 4 columns at 8 g + 4 half
-                    if (g < ng) tmem_st4(tmem_a0 + lane_base + s * C::A_COLS + 8 * g + 4 * half,
-                                         bcur[g].x, bcur[g].y, bcur[g].z, bcur[g].w);
-                tmem_st_wait();
-                tcgen05_fence_before();
+                const long long t_g0 = prof ? clock64() : 0;
+                cp_async_wait_group<C::L_STAGES - 2>();      // groups 0 .. lb + L_STAGES - 2 are committed: lb is done
+                if (prof) w_group += (unsigned long long)(clock64() - t_g0);
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(BAR_FULL + 8 * s);
-                if (td == 0) mbar_arrive(BAR_FULL + 8 * s);     // stands in for the TMA producer's arrival
-                if (++s == uint32_t(C::STAGES)) { s = 0; ph ^= 1u; }
-#pragma unroll
-                for (uint32_t g = 0; g < 4; ++g) bcur[g] = bnext[g];
+                if (lane == 0) mbar_arrive(BAR_LFULL + 8 * cs);
+                if (++cs == uint32_t(C::L_STAGES)) cs = 0;
+                if (lb + C::L_STAGES - 1 < n_lb) ok = issue_block(lb + C::L_STAGES - 1);
+                cp_async_commit();
             }
+            cp_async_wait_group<0>();
+            if (prof && td == 0) { prof_row[10] = w_lempty; prof_row[11] = w_issue; prof_row[12] = w_group; prof_row[13] = n_lb; }
         }
         if (prof && td == 0) prof_row[6] = (unsigned long long)(clock64() - t_lora);
 
         // ---- join the epilogue ----
         if (ok && mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 64)) {
             tcgen05_fence_after();
-            epilogue_columns<MT>(p, tmem_acc, q, lane, f0, m0, 1 + half, 3);
+            epilogue_columns<MT>(p, tmem_acc, q, lane, f0, m0, 1 + ((warp - DEQ_WARP0) >> 2), 5);
         }
     }
 

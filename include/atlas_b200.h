@@ -138,6 +138,13 @@ typedef struct atlas_b200_linear_desc {
     void*           lora_t;
     void*           ws;             /* reserved, may be NULL */
     size_t          ws_bytes;
+    /* Optional: the B side of the adapter pool as a strided array.  When b_table[s] ==
+     * b_pool_base + s * b_slot_stride for every resident slot s — which is how the reference lays its
+     * pool out (slot k at k * pool_slot_bytes, crates/spark-model/src/lora/slot_math.rs:124-137) — pass the
+     * base and the stride (bytes, a multiple of 16) and the tcgen05 path fetches B_s tiles by TMA.
+     * NULL / 0: B_s is read through b_table with ordinary loads (any placement, slower). */
+    const void*     b_pool_base;
+    size_t          b_slot_stride;
 } atlas_b200_linear_desc;
 
 ATLAS_B200_API int atlas_b200_nvfp4_lora_linear(const atlas_b200_linear_desc* desc, void* stream);
@@ -212,11 +219,12 @@ ATLAS_B200_API int atlas_b200_device_status(uint32_t* out_word, int clear);
 ATLAS_B200_API int atlas_b200_last_variant(void);
 /* Per-CTA cycle counters of the tcgen05 kernel, the counterpart of the reference's per-phase timers
  * (crates/spark-model/src/layers/qwen3_attention/trait_impl/multi_seq/mod.rs:125-141).  While a device
- * buffer of `n_words` u64 is set (10 words per CTA, CTA index = blockIdx.y * gridDim.x + blockIdx.x) each
+ * buffer of `n_words` u64 is set (16 words per CTA, CTA index = blockIdx.y * gridDim.x + blockIdx.x) each
  * launch that fits writes, in SM cycles unless noted: [0] low 32 bits: MMA thread waiting for operands,
  * high 32 bits: kernel entry to first MMA wait; [1] CTA lifetime; [2] MMA role total; [3] expansion warps
  * waiting for raw weights; [4] waiting for a free stage; [5] expansion total; [6] LoRA operand build;
- * [7] epilogue; [8]/[9] %globaltimer (ns) at CTA entry / exit.  Pass NULL to switch it off (default). */
+ * [7] epilogue; [8]/[9] %globaltimer (ns) at CTA entry / exit; [10]-[12] LoRA operand build: waiting for a free
+ * stage, issuing copies, waiting for copies; [13] LoRA K blocks.  Pass NULL to switch it off (default). */
 ATLAS_B200_API int atlas_b200_set_profile_buffer(void* device_buffer, size_t n_words);
 ATLAS_B200_API const char* atlas_b200_version(void);
 

@@ -62,14 +62,14 @@ class DeviceCase:
         self.lora_t = torch.zeros((case.M, case.max_rank), dtype=torch.int16, device="cuda")
         self.torch, self.atlas = torch, atlas
 
-    def run(self, *, lora=True, with_ranks=True, flags=0, fill=0x7FC0):
+    def run(self, *, lora=True, with_ranks=True, flags=0, fill=0x7FC0, strided=True):
         """Returns (y bits [M, out_row_stride], variant). y is pre-filled with a NaN pattern."""
         torch, atlas, c = self.torch, self.atlas, self.case
         y = torch.full((c.M, self.out_row_stride), np.int16(np.uint16(fill).view(np.int16)), dtype=torch.int16, device="cuda")
         d = atlas.make_linear_desc(
             x=self.x, m=c.M, k=c.K, n=c.N, y=y, w_packed=self.packed, w_scale=self.scales, scale2=c.scale2,
             w_bf16=self.w_bf16, x_row_stride=self.x_row_stride, out_row_stride=self.out_row_stride,
-            seq_slot=self.seq_slot if lora else None, route=self.pool.route(with_ranks) if lora else None,
+            seq_slot=self.seq_slot if lora else None, route=self.pool.route(with_ranks, strided) if lora else None,
             lora_t=self.lora_t if lora else None, flags=flags)
         variant = atlas.nvfp4_lora_linear(d)
         torch.cuda.synchronize()

@@ -61,6 +61,9 @@ def test_fused_lora(cuda, atlas, oracle, M, K, N, ranks, max_rank, with_ranks):
     assert variant == atlas.VARIANT_TCGEN05
     want = ideal(oracle, case, use_ranks=with_ranks)
     assert_close(oracle, y, want, "fused")
+    # B_s through the address tables (no strided pool declared) must give the same bits as B_s by TMA
+    y_tab, _ = dc.run(with_ranks=with_ranks, flags=_tc(atlas), strided=False)
+    assert np.array_equal(y_tab, y)
     yb, _ = dc.run(lora=False, flags=_tc(atlas))
     none = case.seq_slot < 0
     assert none.any() and np.array_equal(y[none], yb[none])            # routing is exact

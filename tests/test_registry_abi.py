@@ -27,7 +27,8 @@ def test_linear_desc_layout_matches_header(atlas):
     assert d.n.offset == 20 and d.w_packed.offset == 24 and d.w_bf16.offset == 40
     assert d.scale2.offset == 48 and d.flags.offset == 52 and d.seq_slot.offset == 56
     assert d.max_loras.offset == 96 and d.y.offset == 104 and d.lora_t.offset == 120
-    assert C.sizeof(d) == 144
+    assert d.b_pool_base.offset == 144 and d.b_slot_stride.offset == 152
+    assert C.sizeof(d) == 160
 
 
 def test_seq_slot_and_scaling_match_oracle(atlas, oracle):
