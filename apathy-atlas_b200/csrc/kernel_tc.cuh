@@ -23,12 +23,12 @@
 // kernel (TMA writes + MMA operand reads + raw-code reads all share it), and a BF16 weight tile
 // that is written to and read back from shared memory every K block costs a third of it.
 //
-// Warp roles (22 warps, 704 threads):
+// Warp roles (14 warps, 448 threads):
 //   warp 0        TMA producer: x tiles (SWIZZLE_128B) and raw weight stages (packed codes with
 //                 SWIZZLE_128B + scale bytes) through mbarrier rings
 //   warp 1        TMEM allocation, tcgen05.mma issue, tcgen05.commit
 //   warps 2-5     build the tile's granule list while the main loop runs; then the epilogue
-//   warps 6-21    expand raw NVFP4 into the BF16 weight operand (TMEM); build the LoRA operands;
+//   warps 6-13    expand raw NVFP4 into the BF16 weight operand (TMEM); build the LoRA operands;
 //                 then join the epilogue: tcgen05.ld -> scale -> BF16 -> global
 //
 // Every wait is bounded: on expiry the waiter records a status code, raises the CTA's abort
@@ -47,10 +47,13 @@ constexpr int KB = 64;               // K elements per MMA stage (one 128-byte s
 constexpr int KRAW = 256;            // K elements per raw weight stage
 constexpr int RAW_PACKED_BYTES = FT * (KRAW / 2);    // 16 KiB
 constexpr int RAW_SCALE_BYTES = FT * (KRAW / 16);    // 2 KiB
-constexpr int NUM_THREADS = 704;
-// sixteen expansion warps in two groups of eight; a group expands every other K block, so that the
-// latency of one group's hand-over (TMEM store wait, fences, barrier traffic) hides under the other's work
-constexpr int DEQ_WARP0 = 6, DEQ_WARPS = 16, DEQ_GROUP_WARPS = 8, DEQ_THREADS = 512;
+// Expansion warps come in groups of eight (one warp per TMEM quadrant and K half).  With G groups, group
+// i expands K blocks i, i+G, ... of each raw stage.  One group measured best: a second group does not
+// shorten the K loop (which is bound by shared-memory bandwidth at 256 tokens and by the MMA thread's
+// issue rate below) and takes issue slots from the MMA thread.
+constexpr int DEQ_GROUPS = 1;
+constexpr int DEQ_WARP0 = 6, DEQ_GROUP_WARPS = 8, DEQ_WARPS = 8 * DEQ_GROUPS, DEQ_THREADS = 32 * DEQ_WARPS;
+constexpr int NUM_THREADS = 32 * (DEQ_WARP0 + DEQ_WARPS);
 constexpr int EPI_WARP0 = 2, EPI_THREADS = 128;
 constexpr int MAX_LORAS_TC = 4096;
 constexpr int MAX_RANK_TC = 64;
@@ -461,6 +464,27 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     }
                 }
             }
+            // LoRA K blocks: when the adapter pool is strided, this thread also fetches the B_s tiles
+            // (one 3-D TMA per granule), running ahead of the warps that build the masked-t tiles.
+            if (p.seq_slot && p.b_pool_strided && !*abort_flag &&
+                mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER, 64)) {
+                const uint32_t n_gran = misc[1];
+                // the staging area may be overwritten once the expansion warps have seen every base MMA finish
+                if (n_gran && mbar_wait(BAR_DRAINED, 0, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER, 32)) {
+                    uint32_t ls = 0, lph = 0;
+                    for (uint32_t g0 = 0; g0 < n_gran; g0 += 4) {
+                        if (!mbar_wait(BAR_LEMPTY + 8 * ls, lph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER)) break;
+                        const uint32_t ng = min(4u, n_gran - g0);
+                        const uint32_t base = x_tile0 + ls * C::L_BLOCK;
+                        mbar_arrive_expect_tx(BAR_LFULL + 8 * ls, ng * C::L_GRAN_A);
+                        for (uint32_t g = 0; g < ng; ++g) {
+                            const uint32_t e = gran[g0 + g];
+                            tma_load_3d(base + g * C::L_GRAN_A, &map_b, int32_t((e & 3u) * 16u), int32_t(f0), int32_t(e >> 2), BAR_LFULL + 8 * ls);
+                        }
+                        if (++ls == uint32_t(C::L_STAGES)) { ls = 0; lph ^= 1u; }
+                    }
+                }
+            }
         }
     } else if (warp == 1) {
         // ===================================== MMA issuer =======================================
@@ -571,6 +595,23 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             }
             if (te == 0) misc[1] = n_gran;
             named_bar_sync(1, EPI_THREADS);
+            // For every token row: where its slot's granules sit in the list (they are consecutive) and
+            // how many there are, packed (pos << 3 | count); 0xFFFF = the row takes no LoRA term.  The
+            // slot bitmap is dead by now and its space is re-used.
+            uint16_t* row_pg = reinterpret_cast<uint16_t*>(bitmap);
+            for (uint32_t r = te; r < uint32_t(MT); r += EPI_THREADS) {
+                const int32_t sl = slot_arr[r];
+                uint16_t pg = 0xFFFFu;
+                if (sl >= 0) {
+                    const uint32_t key = uint32_t(sl) << 2;       // first entry >= key is (sl, granule 0)
+                    uint32_t lo = 0, hi = n_gran;
+                    while (lo < hi) { const uint32_t mid = (lo + hi) >> 1; if (gran[mid] < key) lo = mid + 1; else hi = mid; }
+                    const uint32_t rk = p.rank_table ? min(p.rank_table[sl], p.max_rank) : p.max_rank;
+                    pg = uint16_t((lo << 3) | ((rk + 15u) / 16u));
+                }
+                row_pg[r] = pg;
+            }
+            named_bar_sync(1, EPI_THREADS);
         }
         if (te == 0) mbar_arrive(BAR_LIST);
         // Pull this CTA's rows of every B_s it will need into L2 now, while the base K loop runs:
@@ -590,7 +631,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         if (mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 512)) {
             const long long t_epi = clock64();
             tcgen05_fence_after();
-            epilogue_columns<MT>(p, tmem_acc, warp & 3u, lane, f0, m0, 0, 5);
+            epilogue_columns<MT>(p, tmem_acc, warp & 3u, lane, f0, m0, 0, 1 + DEQ_WARPS / 4);
             if (prof && te == 0) prof_row[7] = (unsigned long long)(clock64() - t_epi);
         }
     } else {
@@ -600,7 +641,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         // that each warp has two independent dependency chains in flight.
         const uint32_t q = warp & 3u;
         const uint32_t half = ((warp - DEQ_WARP0) >> 2) & 1u;
-        const uint32_t grp = (warp - DEQ_WARP0) >> 3;       // group 0 expands K blocks 0,2 of a raw stage, group 1 blocks 1,3
+        const uint32_t grp = (warp - DEQ_WARP0) >> 3;       // expansion group of this warp
         const uint32_t row = q * 32 + lane;
         const uint32_t td = tid - DEQ_WARP0 * 32;
         const uint32_t lane_base = (q * 32u) << 16;
@@ -615,16 +656,19 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             if (!ok) break;
             const uint4 sc4 = lds128(raws0 + rs * RAW_SCALE_BYTES + row * 16);
             const uint32_t scw[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
-            if (ri * 4 + grp < num_kb) {
-                const bool two = ri * 4 + grp + 2 < num_kb;
+#pragma unroll
+            for (uint32_t jr = 0; jr < 4; jr += 2 * DEQ_GROUPS) {
+                if (ri * 4 + jr + grp >= num_kb) break;
+                const bool two = ri * 4 + jr + grp + DEQ_GROUPS < num_kb;
                 uint32_t o[2][16];
 #pragma unroll
                 for (uint32_t u = 0; u < 2; ++u) {
-                    const uint32_t j = grp + 2 * u;
+                    const uint32_t j = jr + grp + DEQ_GROUPS * u;       // K block of the raw stage (0..3)
                     // 32 codes of this row: logical chunk 2j + half of the swizzled 128-byte raw row
                     const uint4 pk = lds128(rawp0 + rs * RAW_PACKED_BYTES + sw128_off(row, 2 * j + half));
                     const uint32_t pw[4] = {pk.x, pk.y, pk.z, pk.w};
-                    const uint32_t sbytes = (grp ? (u ? scw[3] : scw[1]) : (u ? scw[2] : scw[0])) >> (16 * half);   // scale bytes 2*half, 2*half+1 of word j
+                    const uint32_t scj = j == 0 ? scw[0] : (j == 1 ? scw[1] : (j == 2 ? scw[2] : scw[3]));
+                    const uint32_t sbytes = scj >> (16 * half);          // scale bytes 2*half, 2*half+1 of word j
                     const uint32_t mul0 = e4m3_to_bf16x2_shifted(sbytes & 0xFFu);
                     const uint32_t mul1 = e4m3_to_bf16x2_shifted((sbytes >> 8) & 0xFFu);
 #pragma unroll
@@ -635,7 +679,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     }
                 }
                 const uint32_t s0 = s, ph0 = ph;
-                uint32_t s1 = s0 + 2, ph1 = ph0;
+                uint32_t s1 = s0 + DEQ_GROUPS, ph1 = ph0;
                 if (s1 >= uint32_t(C::STAGES)) { s1 -= C::STAGES; ph1 ^= 1u; }
                 ok = mbar_wait_timed(BAR_EMPTY + 8 * s0, ph0 ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_empty);
                 if (!ok) break;
@@ -655,7 +699,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     mbar_arrive(BAR_FULL + 8 * s0);
                     if (two) mbar_arrive(BAR_FULL + 8 * s1);
                 }
-                s = s1 + 2; ph = ph1;                        // four K blocks per raw stage
+                s = s1 + DEQ_GROUPS; ph = ph1;
                 if (s >= uint32_t(C::STAGES)) { s -= C::STAGES; ph ^= 1u; }
             }
             if (!ok) break;
@@ -699,19 +743,31 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         }
         if (ok && n_lb > 0) {
             constexpr uint32_t T_TASKS = (uint32_t(MT) * 2 + DEQ_THREADS - 1) / DEQ_THREADS;   // per granule
-            // task -> (row = task % MT, chunk = task / MT): eight neighbouring lanes write eight
-            // different swizzled chunks; everything independent of the granule is computed once
-            int32_t t_slot[T_TASKS];
+            // Masked-t side.  Task -> (row = task % MT, 16-byte chunk = task / MT): eight neighbouring lanes
+            // write eight different swizzled chunks.  A row's slot owns `t_ng` consecutive granules
+            // starting at list position `t_pos`, so whether block lb touches the row is arithmetic on lb.
+            // All t tiles are zeroed once; afterwards a task only writes where its row is routed to the
+            // granule (a copy of 16 bytes of t) or was, the last time the stage was used (zeros again).
+            const uint16_t* row_pg = reinterpret_cast<const uint16_t*>(bitmap);
+            int32_t t_pos[T_TASKS];
+            uint32_t t_ng[T_TASKS];
             const uint16_t* t_src[T_TASKS];
-            uint32_t t_dst[T_TASKS], t_hh[T_TASKS];
+            uint32_t t_dst[T_TASKS];
 #pragma unroll
             for (uint32_t u = 0; u < T_TASKS; ++u) {
                 const uint32_t task = td + u * DEQ_THREADS;
                 const uint32_t r = task & (uint32_t(MT) - 1u), hh = task / uint32_t(MT);
-                t_hh[u] = hh;
-                t_slot[u] = (task < uint32_t(MT) * 2) ? slot_arr[r] : -2;     // -2 never matches: no task
+                const uint32_t pg = (task < uint32_t(MT) * 2 && p.seq_slot) ? row_pg[r] : 0xFFFFu;
+                t_ng[u] = pg == 0xFFFFu ? 0u : (pg & 7u);
+                t_pos[u] = int32_t(pg >> 3);
                 t_src[u] = p.t + size_t(m0 + r) * p.max_rank + 8 * hh;
                 t_dst[u] = C::L_TILE_A + r * 32u + ((hh ^ ((r >> 2) & 1u)) << 4);
+                // granule columns beyond max_rank do not exist in t: treat as not routed
+                if (t_ng[u] && 16 * (t_ng[u] - 1) + 8 * hh >= p.max_rank) t_ng[u] -= 1;
+            }
+            for (uint32_t i = td; i < uint32_t(C::L_STAGES) * uint32_t(MT) * 8u; i += DEQ_THREADS) {
+                const uint32_t st_i = i / (uint32_t(MT) * 8u), off = (i % (uint32_t(MT) * 8u)) * 16u;
+                sts128(x_tile0 + st_i * C::L_BLOCK + C::L_TILE_A + off, 0u, 0u, 0u, 0u);
             }
             // B_s side: this thread copies chunk (2 g + a_h) of feature row a_row
             const uint32_t a_row = td & 127u, a_h = (td >> 7) & 1u;    // threads 0..255 copy B_s when it does not come by TMA
@@ -725,32 +781,28 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 const long long t_i0 = prof ? clock64() : 0;
                 const uint32_t base = x_tile0 + ls * C::L_BLOCK;
                 const uint32_t ng = min(4u, n_gran - lb * 4);
-                if (td == 0) {   // the block's ninth arrival: with the TMA byte count, or plain
-                    if (p.b_pool_strided) mbar_arrive_expect_tx(BAR_LFULL + 8 * ls, ng * C::L_GRAN_A);
-                    else mbar_arrive(BAR_LFULL + 8 * ls);
-                }
+                // the block's ninth arrival comes from the TMA producer when it fetches B_s, else from here
+                if (td == 0 && !p.b_pool_strided) mbar_arrive(BAR_LFULL + 8 * ls);
+                if (!p.b_pool_strided)
 #pragma unroll
                 for (uint32_t g = 0; g < 4; ++g) {
                     if (g < ng) {
-                        const uint32_t e = gran[lb * 4 + g];
-                        const int32_t slot = int32_t(e >> 2);
-                        const uint32_t j0 = (e & 3u) * 16u;
-                        if (p.b_pool_strided) {
-                            if (td == 0) tma_load_3d(base + g * C::L_GRAN_A, &map_b, int32_t(j0), int32_t(f0), slot, BAR_LFULL + 8 * ls);
-                        } else if (td < 256u) {
+                        const uint32_t j0 = (gran[lb * 4 + g] & 3u) * 16u;
+                        if (td < 256u) {
                             const bool live = f < p.N && j0 + 8 * a_h < p.max_rank;
                             const uint16_t* src = live ? reinterpret_cast<const uint16_t*>(gran_b[lb * 4 + g]) + a_src_off + j0 : p.t;
                             cp_async_16_zfill(base + g * C::L_GRAN_A + a_dst, src, live ? 16u : 0u);
                         }
+                    }
+                }
 #pragma unroll
-                        for (uint32_t u = 0; u < T_TASKS; ++u) {
-                            if (t_slot[u] != -2) {
-                                // a hit copies 16 bytes of t; a miss stores zeros
-                                const bool hit = t_slot[u] == slot && j0 + 8 * t_hh[u] < p.max_rank;
-                                if (hit) cp_async_16_zfill(base + g * C::L_GRAN_T + t_dst[u], t_src[u] + j0, 16u);
-                                else sts128(base + g * C::L_GRAN_T + t_dst[u], 0u, 0u, 0u, 0u);
-                            }
-                        }
+                for (uint32_t u = 0; u < T_TASKS; ++u) {
+                    const int32_t d = int32_t(lb * 4) - t_pos[u];        // granule of the row's slot that block lb starts with
+#pragma unroll
+                    for (int32_t g = 0; g < 4; ++g) {
+                        const uint32_t k = uint32_t(d + g);
+                        if (k < t_ng[u]) cp_async_16_zfill(base + g * C::L_GRAN_T + t_dst[u], t_src[u] + 16 * k, 16u);
+                        else if (uint32_t(d + g - 4 * C::L_STAGES) < t_ng[u]) sts128(base + g * C::L_GRAN_T + t_dst[u], 0u, 0u, 0u, 0u);
                     }
                 }
                 if (++ls == uint32_t(C::L_STAGES)) { ls = 0; lph ^= 1u; }
@@ -785,7 +837,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         // ---- join the epilogue ----
         if (ok && mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 64)) {
             tcgen05_fence_after();
-            epilogue_columns<MT>(p, tmem_acc, q, lane, f0, m0, 1 + ((warp - DEQ_WARP0) >> 2), 5);
+            epilogue_columns<MT>(p, tmem_acc, q, lane, f0, m0, 1 + ((warp - DEQ_WARP0) >> 2), 1 + DEQ_WARPS / 4);
         }
     }
 
