@@ -31,6 +31,9 @@ import numpy as np
 
 METRIC = "NVFP4+multi-LoRA linear tokens/s"
 FP4_PEAK_TFLOPS = 9000.0          # B200 dense NVFP4, nominal (no measured figure on this pool)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the tcgen05 kernel, from the ncu captures
+# summarised under profiles/ (per workload; None where no capture exists)
+NCU_TRAFFIC_BYTES = {"config1": 74.1e6}
 WORKLOADS = {"config0": 0, "config1": 1, "config2": 2, "config3": 3, "config4": 4}
 
 
@@ -284,7 +287,7 @@ def main():
             "config": workload_config(args, case, tp),
             "tflops": work["flops"] / (step_ms * 1e-3) / 1e12,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
-                         "traffic": None, "peak_kind": peak_kind,
+                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if tp == 1 else None, "peak_kind": peak_kind,
                          "kernel": "nvfp4_lora_linear_tc_kernel (per rank)", "kernel_ms": main_ms,
                          "algorithmic_bytes": shard_work["main_kernel"]},
             "layer_roofline": {"time_us": t_roof * 1e6, "frac": t_roof / (step_ms * 1e-3),
