@@ -42,6 +42,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 struct Runtime {
     bool sm100 = false;
+    int sm_count = 148;
     EncodeTiledFn encode = nullptr;
     bool tc_attr_set[5] = {false, false, false, false, false};
 };
@@ -55,6 +56,7 @@ static Runtime& runtime() {
         int major = 0;
         cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
         rt.sm100 = (major == 10);
+        cudaDeviceGetAttribute(&rt.sm_count, cudaDevAttrMultiProcessorCount, dev);
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
@@ -63,6 +65,8 @@ static Runtime& runtime() {
     });
     return rt;
 }
+
+static int rt_sm_count() { return runtime().sm_count > 0 ? runtime().sm_count : 148; }
 
 static bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem, const void* base, uint64_t inner,
                       uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
@@ -328,10 +332,17 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
             if (rc) return rc;
         }
         const bool after_shrink = d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK);
-        if (d.m <= 16) rc = launch_tc<16>(d, 0, after_shrink, st);
-        else if (d.m <= 32) rc = launch_tc<32>(d, 1, after_shrink, st);
-        else if (d.m <= 64) rc = launch_tc<64>(d, 2, after_shrink, st);
-        else if (d.m <= 128) rc = launch_tc<128>(d, 3, after_shrink, st);
+        // Token tile: the smallest power of two that covers m, at most 256 — then halved (down to 64)
+        // while the grid would leave more than a quarter of the SMs without a CTA, e.g. for a
+        // column shard of a wide layer: more, lighter CTAs finish sooner than few heavy ones.
+        uint32_t mt = 16;
+        while (mt < 256 && mt < d.m) mt <<= 1;
+        const uint32_t f_tiles = (d.n + tc::FT - 1) / tc::FT;
+        while (mt > 64 && f_tiles * ((d.m + mt - 1) / mt) * 4 < uint32_t(rt_sm_count()) * 3) mt >>= 1;
+        if (mt == 16) rc = launch_tc<16>(d, 0, after_shrink, st);
+        else if (mt == 32) rc = launch_tc<32>(d, 1, after_shrink, st);
+        else if (mt == 64) rc = launch_tc<64>(d, 2, after_shrink, st);
+        else if (mt == 128) rc = launch_tc<128>(d, 3, after_shrink, st);
         else rc = launch_tc<256>(d, 4, after_shrink, st);
         if (rc == ATLAS_B200_OK) t_last_variant = ATLAS_B200_VARIANT_TCGEN05;
         return rc;
