@@ -23,7 +23,12 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libatlas_b200.so")
 
 VARIANT_NONE, VARIANT_SIMT, VARIANT_TCGEN05 = 0, 1, 2
-FLAG_FORCE_SIMT, FLAG_FORCE_TCGEN05, FLAG_STAGED_LORA, FLAG_REUSE_SHRINK = 1, 2, 4, 8
+FLAG_FORCE_SIMT, FLAG_FORCE_TCGEN05, FLAG_STAGED_LORA, FLAG_REUSE_SHRINK, FLAG_ACT_FP4 = 1, 2, 4, 8, 16
+
+
+def act_fp4_ws_bytes(m: int, k: int) -> int:
+    """Scratch a FLAG_ACT_FP4 call needs in `ws` (ATLAS_B200_ACT_FP4_WS_BYTES): packed codes, then scale bytes."""
+    return (m * (k // 2) + 255) // 256 * 256 + m * (k // 16)
 MODULES = ("q", "k", "v", "o", "gate", "up", "down")
 
 EXPORTS = (
@@ -239,7 +244,7 @@ def quantize_bf16_to_nvfp4(inp, packed, scales, scale2: float, n: int, k: int, s
 
 def make_linear_desc(*, x, m, k, n, y, w_packed=None, w_scale=None, scale2=1.0, w_bf16=None,
                      x_row_stride=None, out_row_stride=None, seq_slot=None, route: Optional[LoraRoute] = None,
-                     lora_t=None, flags=0) -> LinearDesc:
+                     lora_t=None, flags=0, ws=None, ws_bytes=0) -> LinearDesc:
     d = LinearDesc()
     d.x, d.m, d.k = _ptr(x), m, k
     d.x_row_stride = x_row_stride if x_row_stride is not None else k
@@ -256,6 +261,7 @@ def make_linear_desc(*, x, m, k, n, y, w_packed=None, w_scale=None, scale2=1.0, 
         d.b_pool_base, d.b_slot_stride = _ptr(route.b_pool_base), route.b_slot_stride
     d.y = _ptr(y)
     d.out_row_stride = out_row_stride if out_row_stride is not None else n
+    d.ws, d.ws_bytes = _ptr(ws), ws_bytes
     return d
 
 

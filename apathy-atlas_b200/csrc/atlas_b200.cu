@@ -44,7 +44,7 @@ struct Runtime {
     bool sm100 = false;
     int sm_count = 148;
     EncodeTiledFn encode = nullptr;
-    bool tc_attr_set[5] = {false, false, false, false, false};
+    bool tc_attr_set[10] = {};        // token tiles 16..256, A16 then A4
 };
 
 static Runtime& runtime() {
@@ -220,19 +220,34 @@ static bool tc_eligible(const atlas_b200_linear_desc& d) {
     return true;
 }
 
-template <int MT>
+// Bytes of `ws` the FP4-activation mode needs: packed codes [m, k/2] then scale bytes [m, k/16],
+// the second at a 256-byte boundary.
+static size_t act_fp4_codes_bytes(const atlas_b200_linear_desc& d) { return (size_t(d.m) * (d.k / 2) + 255) / 256 * 256; }
+static size_t act_fp4_ws_bytes(const atlas_b200_linear_desc& d) { return act_fp4_codes_bytes(d) + size_t(d.m) * (d.k / 16); }
+
+template <int MT, bool A4>
 static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_shrink, cudaStream_t st) {
-    using C = tc::Cfg<MT>;
+    using C = tc::Cfg<MT, A4>;
     Runtime& rt = runtime();
+    slot_idx += A4 ? 5 : 0;
     if (!rt.tc_attr_set[slot_idx]) {
-        cudaError_t e = cudaFuncSetAttribute(tc::nvfp4_lora_linear_tc_kernel<MT>,
+        cudaError_t e = cudaFuncSetAttribute(tc::nvfp4_lora_linear_tc_kernel<MT, A4>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return cuda_status(e);
         rt.tc_attr_set[slot_idx] = true;
     }
-    CUtensorMap map_x, map_w, map_s, map_b;
-    if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.x, d.k, d.m, uint64_t(d.x_row_stride) * 2, tc::KB, MT,
-                   CU_TENSOR_MAP_SWIZZLE_128B))
+    CUtensorMap map_x, map_w, map_s, map_b, map_xs;
+    if (A4) {
+        // the quantised activations in `ws`, in the weights' own layout
+        const uint8_t* codes = static_cast<const uint8_t*>(d.ws);
+        if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, d.k / 2, d.m, d.k / 2, tc::KRAW / 2, MT,
+                       CU_TENSOR_MAP_SWIZZLE_128B))
+            return ATLAS_B200_ERR_DIMS;
+        if (!encode_2d(&map_xs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes + act_fp4_codes_bytes(d), d.k / 16, d.m, d.k / 16,
+                       tc::KRAW / 16, MT, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return ATLAS_B200_ERR_DIMS;
+    } else if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.x, d.k, d.m, uint64_t(d.x_row_stride) * 2, tc::KB, MT,
+                          CU_TENSOR_MAP_SWIZZLE_128B))
         return ATLAS_B200_ERR_DIMS;
     if (!encode_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.w_packed, d.k / 2, d.n, d.k / 2, tc::KRAW / 2, tc::FT,
                    CU_TENSOR_MAP_SWIZZLE_128B))
@@ -256,6 +271,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     } else {
         map_b = map_s;   // never dereferenced
     }
+    if (!A4) map_xs = map_s;   // never dereferenced
 
     tc::Params p{};
     p.b_pool_strided = b_strided ? 1u : 0u;
@@ -267,7 +283,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     p.y = static_cast<uint16_t*>(d.y);
     p.M = d.m; p.N = d.n; p.K = d.k; p.out_row_stride = d.out_row_stride;
     p.max_loras = d.max_loras; p.max_rank = d.max_rank;
-    p.out_scale = d.scale2 * kWeightPreScale;
+    p.out_scale = A4 ? d.scale2 : d.scale2 * kWeightPreScale;
     dim3 grid((d.n + tc::FT - 1) / tc::FT, (d.m + MT - 1) / MT);
     p.profile = (g_profile_buf && size_t(grid.x) * grid.y * tc::PROFILE_WORDS <= g_profile_words) ? g_profile_buf : nullptr;
     if (grid.y > 65535) return ATLAS_B200_ERR_LIMIT;
@@ -285,7 +301,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     cfg.attrs = attr;
     cfg.numAttrs = after_shrink ? 1 : 0;
     p.wait_for_shrink = after_shrink ? 1u : 0u;
-    return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_kernel<MT>, map_x, map_w, map_s, map_b, p));
+    return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_kernel<MT, A4>, map_x, map_w, map_s, map_b, map_xs, p));
 }
 
 static int validate_linear(const atlas_b200_linear_desc& d) {
@@ -313,6 +329,22 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
     bool use_tc = !(d.flags & ATLAS_B200_FLAG_FORCE_SIMT) && !staged && tc_eligible(d);
     if (!use_tc && (d.flags & ATLAS_B200_FLAG_FORCE_TCGEN05)) return ATLAS_B200_ERR_DIMS;
 
+    const bool act_fp4 = (d.flags & ATLAS_B200_FLAG_ACT_FP4) != 0;
+    if (act_fp4) {
+        // FP4 activations exist on the tensor-core path only: no other path is substituted for it
+        if (!use_tc) return ATLAS_B200_ERR_DIMS;
+        if (!d.ws || !aligned(d.ws, 256)) return d.ws ? ATLAS_B200_ERR_ALIGN : ATLAS_B200_ERR_NULL;
+        if (d.ws_bytes < act_fp4_ws_bytes(d)) return ATLAS_B200_ERR_WORKSPACE;
+        // x -> NVFP4 with a tensor scale of one (scale byte = E4M3 of group max / 6), the activation side
+        // of crates/spark-model/src/layers/ops/gemm_fp4.rs:20-40
+        uint8_t* codes = static_cast<uint8_t*>(d.ws);
+        const size_t groups = size_t(d.m) * (d.k / 16);
+        const unsigned blocks = unsigned(std::min<size_t>((groups + 255) / 256, size_t(rt_sm_count()) * 16));
+        quantize_nvfp4_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(d.x), codes, codes + act_fp4_codes_bytes(d),
+                                                      1.0f, d.m, d.k, d.x_row_stride, 1u);
+        rc = launch_status();
+        if (rc) return rc;
+    }
     if (use_tc) {
         if (d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK)) {
             // shrink first: t = scale_s / (scale2 * 2^8) * (A_s x), the unit of the MMA accumulator
@@ -325,7 +357,7 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
             sp.rank_table = d.rank_table;
             sp.out = static_cast<uint16_t*>(d.lora_t);
             sp.M = d.m; sp.k_in = d.k; sp.max_rank = d.max_rank; sp.x_row_stride = d.x_row_stride; sp.max_loras = d.max_loras;
-            sp.post = 1.0f / (d.scale2 * kWeightPreScale);
+            sp.post = act_fp4 ? 1.0f / d.scale2 : 1.0f / (d.scale2 * kWeightPreScale);
             // A small batch: let the main kernel start under the shrink.  A large one: the shrink is a
             // sizeable grid that should have the whole machine first; the main kernel then follows it.
             rc = launch_shrink(sp, d.max_loras, st, d.m <= 1024);
@@ -339,11 +371,17 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
         while (mt < 256 && mt < d.m) mt <<= 1;
         const uint32_t f_tiles = (d.n + tc::FT - 1) / tc::FT;
         while (mt > 64 && f_tiles * ((d.m + mt - 1) / mt) * 4 < uint32_t(rt_sm_count()) * 3) mt >>= 1;
-        if (mt == 16) rc = launch_tc<16>(d, 0, after_shrink, st);
-        else if (mt == 32) rc = launch_tc<32>(d, 1, after_shrink, st);
-        else if (mt == 64) rc = launch_tc<64>(d, 2, after_shrink, st);
-        else if (mt == 128) rc = launch_tc<128>(d, 3, after_shrink, st);
-        else rc = launch_tc<256>(d, 4, after_shrink, st);
+        if (act_fp4) {
+            if (mt == 16) rc = launch_tc<16, true>(d, 0, after_shrink, st);
+            else if (mt == 32) rc = launch_tc<32, true>(d, 1, after_shrink, st);
+            else if (mt == 64) rc = launch_tc<64, true>(d, 2, after_shrink, st);
+            else if (mt == 128) rc = launch_tc<128, true>(d, 3, after_shrink, st);
+            else rc = launch_tc<256, true>(d, 4, after_shrink, st);
+        } else if (mt == 16) rc = launch_tc<16, false>(d, 0, after_shrink, st);
+        else if (mt == 32) rc = launch_tc<32, false>(d, 1, after_shrink, st);
+        else if (mt == 64) rc = launch_tc<64, false>(d, 2, after_shrink, st);
+        else if (mt == 128) rc = launch_tc<128, false>(d, 3, after_shrink, st);
+        else rc = launch_tc<256, false>(d, 4, after_shrink, st);
         if (rc == ATLAS_B200_OK) t_last_variant = ATLAS_B200_VARIANT_TCGEN05;
         return rc;
     }
@@ -432,8 +470,9 @@ int atlas_b200_quantize_bf16_to_nvfp4(const void* in_bf16, void* packed, void* s
     if (k % 16 != 0) return ATLAS_B200_ERR_DIMS;
     const size_t groups = size_t(n) * (k / 16);
     const unsigned blocks = unsigned(std::min<size_t>((groups + 255) / 256, 148 * 16));
+    const uint32_t vec = aligned(in_bf16, 16) && aligned(packed, 8) && k % 16 == 0;
     quantize_nvfp4_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint16_t*>(in_bf16), static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales), scale2, n, k);
+        static_cast<const uint16_t*>(in_bf16), static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales), scale2, n, k, k, vec);
     return launch_status();
 }
 

@@ -14,6 +14,7 @@ namespace atlas {
 enum : uint32_t {
     STATUS_OK = 0,
     STATUS_SLOT_OUT_OF_RANGE = 1,   // seq_slot[i] >= max_loras
+    STATUS_NEGATIVE_SCALE = 2,      // FP4-activation mode met a weight scale byte with its sign bit set; the sign was dropped
     STATUS_WAIT_EXPIRED_PRODUCER = 0x100,
     STATUS_WAIT_EXPIRED_DEQUANT = 0x101,
     STATUS_WAIT_EXPIRED_MMA = 0x102,

@@ -63,22 +63,39 @@ constexpr int PROFILE_WORDS = 16;
 #define MMA_BACKOFF_NS 32
 #endif                    // u64 words per CTA in the optional profile buffer
 
-template <int MT> struct Cfg {
+// A4 = true selects the block-scaled FP4 x FP4 form (activations quantised to NVFP4 by a kernel that
+// runs first): both MMA operands are the packed 4-bit tiles exactly as TMA delivers them, the E4M3 block
+// scales of both sides are put into tensor memory by the expansion warps, and one pipeline stage covers
+// 256 K elements (four K=64 instructions of kind::mxf4nvf4).
+template <int MT, bool A4 = false> struct Cfg {
     static constexpr int X_TILE_BYTES = MT * KB * 2;
-    static constexpr int STAGES = MT >= 256 ? 5 : (MT >= 128 ? 6 : 8);
+    // A4: one stage = packed W [128 x 128 B] | packed x [MT x 128 B] | W scale bytes [128 x 16] | x scale bytes [MT x 16]
+    static constexpr int S4_W = 0;
+    static constexpr int S4_X = S4_W + RAW_PACKED_BYTES;
+    static constexpr int S4_WS = S4_X + MT * 128;
+    static constexpr int S4_XS = S4_WS + RAW_SCALE_BYTES;
+    static constexpr int S4_BYTES = ((S4_XS + MT * 16) + 1023) / 1024 * 1024;
+    static constexpr int S4_STAGES = (200 * 1024) / S4_BYTES > 8 ? 8 : (200 * 1024) / S4_BYTES;
+    static constexpr int STAGES = A4 ? S4_STAGES : (MT >= 256 ? 5 : (MT >= 128 ? 6 : 8));
     // raw weight stages in flight: small token tiles leave shared memory free, and they are the
     // HBM-bound shapes that need many bytes in flight per SM
-    static constexpr int RAW_STAGES = MT >= 256 ? 2 : (MT >= 128 ? 4 : 6);
+    static constexpr int RAW_STAGES = A4 ? STAGES : (MT >= 256 ? 2 : (MT >= 128 ? 4 : 6));
     static constexpr int A_COLS = KB / 2;                                  // TMEM columns of one weight-operand stage
     static constexpr int TMEM_A_BASE = MT < 32 ? 32 : MT;                  // accumulator occupies [0, MT)
-    static constexpr int TMEM_NEEDED = TMEM_A_BASE + STAGES * A_COLS;
+    // A4: scale factors in TMEM.  One instruction reads, per operand, 4 scale bytes (one 32-bit column
+    // entry) for each of its rows; lane l of every 32-lane quadrant holds rows l, l+32, l+64, l+96 of a
+    // 128-row block in 4 consecutive columns.  Per stage: W 4 instructions x 4 columns, then x 4
+    // instructions x (4 columns per 128 tokens).
+    static constexpr int XSF_BLOCKS = MT > 128 ? MT / 128 : 1;
+    static constexpr int SF_COLS = 16 + 16 * XSF_BLOCKS;
+    static constexpr int TMEM_NEEDED = TMEM_A_BASE + (A4 ? STAGES * SF_COLS : STAGES * A_COLS);
     static constexpr int TMEM_COLS = TMEM_NEEDED <= 64 ? 64 : TMEM_NEEDED <= 128 ? 128 : TMEM_NEEDED <= 256 ? 256 : 512;
     static constexpr int MAX_GRANULES = MT * (MAX_RANK_TC / 16);
     // shared memory map (offsets from a 1024-byte aligned base)
     static constexpr int OFF_X = 0;
     static constexpr int OFF_RAWP = OFF_X + STAGES * X_TILE_BYTES;
     static constexpr int OFF_RAWS = OFF_RAWP + RAW_STAGES * RAW_PACKED_BYTES;
-    static constexpr int STAGING_BASE = OFF_RAWS + RAW_STAGES * RAW_SCALE_BYTES;
+    static constexpr int STAGING_BASE = A4 ? STAGES * S4_BYTES : OFF_RAWS + RAW_STAGES * RAW_SCALE_BYTES;
     // After the base K loop the whole staging area is re-used for the LoRA K blocks: each block holds up
     // to four granules, each a B_s tile [128 x 16] and a masked-t tile [MT x 16], BF16, K-major, SWIZZLE_32B.
     static constexpr int L_GRAN_A = FT * 32;                                     // one granule of B_s: [128 x 16] BF16
@@ -108,7 +125,7 @@ struct Params {
     const uint16_t* t;             // [M, max_rank] pre-scaled shrink result
     uint16_t* y;
     uint32_t M, N, K, out_row_stride, max_loras, max_rank;
-    float out_scale;               // scale2 * 2^8
+    float out_scale;               // scale2 * 2^8 (A16) or scale2 (A4)
     uint32_t b_pool_strided;       // B_s tiles can be fetched by TMA from a [max_loras][N][max_rank] strided pool
     uint32_t wait_for_shrink;      // launched as a programmatic dependent of the shrink: wait before reading t
     unsigned long long* profile;   // nullable: per-CTA wait/busy cycle counters (PROFILE_WORDS per CTA)
@@ -222,6 +239,20 @@ __device__ __forceinline__ void umma_bf16_ss(uint32_t d_tmem, uint64_t a_desc, u
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// D[tmem] (+)= (A * SFA)[smem] * (B * SFB)[smem]^T : E2M1 operands (K = 64 per instruction), one UE4M3
+// scale per 16 elements held in tensor memory; one thread issues.
+__device__ __forceinline__ void umma_nvfp4_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+// block-scaled instruction descriptor: A = B = E2M1, UE4M3 scales, both K-major, M = 128, N = n, K = 64
+__host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t n) {
+    return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (0u << 23) | ((128u >> 4) << 24);
+}
 // registers -> 32 lanes x N consecutive 32-bit TMEM columns (lane = this warp's quadrant base + laneid)
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
@@ -331,14 +362,17 @@ __device__ __forceinline__ void epilogue_columns(const Params& p, uint32_t tmem_
     }
 }
 
-template <int MT>
+// map_x: activations (A16: BF16 [M, K]; A4: packed codes [M, K/2]); map_w / map_s: packed weight codes and
+// their scale bytes; map_b: the strided adapter pool's B side; map_xs: A4 only, activation scale bytes [M, K/16].
+template <int MT, bool A4>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                             const __grid_constant__ CUtensorMap map_w,
                             const __grid_constant__ CUtensorMap map_s,
                             const __grid_constant__ CUtensorMap map_b,
+                            const __grid_constant__ CUtensorMap map_xs,
                             const Params p) {
-    using C = Cfg<MT>;
+    using C = Cfg<MT, A4>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -371,7 +405,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t f0 = blockIdx.x * FT;
     const uint32_t m0 = blockIdx.y * MT;
-    const uint32_t num_kb = (p.K + KB - 1) / KB;
+    const uint32_t num_kb = A4 ? p.K / KRAW : (p.K + KB - 1) / KB;     // pipeline steps of the base K loop
     const bool prof = p.profile != nullptr;
     const long long t_entry = clock64();
     const uint64_t t_entry_ns = prof ? global_timer_ns() : 0;
@@ -406,16 +440,36 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         tma_prefetch_desc(&map_w);
         tma_prefetch_desc(&map_s);
         if (p.b_pool_strided) tma_prefetch_desc(&map_b);
+        if (A4) tma_prefetch_desc(&map_xs);
     }
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_acc = misc[0];
-    const uint32_t tmem_a0 = tmem_acc + C::TMEM_A_BASE;   // weight-operand stages: [tmem_a0 + s * A_COLS, + A_COLS)
+    const uint32_t tmem_a0 = tmem_acc + C::TMEM_A_BASE;   // A16: weight-operand stages [tmem_a0 + s * A_COLS, + A_COLS);
+                                                          // A4: scale-factor stages [tmem_a0 + s * SF_COLS, + SF_COLS)
 
     if (warp == 0) {
         // ===================================== TMA producer =====================================
-        if (lane == 0) {
+        if (lane == 0 && A4) {
+            // One ring: a stage's two packed operand tiles complete FULL[s] (which the MMA thread waits
+            // on), its two scale-byte tiles FULL_RAW[s] (which the warps that move them to TMEM wait on).
+            const uint32_t rot = blockIdx.x % num_kb;
+            uint32_t s = 0, ph = 0;
+            for (uint32_t it = 0; it < num_kb; ++it) {
+                if (!mbar_wait(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER, 32)) break;
+                const uint32_t st = smem_base + s * C::S4_BYTES;
+                const uint32_t kk = (it + rot) % num_kb;
+                mbar_arrive_expect_tx(BAR_FULL_RAW + 8 * s, RAW_SCALE_BYTES + MT * 16);
+                tma_load_2d(st + C::S4_WS, &map_s, int32_t(kk * (KRAW / 16)), int32_t(f0), BAR_FULL_RAW + 8 * s);
+                tma_load_2d(st + C::S4_XS, &map_xs, int32_t(kk * (KRAW / 16)), int32_t(m0), BAR_FULL_RAW + 8 * s);
+                mbar_arrive_expect_tx(BAR_FULL + 8 * s, RAW_PACKED_BYTES + MT * 128);
+                tma_load_2d(st + C::S4_W, &map_w, int32_t(kk * (KRAW / 2)), int32_t(f0), BAR_FULL + 8 * s);
+                tma_load_2d(st + C::S4_X, &map_x, int32_t(kk * (KRAW / 2)), int32_t(m0), BAR_FULL + 8 * s);
+                if (++s == uint32_t(C::STAGES)) { s = 0; ph ^= 1u; }
+            }
+        }
+        if (lane == 0 && !A4) {
             // One thread feeds two rings without blocking on either: activation tiles (one per K
             // block) and raw weight stages (codes + scale bytes, one per four K blocks), so the
             // weight stream runs ahead of the activation stream.
@@ -464,6 +518,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     }
                 }
             }
+        }
+        if (lane == 0) {
             // LoRA K blocks: when the adapter pool is strided, this thread also fetches the B_s tiles
             // (one 3-D TMA per granule), running ahead of the warps that build the masked-t tiles.
             if (p.seq_slot && p.b_pool_strided && !*abort_flag &&
@@ -502,6 +558,26 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             uint64_t b_desc = make_kmajor_sw128_desc(x_tile0);
             constexpr uint64_t b_desc_step = uint64_t(C::X_TILE_BYTES >> 4);
             bool ready = false;                              // result of an early look at this block's barrier
+            if constexpr (A4) {
+                // four K=64 block-scaled instructions per stage; both operands are the packed tiles, the
+                // scales sit in this stage's TMEM columns
+                constexpr uint32_t idesc4 = make_idesc_nvfp4(MT);
+                uint32_t st = smem_base, sf = tmem_a0;
+                for (uint32_t it = 0; it < num_kb; ++it) {
+                    ok = mbar_wait_timed(bar_full, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full, MMA_BACKOFF_NS);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint64_t wa = make_kmajor_sw128_desc(st + C::S4_W);
+                    const uint64_t xb = make_kmajor_sw128_desc(st + C::S4_X);
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i)   // 64 k = 32 bytes along the swizzled 128-byte row
+                        umma_nvfp4_ss(tmem_acc, wa + 2 * i, xb + 2 * i, idesc4, sf + 4 * i, sf + 16 + 4 * C::XSF_BLOCKS * i, acc | i);
+                    umma_commit(bar_empty);
+                    acc = 1u;
+                    bar_full += 8; bar_empty += 8; st += C::S4_BYTES; sf += C::SF_COLS;
+                    if (++s == uint32_t(C::STAGES)) { s = 0; ph ^= 1u; bar_full = BAR_FULL; bar_empty = BAR_EMPTY; st = smem_base; sf = tmem_a0; }
+                }
+            } else
             for (uint32_t it = 0; it < num_kb; ++it) {
                 if (!ready) {
                     ok = mbar_wait_timed(bar_full, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full, MMA_BACKOFF_NS);
@@ -651,6 +727,68 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         const uint32_t num_raw = (num_kb + 3u) / 4u;
         uint32_t s = grp, ph = 0;                            // stage / phase of this group's next K block
         uint32_t rs = 0, rph = 0;
+        if constexpr (A4) {
+            // Block scales, shared memory -> registers -> TMEM.  The warp of quadrant q writes lanes
+            // [32 q, +32); the MMA wants every quadrant to hold the same 32 x 4-column image (lane l:
+            // rows l, l+32, l+64, l+96 of the 128-row block), so the four warps of a half write the same
+            // values.  half 0 moves the weight scales, half 1 the activation scales.
+            s = 0;
+            for (uint32_t it = 0; ok && it < num_kb; ++it) {
+                ok = mbar_wait_timed(BAR_FULL_RAW + 8 * s, ph, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_raw);
+                if (!ok) break;
+                const uint32_t st = smem_base + s * C::S4_BYTES;
+                const uint32_t sf = tmem_a0 + lane_base + s * C::SF_COLS;
+                if (half == 0) {
+                    uint32_t r[16];
+                    uint32_t neg = 0;
+#pragma unroll
+                    for (uint32_t c = 0; c < 4; ++c) {
+                        const uint4 v = lds128(st + C::S4_WS + (lane + 32 * c) * 16);
+                        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i) {
+                            // a NaN scale byte decodes to zero (as in the scalar decode); the MMA reads
+                            // unsigned scales, so a sign bit cannot be honoured: it is reported and dropped
+                            const uint32_t nan = __vcmpeq4(w[i] & 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+                            neg |= w[i] & ~nan;
+                            r[4 * i + c] = w[i] & ~nan & 0x7F7F7F7Fu;
+                        }
+                    }
+                    if (neg & 0x80808080u) record_status(STATUS_NEGATIVE_SCALE);
+                    tmem_st16(sf, r);
+                } else if constexpr (C::XSF_BLOCKS == 1) {
+                    uint32_t r[16];                           // column = 4 i + c
+#pragma unroll
+                    for (uint32_t c = 0; c < 4; ++c) {
+                        const uint32_t row = lane + 32 * c;
+                        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                        if (row < uint32_t(MT)) v = lds128(st + C::S4_XS + row * 16);
+                        r[c] = v.x; r[4 + c] = v.y; r[8 + c] = v.z; r[12 + c] = v.w;
+                    }
+                    tmem_st16(sf + 16, r);
+                } else {
+                    {
+                        static_assert(C::XSF_BLOCKS <= 2, "token tiles of at most 256");
+                        uint32_t r0[16], r1[16];              // instructions 0,1 and 2,3: column = 8 i + 4 blk + c
+#pragma unroll
+                        for (uint32_t blk = 0; blk < 2; ++blk)
+#pragma unroll
+                            for (uint32_t c = 0; c < 4; ++c) {
+                                const uint4 v = lds128(st + C::S4_XS + (128 * blk + 32 * c + lane) * 16);
+                                r0[4 * blk + c] = v.x; r0[8 + 4 * blk + c] = v.y;
+                                r1[4 * blk + c] = v.z; r1[8 + 4 * blk + c] = v.w;
+                            }
+                        tmem_st16(sf + 16, r0);
+                        tmem_st16(sf + 32, r1);
+                    }
+                }
+                tmem_st_wait();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR_FULL + 8 * s);
+                if (++s == uint32_t(C::STAGES)) { s = 0; ph ^= 1u; }
+            }
+        } else
         for (uint32_t ri = 0; ok && ri < num_raw; ++ri) {
             ok = mbar_wait_timed(BAR_FULL_RAW + 8 * rs, rph, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_raw);
             if (!ok) break;

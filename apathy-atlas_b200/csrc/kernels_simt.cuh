@@ -68,27 +68,45 @@ __device__ __forceinline__ uint32_t e2m1_quantize(float v) {
     return sign | idx;
 }
 
+// `in_row_stride` (elements) lets the rows of `in` be spaced wider than K (activations); the outputs
+// are dense.  `vec` != 0: rows and outputs are 16-/8-byte aligned, so a group is read with two 128-bit
+// loads and its codes leave as one 64-bit store.
 __global__ void __launch_bounds__(256)
 quantize_nvfp4_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ packed,
-                      uint8_t* __restrict__ scales, float scale2, uint32_t N, uint32_t K) {
+                      uint8_t* __restrict__ scales, float scale2, uint32_t N, uint32_t K, uint32_t in_row_stride,
+                      uint32_t vec) {
     const uint32_t groups = K / 16;
     const size_t total = size_t(N) * groups;
     const float inv_scale2 = scale2 > 0.0f ? __fdiv_rn(1.0f, scale2) : 0.0f;
     for (size_t gi = size_t(blockIdx.x) * blockDim.x + threadIdx.x; gi < total; gi += size_t(gridDim.x) * blockDim.x) {
-        const uint16_t* p = in + gi * 16;
+        const uint16_t* p = in + (gi / groups) * in_row_stride + (gi % groups) * 16;
         float v[16];
         float gmax = 0.0f;
+        if (vec) {
+            const uint4 lo = __ldg(reinterpret_cast<const uint4*>(p)), hi = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+            const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
-        for (int i = 0; i < 16; ++i) { v[i] = __uint_as_float(uint32_t(p[i]) << 16); gmax = fmaxf(gmax, fabsf(v[i])); }
+            for (int i = 0; i < 8; ++i) { v[2 * i] = bf16_lo(w[i]); v[2 * i + 1] = bf16_hi(w[i]); }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(uint32_t(p[i]) << 16);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) gmax = fmaxf(gmax, fabsf(v[i]));
         const float f8 = gmax > 0.0f ? __fdiv_rn(__fmul_rn(gmax, inv_scale2), 6.0f) : 0.0f;
         const uint32_t byte = e4m3_encode_sw(f8);
         scales[gi] = uint8_t(byte);
         const float eff = __fmul_rn(e4m3_decode(byte), scale2);
         const float inv_eff = eff > 0.0f ? __fdiv_rn(1.0f, eff) : 0.0f;
-        uint8_t* q = packed + gi * 8;
+        uint32_t q[2] = {0u, 0u};
 #pragma unroll
-        for (int i = 0; i < 16; i += 2)
-            q[i / 2] = uint8_t((e2m1_quantize(__fmul_rn(v[i + 1], inv_eff)) << 4) | e2m1_quantize(__fmul_rn(v[i], inv_eff)));
+        for (int i = 0; i < 16; ++i) q[i / 8] |= e2m1_quantize(__fmul_rn(v[i], inv_eff)) << (4 * (i % 8));
+        if (vec) {
+            *reinterpret_cast<uint2*>(packed + gi * 8) = make_uint2(q[0], q[1]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) packed[gi * 8 + i] = uint8_t(q[i / 4] >> (8 * (i % 4)));
+        }
     }
 }
 

@@ -55,6 +55,16 @@ extern "C" {
 #define ATLAS_B200_FLAG_STAGED_LORA    4u   /* reference rounding: base->bf16, then shrink/expand/fold in place */
 #define ATLAS_B200_FLAG_REUSE_SHRINK   8u   /* tcgen05 path only: lora_t already holds this call's shrink result (same x,
                                                seq_slot, tables and scale2 as the call that wrote it); skip the shrink launch */
+#define ATLAS_B200_FLAG_ACT_FP4       16u   /* W4A4: the base product sees x quantised to NVFP4 (group of 16, E4M3 scale =
+                                               group max / 6, tensor scale 1) and runs as a block-scaled FP4 x FP4 MMA; the
+                                               LoRA term still sees exact x.  The opt-in W4A4 arm of the reference:
+                                               crates/spark-model/src/layers/ops/gemm_fp4.rs:20-107 with the activation
+                                               quantiser kernels/gb10/common/quantize_bf16_to_nvfp4.cu:176-243.  Needs the
+                                               tcgen05 path (-1 where that path does not take the shape; nothing else is
+                                               substituted) and `ws` of ATLAS_B200_ACT_FP4_WS_BYTES(m, k) bytes, 256-byte
+                                               aligned (-2 / -3 / -4 otherwise).  Weight scale bytes must not carry a sign bit. */
+#define ATLAS_B200_ACT_FP4_WS_BYTES(m, k) \
+    ((((size_t)(m) * ((k) / 2) + 255) / 256) * 256 + (size_t)(m) * ((k) / 16))
 
 /* ---------------------------------------------------------------------------------------
  * Routed multi-adapter LoRA delta over n rows:  out[i,:] += scale_s * (x[i,:] A_s^T) B_s^T,
@@ -136,7 +146,7 @@ typedef struct atlas_b200_linear_desc {
     uint32_t        reserved0;
     /* scratch: shrink result, [m, max_rank] bf16 */
     void*           lora_t;
-    void*           ws;             /* reserved, may be NULL */
+    void*           ws;             /* scratch of ATLAS_B200_FLAG_ACT_FP4 calls; otherwise unused, may be NULL */
     size_t          ws_bytes;
     /* Optional: the B side of the adapter pool as a strided array.  When b_table[s] ==
      * b_pool_base + s * b_slot_stride for every resident slot s — which is how the reference lays its

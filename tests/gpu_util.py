@@ -66,7 +66,11 @@ class DeviceCase:
         """Returns (y bits [M, out_row_stride], variant). y is pre-filled with a NaN pattern."""
         torch, atlas, c = self.torch, self.atlas, self.case
         y = torch.full((c.M, self.out_row_stride), np.int16(np.uint16(fill).view(np.int16)), dtype=torch.int16, device="cuda")
-        d = atlas.make_linear_desc(
+        ws, ws_bytes = None, 0
+        if flags & atlas.FLAG_ACT_FP4:
+            ws_bytes = atlas.act_fp4_ws_bytes(c.M, c.K)
+            ws = self.ws = torch.full((ws_bytes,), 0xA5, dtype=torch.uint8, device="cuda")
+        d = atlas.make_linear_desc(ws=ws, ws_bytes=ws_bytes,
             x=self.x, m=c.M, k=c.K, n=c.N, y=y, w_packed=self.packed, w_scale=self.scales, scale2=c.scale2,
             w_bf16=self.w_bf16, x_row_stride=self.x_row_stride, out_row_stride=self.out_row_stride,
             seq_slot=self.seq_slot if lora else None, route=self.pool.route(with_ranks, strided) if lora else None,
