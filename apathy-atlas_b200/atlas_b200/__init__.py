@@ -23,7 +23,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libatlas_b200.so")
 
 VARIANT_NONE, VARIANT_SIMT, VARIANT_TCGEN05 = 0, 1, 2
-FLAG_FORCE_SIMT, FLAG_FORCE_TCGEN05, FLAG_STAGED_LORA, FLAG_REUSE_SHRINK, FLAG_ACT_FP4 = 1, 2, 4, 8, 16
+FLAG_FORCE_SIMT, FLAG_FORCE_TCGEN05, FLAG_STAGED_LORA, FLAG_REUSE_SHRINK, FLAG_ACT_FP4, FLAG_NO_CTA_PAIR = 1, 2, 4, 8, 16, 32
 
 
 def act_fp4_ws_bytes(m: int, k: int) -> int:

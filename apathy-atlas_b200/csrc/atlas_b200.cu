@@ -44,7 +44,7 @@ struct Runtime {
     bool sm100 = false;
     int sm_count = 148;
     EncodeTiledFn encode = nullptr;
-    bool tc_attr_set[10] = {};        // token tiles 16..256, A16 then A4
+    bool tc_attr_set[20] = {};        // token tiles 16..256 x {A16, A4} x {single CTA, CTA pair}
 };
 
 static Runtime& runtime() {
@@ -225,13 +225,13 @@ static bool tc_eligible(const atlas_b200_linear_desc& d) {
 static size_t act_fp4_codes_bytes(const atlas_b200_linear_desc& d) { return (size_t(d.m) * (d.k / 2) + 255) / 256 * 256; }
 static size_t act_fp4_ws_bytes(const atlas_b200_linear_desc& d) { return act_fp4_codes_bytes(d) + size_t(d.m) * (d.k / 16); }
 
-template <int MT, bool A4>
+template <int MT, bool A4, bool PAIR>
 static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_shrink, cudaStream_t st) {
-    using C = tc::Cfg<MT, A4>;
+    using C = tc::Cfg<MT, A4, PAIR>;
     Runtime& rt = runtime();
-    slot_idx += A4 ? 5 : 0;
+    slot_idx += (A4 ? 5 : 0) + (PAIR ? 10 : 0);
     if (!rt.tc_attr_set[slot_idx]) {
-        cudaError_t e = cudaFuncSetAttribute(tc::nvfp4_lora_linear_tc_kernel<MT, A4>,
+        cudaError_t e = cudaFuncSetAttribute(tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return cuda_status(e);
         rt.tc_attr_set[slot_idx] = true;
@@ -240,13 +240,13 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     if (A4) {
         // the quantised activations in `ws`, in the weights' own layout
         const uint8_t* codes = static_cast<const uint8_t*>(d.ws);
-        if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, d.k / 2, d.m, d.k / 2, tc::KRAW / 2, MT,
+        if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, d.k / 2, d.m, d.k / 2, tc::KRAW / 2, C::XROWS,
                        CU_TENSOR_MAP_SWIZZLE_128B))
             return ATLAS_B200_ERR_DIMS;
         if (!encode_2d(&map_xs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes + act_fp4_codes_bytes(d), d.k / 16, d.m, d.k / 16,
                        tc::KRAW / 16, MT, CU_TENSOR_MAP_SWIZZLE_NONE))
             return ATLAS_B200_ERR_DIMS;
-    } else if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.x, d.k, d.m, uint64_t(d.x_row_stride) * 2, tc::KB, MT,
+    } else if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.x, d.k, d.m, uint64_t(d.x_row_stride) * 2, tc::KB, C::XROWS,
                           CU_TENSOR_MAP_SWIZZLE_128B))
         return ATLAS_B200_ERR_DIMS;
     if (!encode_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.w_packed, d.k / 2, d.n, d.k / 2, tc::KRAW / 2, tc::FT,
@@ -285,6 +285,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     p.max_loras = d.max_loras; p.max_rank = d.max_rank;
     p.out_scale = A4 ? d.scale2 : d.scale2 * kWeightPreScale;
     dim3 grid((d.n + tc::FT - 1) / tc::FT, (d.m + MT - 1) / MT);
+    if (PAIR) grid.x = (grid.x + 1u) & ~1u;      // whole pairs: a CTA past the last feature loads zeros and stores nothing
     p.profile = (g_profile_buf && size_t(grid.x) * grid.y * tc::PROFILE_WORDS <= g_profile_words) ? g_profile_buf : nullptr;
     if (grid.y > 65535) return ATLAS_B200_ERR_LIMIT;
     // Launched as a programmatic dependent of the shrink that precedes it in the stream: its CTAs
@@ -295,13 +296,24 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     cfg.blockDim = dim3(tc::NUM_THREADS);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    unsigned n_attr = 0;
+    if (PAIR) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 2;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
+    if (after_shrink) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = after_shrink ? 1 : 0;
+    cfg.numAttrs = n_attr;
     p.wait_for_shrink = after_shrink ? 1u : 0u;
-    return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_kernel<MT, A4>, map_x, map_w, map_s, map_b, map_xs, p));
+    return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>, map_x, map_w, map_s, map_b, map_xs, p));
 }
 
 static int validate_linear(const atlas_b200_linear_desc& d) {
@@ -371,17 +383,19 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
         while (mt < 256 && mt < d.m) mt <<= 1;
         const uint32_t f_tiles = (d.n + tc::FT - 1) / tc::FT;
         while (mt > 64 && f_tiles * ((d.m + mt - 1) / mt) * 4 < uint32_t(rt_sm_count()) * 3) mt >>= 1;
+        // 128 and 256 tokens: pairs of CTAs issue their MMAs together (see tc::Cfg)
+        const bool pair = mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR);
         if (act_fp4) {
-            if (mt == 16) rc = launch_tc<16, true>(d, 0, after_shrink, st);
-            else if (mt == 32) rc = launch_tc<32, true>(d, 1, after_shrink, st);
-            else if (mt == 64) rc = launch_tc<64, true>(d, 2, after_shrink, st);
-            else if (mt == 128) rc = launch_tc<128, true>(d, 3, after_shrink, st);
-            else rc = launch_tc<256, true>(d, 4, after_shrink, st);
-        } else if (mt == 16) rc = launch_tc<16, false>(d, 0, after_shrink, st);
-        else if (mt == 32) rc = launch_tc<32, false>(d, 1, after_shrink, st);
-        else if (mt == 64) rc = launch_tc<64, false>(d, 2, after_shrink, st);
-        else if (mt == 128) rc = launch_tc<128, false>(d, 3, after_shrink, st);
-        else rc = launch_tc<256, false>(d, 4, after_shrink, st);
+            if (mt == 16) rc = launch_tc<16, true, false>(d, 0, after_shrink, st);
+            else if (mt == 32) rc = launch_tc<32, true, false>(d, 1, after_shrink, st);
+            else if (mt == 64) rc = launch_tc<64, true, false>(d, 2, after_shrink, st);
+            else if (mt == 128) rc = pair ? launch_tc<128, true, true>(d, 3, after_shrink, st) : launch_tc<128, true, false>(d, 3, after_shrink, st);
+            else rc = pair ? launch_tc<256, true, true>(d, 4, after_shrink, st) : launch_tc<256, true, false>(d, 4, after_shrink, st);
+        } else if (mt == 16) rc = launch_tc<16, false, false>(d, 0, after_shrink, st);
+        else if (mt == 32) rc = launch_tc<32, false, false>(d, 1, after_shrink, st);
+        else if (mt == 64) rc = launch_tc<64, false, false>(d, 2, after_shrink, st);
+        else if (mt == 128) rc = pair ? launch_tc<128, false, true>(d, 3, after_shrink, st) : launch_tc<128, false, false>(d, 3, after_shrink, st);
+        else rc = pair ? launch_tc<256, false, true>(d, 4, after_shrink, st) : launch_tc<256, false, false>(d, 4, after_shrink, st);
         if (rc == ATLAS_B200_OK) t_last_variant = ATLAS_B200_VARIANT_TCGEN05;
         return rc;
     }

@@ -67,19 +67,26 @@ constexpr int PROFILE_WORDS = 16;
 // runs first): both MMA operands are the packed 4-bit tiles exactly as TMA delivers them, the E4M3 block
 // scales of both sides are put into tensor memory by the expansion warps, and one pipeline stage covers
 // 256 K elements (four K=64 instructions of kind::mxf4nvf4).
-template <int MT, bool A4 = false> struct Cfg {
-    static constexpr int X_TILE_BYTES = MT * KB * 2;
+//
+// PAIR = true runs the kernel as clusters of two CTAs on neighbouring SMs that issue their MMAs together
+// (cta_group::2, 256 features x MT tokens per instruction): each CTA still owns 128 features, their
+// weight operand and their accumulator, but holds only HALF of the token tile's activation operand in
+// shared memory; the tensor cores of the pair exchange the halves.  That halves the shared-memory traffic
+// of the activation operand, which is what bounds the single-CTA form at 128 and 256 tokens.
+template <int MT, bool A4 = false, bool PAIR = false> struct Cfg {
+    static constexpr int XROWS = PAIR ? MT / 2 : MT;                       // token rows of the tile this CTA stages
+    static constexpr int X_TILE_BYTES = XROWS * KB * 2;
     // A4: one stage = packed W [128 x 128 B] | packed x [MT x 128 B] | W scale bytes [128 x 16] | x scale bytes [MT x 16]
     static constexpr int S4_W = 0;
     static constexpr int S4_X = S4_W + RAW_PACKED_BYTES;
-    static constexpr int S4_WS = S4_X + MT * 128;
+    static constexpr int S4_WS = S4_X + XROWS * 128;
     static constexpr int S4_XS = S4_WS + RAW_SCALE_BYTES;
     static constexpr int S4_BYTES = ((S4_XS + MT * 16) + 1023) / 1024 * 1024;
     static constexpr int S4_STAGES = (200 * 1024) / S4_BYTES > 8 ? 8 : (200 * 1024) / S4_BYTES;
-    static constexpr int STAGES = A4 ? S4_STAGES : (MT >= 256 ? 5 : (MT >= 128 ? 6 : 8));
+    static constexpr int STAGES = A4 ? S4_STAGES : (XROWS >= 256 ? 5 : (XROWS >= 128 ? 6 : 8));
     // raw weight stages in flight: small token tiles leave shared memory free, and they are the
     // HBM-bound shapes that need many bytes in flight per SM
-    static constexpr int RAW_STAGES = A4 ? STAGES : (MT >= 256 ? 2 : (MT >= 128 ? 4 : 6));
+    static constexpr int RAW_STAGES = A4 ? STAGES : (XROWS >= 256 ? 2 : (XROWS >= 128 ? 4 : 6));
     static constexpr int A_COLS = KB / 2;                                  // TMEM columns of one weight-operand stage
     static constexpr int TMEM_A_BASE = MT < 32 ? 32 : MT;                  // accumulator occupies [0, MT)
     // A4: scale factors in TMEM.  One instruction reads, per operand, 4 scale bytes (one 32-bit column
@@ -99,7 +106,7 @@ template <int MT, bool A4 = false> struct Cfg {
     // After the base K loop the whole staging area is re-used for the LoRA K blocks: each block holds up
     // to four granules, each a B_s tile [128 x 16] and a masked-t tile [MT x 16], BF16, K-major, SWIZZLE_32B.
     static constexpr int L_GRAN_A = FT * 32;                                     // one granule of B_s: [128 x 16] BF16
-    static constexpr int L_GRAN_T = MT * 32;                                     // one granule of masked t: [MT x 16] BF16
+    static constexpr int L_GRAN_T = XROWS * 32;                                  // one granule of masked t: [XROWS x 16] BF16
     static constexpr int L_TILE_A = 4 * L_GRAN_A;
     static constexpr int L_BLOCK = L_TILE_A + 4 * L_GRAN_T;
     static constexpr int L_STAGES = (STAGING_BASE / L_BLOCK) >= 4 ? 4 : ((STAGING_BASE / L_BLOCK) >= 3 ? 3 : 4);
@@ -113,6 +120,7 @@ template <int MT, bool A4 = false> struct Cfg {
     static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_STAGES + 3 + 2 * L_STAGES;
     static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;                      // tmem ptr, n_gran, abort
     static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;                      // + alignment slack
+    static_assert(!PAIR || MT >= 128, "pairs are built for token tiles of 128 and 256");
     static_assert(TMEM_NEEDED <= 512, "tensor memory budget");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
@@ -208,10 +216,52 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+// Two-CTA form: the data lands in this CTA's shared memory, the bytes are counted on an mbarrier that may
+// live in the pair's other CTA (`bar` is a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1, int32_t c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+// shared::cluster address of this CTA's shared-memory address `addr` as seen in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+// arrive on an mbarrier given by its shared::cluster address (possibly in the other CTA)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+    // (CTA-scope release, as for a local arrive: what the barrier orders here is tensor-memory and async-proxy
+    //  traffic, fenced separately; a cluster-scope release measured ~1700 cycles per arrive)
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
+// Two-CTA forms: executed by the same warp of both CTAs of a pair; the same columns are taken in both.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
 }
@@ -224,34 +274,67 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
 
 // D[tmem] (+)= A[tmem] * B[smem]^T, BF16 inputs, FP32 accumulate; one thread issues.
 // A: 128 lanes x 8 columns (16 BF16 per lane, two per 32-bit column, even k in the low half).
+template <bool PAIR = false>
 __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    if constexpr (PAIR) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    
+    }
 }
 // D[tmem] (+)= A[smem] * B[smem]^T (both operands K-major shared-memory tiles); one thread issues.
+template <bool PAIR = false>
 __device__ __forceinline__ void umma_bf16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    if constexpr (PAIR) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    
+    }
 }
 // D[tmem] (+)= (A * SFA)[smem] * (B * SFB)[smem]^T : E2M1 operands (K = 64 per instruction), one UE4M3
 // scale per 16 elements held in tensor memory; one thread issues.
+template <bool PAIR = false>
 __device__ __forceinline__ void umma_nvfp4_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+    if constexpr (PAIR) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+    
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+    
+    }
 }
 // block-scaled instruction descriptor: A = B = E2M1, UE4M3 scales, both K-major, M = 128, N = n, K = 64
-__host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t n) {
-    return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (0u << 23) | ((128u >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t n, uint32_t m = 128u) {
+    return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (0u << 23) | ((m >> 4) << 24);
 }
 // registers -> 32 lanes x N consecutive 32-bit TMEM columns (lane = this warp's quadrant base + laneid)
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -265,8 +348,17 @@ __device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b,
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // Arrive on an mbarrier once all tcgen05.mma issued so far by this thread have completed.
+// When every MMA issued so far has completed, arrive on mbarrier `bar`; the pair form arrives on the
+// barrier at that shared-memory offset in BOTH CTAs of the pair.
+template <bool PAIR = false>
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    if constexpr (PAIR) {
+        const uint16_t both = 3;
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                     ::"r"(bar), "h"(both) : "memory");
+    } else {
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    }
 }
 
 // 32 lanes x 16 consecutive columns of 32-bit TMEM -> 16 registers per thread.
@@ -297,8 +389,8 @@ __device__ __forceinline__ uint64_t make_kmajor_sw32_desc(uint32_t smem_addr) {
 // byte offset of 16-byte chunk `c` (0..1) of row `r` in a SWIZZLE_32B tile of 32-byte rows
 __device__ __forceinline__ uint32_t sw32_off(uint32_t r, uint32_t c) { return r * 32u + ((c ^ ((r >> 2) & 1u)) << 4); }
 // kind::f16 instruction descriptor: D = F32, A = B = BF16, both K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t make_idesc_bf16(uint32_t n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc_bf16(uint32_t n, uint32_t m = 128u) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -364,7 +456,7 @@ __device__ __forceinline__ void epilogue_columns(const Params& p, uint32_t tmem_
 
 // map_x: activations (A16: BF16 [M, K]; A4: packed codes [M, K/2]); map_w / map_s: packed weight codes and
 // their scale bytes; map_b: the strided adapter pool's B side; map_xs: A4 only, activation scale bytes [M, K/16].
-template <int MT, bool A4>
+template <int MT, bool A4, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                             const __grid_constant__ CUtensorMap map_w,
@@ -372,7 +464,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                             const __grid_constant__ CUtensorMap map_b,
                             const __grid_constant__ CUtensorMap map_xs,
                             const Params p) {
-    using C = Cfg<MT, A4>;
+    using C = Cfg<MT, A4, PAIR>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -405,6 +497,11 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t f0 = blockIdx.x * FT;
     const uint32_t m0 = blockIdx.y * MT;
+    // a pair = the two CTAs of a cluster (neighbouring feature tiles); its first CTA issues the MMAs for both
+    const uint32_t cta_rank = PAIR ? cluster_cta_rank() : 0u;
+    const bool leader = cta_rank == 0u;
+    const uint32_t mx0 = m0 + cta_rank * C::XROWS;       // first token row whose activations this CTA stages
+    constexpr uint32_t CTAS = PAIR ? 2u : 1u;
     const uint32_t num_kb = A4 ? p.K / KRAW : (p.K + KB - 1) / KB;     // pipeline steps of the base K loop
     const bool prof = p.profile != nullptr;
     const long long t_entry = clock64();
@@ -413,7 +510,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
 
     if (tid == 0) {
         for (int i = 0; i < C::STAGES; ++i) {
-            mbar_init(BAR_FULL + 8 * i, DEQ_GROUP_WARPS + 1);
+            mbar_init(BAR_FULL + 8 * i, CTAS * DEQ_GROUP_WARPS + 1);     // used in the pair's first CTA only
             mbar_init(BAR_EMPTY + 8 * i, 1);
         }
         for (int i = 0; i < C::RAW_STAGES; ++i) {
@@ -424,7 +521,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         mbar_init(BAR_LIST, 1);
         mbar_init(BAR_DRAINED, DEQ_WARPS);
         for (int i = 0; i < C::L_STAGES; ++i) {
-            mbar_init(BAR_LFULL + 8 * i, DEQ_WARPS + 1);
+            mbar_init(BAR_LFULL + 8 * i, CTAS * DEQ_WARPS + 1);
             mbar_init(BAR_LEMPTY + 8 * i, 1);
         }
         misc[1] = 0;
@@ -432,8 +529,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_base + C::OFF_MISC, C::TMEM_COLS);
-        tmem_relinquish();
+        if constexpr (PAIR) { tmem_alloc_pair(smem_base + C::OFF_MISC, C::TMEM_COLS); tmem_relinquish_pair(); }
+        else { tmem_alloc(smem_base + C::OFF_MISC, C::TMEM_COLS); tmem_relinquish(); }
     }
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&map_x);
@@ -443,8 +540,16 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         if (A4) tma_prefetch_desc(&map_xs);
     }
     tcgen05_fence_before();
-    __syncthreads();
+    __syncwarp();
+    // (pair: neither CTA may signal the other's barriers before they are initialised)
+    if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
     tcgen05_fence_after();
+    // barriers the MMA thread waits on live in the pair's first CTA; everyone else arrives there
+    const uint32_t full_at_leader = PAIR ? map_to_cta(BAR_FULL, 0u) : BAR_FULL;
+    const uint32_t lfull_at_leader = PAIR ? map_to_cta(BAR_LFULL, 0u) : BAR_LFULL;
+    auto arrive_at_leader = [&](uint32_t bar_at_leader) {
+        if constexpr (PAIR) mbar_arrive_cluster(bar_at_leader); else mbar_arrive(bar_at_leader);
+    };
     const uint32_t tmem_acc = misc[0];
     const uint32_t tmem_a0 = tmem_acc + C::TMEM_A_BASE;   // A16: weight-operand stages [tmem_a0 + s * A_COLS, + A_COLS);
                                                           // A4: scale-factor stages [tmem_a0 + s * SF_COLS, + SF_COLS)
@@ -454,7 +559,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         if (lane == 0 && A4) {
             // One ring: a stage's two packed operand tiles complete FULL[s] (which the MMA thread waits
             // on), its two scale-byte tiles FULL_RAW[s] (which the warps that move them to TMEM wait on).
-            const uint32_t rot = blockIdx.x % num_kb;
+            const uint32_t rot = (blockIdx.x / CTAS) % num_kb;     // (the CTAs of a pair walk K in the same order)
             uint32_t s = 0, ph = 0;
             for (uint32_t it = 0; it < num_kb; ++it) {
                 if (!mbar_wait(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER, 32)) break;
@@ -463,9 +568,14 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 mbar_arrive_expect_tx(BAR_FULL_RAW + 8 * s, RAW_SCALE_BYTES + MT * 16);
                 tma_load_2d(st + C::S4_WS, &map_s, int32_t(kk * (KRAW / 16)), int32_t(f0), BAR_FULL_RAW + 8 * s);
                 tma_load_2d(st + C::S4_XS, &map_xs, int32_t(kk * (KRAW / 16)), int32_t(m0), BAR_FULL_RAW + 8 * s);
-                mbar_arrive_expect_tx(BAR_FULL + 8 * s, RAW_PACKED_BYTES + MT * 128);
-                tma_load_2d(st + C::S4_W, &map_w, int32_t(kk * (KRAW / 2)), int32_t(f0), BAR_FULL + 8 * s);
-                tma_load_2d(st + C::S4_X, &map_x, int32_t(kk * (KRAW / 2)), int32_t(m0), BAR_FULL + 8 * s);
+                if (leader) mbar_arrive_expect_tx(BAR_FULL + 8 * s, CTAS * (RAW_PACKED_BYTES + C::XROWS * 128));
+                if constexpr (PAIR) {
+                    tma_load_2d_pair(st + C::S4_W, &map_w, int32_t(kk * (KRAW / 2)), int32_t(f0), full_at_leader + 8 * s);
+                    tma_load_2d_pair(st + C::S4_X, &map_x, int32_t(kk * (KRAW / 2)), int32_t(mx0), full_at_leader + 8 * s);
+                } else {
+                    tma_load_2d(st + C::S4_W, &map_w, int32_t(kk * (KRAW / 2)), int32_t(f0), BAR_FULL + 8 * s);
+                    tma_load_2d(st + C::S4_X, &map_x, int32_t(kk * (KRAW / 2)), int32_t(m0), BAR_FULL + 8 * s);
+                }
                 if (++s == uint32_t(C::STAGES)) { s = 0; ph ^= 1u; }
             }
         }
@@ -476,7 +586,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             // CTAs start their K loop at different K offsets (a rotation in units of one raw stage),
             // so concurrently running CTAs do not all pull the same activation lines at one moment.
             const uint32_t num_raw = (num_kb + 3u) / 4u;
-            const uint32_t rot_raw = (num_kb % 4u == 0u) ? (blockIdx.x % num_raw) : 0u;
+            const uint32_t rot_raw = (num_kb % 4u == 0u) ? ((blockIdx.x / CTAS) % num_raw) : 0u;   // (same for both CTAs of a pair)
             uint32_t it = 0, ri = 0, spins = 0;
             uint64_t t0 = 0;
             while (it < num_kb || ri < num_raw) {
@@ -495,9 +605,10 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 if (it < num_kb) {
                     const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
                     if (mbar_try_wait(BAR_EMPTY + 8 * s, ph ^ 1u)) {
-                        mbar_arrive_expect_tx(BAR_FULL + 8 * s, C::X_TILE_BYTES);
+                        if (leader) mbar_arrive_expect_tx(BAR_FULL + 8 * s, CTAS * C::X_TILE_BYTES);
                         const uint32_t kb = (it + 4u * rot_raw) % num_kb;
-                        tma_load_2d(x_tile0 + s * C::X_TILE_BYTES, &map_x, int32_t(kb * KB), int32_t(m0), BAR_FULL + 8 * s);
+                        if constexpr (PAIR) tma_load_2d_pair(x_tile0 + s * C::X_TILE_BYTES, &map_x, int32_t(kb * KB), int32_t(mx0), full_at_leader + 8 * s);
+                        else tma_load_2d(x_tile0 + s * C::X_TILE_BYTES, &map_x, int32_t(kb * KB), int32_t(m0), BAR_FULL + 8 * s);
                         ++it;
                         progressed = true;
                     }
@@ -532,10 +643,11 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                         if (!mbar_wait(BAR_LEMPTY + 8 * ls, lph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER)) break;
                         const uint32_t ng = min(4u, n_gran - g0);
                         const uint32_t base = x_tile0 + ls * C::L_BLOCK;
-                        mbar_arrive_expect_tx(BAR_LFULL + 8 * ls, ng * C::L_GRAN_A);
+                        if (leader) mbar_arrive_expect_tx(BAR_LFULL + 8 * ls, CTAS * ng * C::L_GRAN_A);
                         for (uint32_t g = 0; g < ng; ++g) {
                             const uint32_t e = gran[g0 + g];
-                            tma_load_3d(base + g * C::L_GRAN_A, &map_b, int32_t((e & 3u) * 16u), int32_t(f0), int32_t(e >> 2), BAR_LFULL + 8 * ls);
+                            if constexpr (PAIR) tma_load_3d_pair(base + g * C::L_GRAN_A, &map_b, int32_t((e & 3u) * 16u), int32_t(f0), int32_t(e >> 2), lfull_at_leader + 8 * ls);
+                            else tma_load_3d(base + g * C::L_GRAN_A, &map_b, int32_t((e & 3u) * 16u), int32_t(f0), int32_t(e >> 2), BAR_LFULL + 8 * ls);
                         }
                         if (++ls == uint32_t(C::L_STAGES)) { ls = 0; lph ^= 1u; }
                     }
@@ -548,8 +660,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         // queued, so whatever this thread executes between the last MMA of one K block and the
         // first of the next must fit inside that short queue or the tensor pipe drains: the loop
         // carries its stage/phase/operand addresses incrementally and waits on ONE barrier per block.
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_bf16(MT);
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = make_idesc_bf16(MT, 128u * CTAS);
             unsigned long long w_full = 0;
             const long long t_begin = prof ? clock64() : 0;
             bool ok = true;
@@ -561,7 +673,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             if constexpr (A4) {
                 // four K=64 block-scaled instructions per stage; both operands are the packed tiles, the
                 // scales sit in this stage's TMEM columns
-                constexpr uint32_t idesc4 = make_idesc_nvfp4(MT);
+                constexpr uint32_t idesc4 = make_idesc_nvfp4(MT, 128u * CTAS);
                 uint32_t st = smem_base, sf = tmem_a0;
                 for (uint32_t it = 0; it < num_kb; ++it) {
                     ok = mbar_wait_timed(bar_full, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full, MMA_BACKOFF_NS);
@@ -571,8 +683,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     const uint64_t xb = make_kmajor_sw128_desc(st + C::S4_X);
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i)   // 64 k = 32 bytes along the swizzled 128-byte row
-                        umma_nvfp4_ss(tmem_acc, wa + 2 * i, xb + 2 * i, idesc4, sf + 4 * i, sf + 16 + 4 * C::XSF_BLOCKS * i, acc | i);
-                    umma_commit(bar_empty);
+                        umma_nvfp4_ss<PAIR>(tmem_acc, wa + 2 * i, xb + 2 * i, idesc4, sf + 4 * i, sf + 16 + 4 * C::XSF_BLOCKS * i, acc | i);
+                    umma_commit<PAIR>(bar_empty);
                     acc = 1u;
                     bar_full += 8; bar_empty += 8; st += C::S4_BYTES; sf += C::SF_COLS;
                     if (++s == uint32_t(C::STAGES)) { s = 0; ph ^= 1u; bar_full = BAR_FULL; bar_empty = BAR_EMPTY; st = smem_base; sf = tmem_a0; }
@@ -592,17 +704,18 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     n_full = BAR_FULL; n_empty = BAR_EMPTY; n_a = tmem_a0; n_b = b_desc - b_desc_step * (C::STAGES - 1);
                 }
                 // 16 k per instruction: 8 TMEM columns of A, 32 bytes along the swizzled row of B
-                umma_bf16_ts(tmem_acc, a_tmem, b_desc, idesc, acc);
-                umma_bf16_ts(tmem_acc, a_tmem + 8, b_desc + 2, idesc, 1u);
+                umma_bf16_ts<PAIR>(tmem_acc, a_tmem, b_desc, idesc, acc);
+                umma_bf16_ts<PAIR>(tmem_acc, a_tmem + 8, b_desc + 2, idesc, 1u);
                 // look at the next block's barrier while the tensor pipe still holds queued work
                 ready = mbar_try_wait(n_full, n_ph);
-                umma_bf16_ts(tmem_acc, a_tmem + 16, b_desc + 4, idesc, 1u);
-                umma_bf16_ts(tmem_acc, a_tmem + 24, b_desc + 6, idesc, 1u);
-                umma_commit(bar_empty);
+                umma_bf16_ts<PAIR>(tmem_acc, a_tmem + 16, b_desc + 4, idesc, 1u);
+                umma_bf16_ts<PAIR>(tmem_acc, a_tmem + 24, b_desc + 6, idesc, 1u);
+                umma_commit<PAIR>(bar_empty);
                 acc = 1u;
                 bar_full = n_full; bar_empty = n_empty; a_tmem = n_a; b_desc = n_b; ph = n_ph;
             }
             ready = false;
+            if (prof) { prof_row[14] = (unsigned long long)(clock64() - t_begin); prof_row[15] = w_full; }
             // base K blocks issued; the LoRA K blocks follow once the granule list is known
             if (ok) ok = mbar_wait(BAR_LIST, 0, abort_flag, STATUS_WAIT_EXPIRED_MMA, 32);
             if (ok) {
@@ -617,12 +730,12 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     const uint64_t la = make_kmajor_sw32_desc(x_tile0 + ls * C::L_BLOCK);
                     const uint64_t lb_ = make_kmajor_sw32_desc(x_tile0 + ls * C::L_BLOCK + C::L_TILE_A);
                     for (uint32_t k = 0; k < ksteps; ++k)   // one granule = one 16-wide K step with its own pair of tiles
-                        umma_bf16_ss(tmem_acc, la + k * (C::L_GRAN_A >> 4), lb_ + k * (C::L_GRAN_T >> 4), idesc, 1u);
-                    umma_commit(BAR_LEMPTY + 8 * ls);
+                        umma_bf16_ss<PAIR>(tmem_acc, la + k * (C::L_GRAN_A >> 4), lb_ + k * (C::L_GRAN_T >> 4), idesc, 1u);
+                    umma_commit<PAIR>(BAR_LEMPTY + 8 * ls);
                     if (++ls == uint32_t(C::L_STAGES)) { ls = 0; lph ^= 1u; }
                 }
             }
-            if (ok) umma_commit(BAR_ACC);
+            if (ok) umma_commit<PAIR>(BAR_ACC);
             if (prof) { prof_row[0] = w_full + ((unsigned long long)(t_begin - t_entry) << 32); prof_row[2] = (unsigned long long)(clock64() - t_begin); }
         }
         __syncwarp();
@@ -785,7 +898,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 tmem_st_wait();
                 tcgen05_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(BAR_FULL + 8 * s);
+                if (lane == 0) arrive_at_leader(full_at_leader + 8 * s);
                 if (++s == uint32_t(C::STAGES)) { s = 0; ph ^= 1u; }
             }
         } else
@@ -834,8 +947,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(BAR_FULL + 8 * s0);
-                    if (two) mbar_arrive(BAR_FULL + 8 * s1);
+                    arrive_at_leader(full_at_leader + 8 * s0);
+                    if (two) arrive_at_leader(full_at_leader + 8 * s1);
                 }
                 s = s1 + DEQ_GROUPS; ph = ph1;
                 if (s >= uint32_t(C::STAGES)) { s -= C::STAGES; ph ^= 1u; }
@@ -880,7 +993,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             if (ok) ok = mbar_wait(BAR_DRAINED, 0, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
         }
         if (ok && n_lb > 0) {
-            constexpr uint32_t T_TASKS = (uint32_t(MT) * 2 + DEQ_THREADS - 1) / DEQ_THREADS;   // per granule
+            constexpr uint32_t XR = uint32_t(C::XROWS);     // this CTA builds the tile's token rows [cta_rank * XR, + XR)
+            constexpr uint32_t T_TASKS = (XR * 2 + DEQ_THREADS - 1) / DEQ_THREADS;             // per granule
             // Masked-t side.  Task -> (row = task % MT, 16-byte chunk = task / MT): eight neighbouring lanes
             // write eight different swizzled chunks.  A row's slot owns `t_ng` consecutive granules
             // starting at list position `t_pos`, so whether block lb touches the row is arithmetic on lb.
@@ -894,17 +1008,18 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
 #pragma unroll
             for (uint32_t u = 0; u < T_TASKS; ++u) {
                 const uint32_t task = td + u * DEQ_THREADS;
-                const uint32_t r = task & (uint32_t(MT) - 1u), hh = task / uint32_t(MT);
-                const uint32_t pg = (task < uint32_t(MT) * 2 && p.seq_slot) ? row_pg[r] : 0xFFFFu;
+                const uint32_t r = task & (XR - 1u), hh = task / XR;
+                const uint32_t tile_row = cta_rank * XR + r;
+                const uint32_t pg = (task < XR * 2 && p.seq_slot) ? row_pg[tile_row] : 0xFFFFu;
                 t_ng[u] = pg == 0xFFFFu ? 0u : (pg & 7u);
                 t_pos[u] = int32_t(pg >> 3);
-                t_src[u] = p.t + size_t(m0 + r) * p.max_rank + 8 * hh;
+                t_src[u] = p.t + size_t(m0 + tile_row) * p.max_rank + 8 * hh;
                 t_dst[u] = C::L_TILE_A + r * 32u + ((hh ^ ((r >> 2) & 1u)) << 4);
                 // granule columns beyond max_rank do not exist in t: treat as not routed
                 if (t_ng[u] && 16 * (t_ng[u] - 1) + 8 * hh >= p.max_rank) t_ng[u] -= 1;
             }
-            for (uint32_t i = td; i < uint32_t(C::L_STAGES) * uint32_t(MT) * 8u; i += DEQ_THREADS) {
-                const uint32_t st_i = i / (uint32_t(MT) * 8u), off = (i % (uint32_t(MT) * 8u)) * 16u;
+            for (uint32_t i = td; i < uint32_t(C::L_STAGES) * XR * 8u; i += DEQ_THREADS) {
+                const uint32_t st_i = i / (XR * 8u), off = (i % (XR * 8u)) * 16u;
                 sts128(x_tile0 + st_i * C::L_BLOCK + C::L_TILE_A + off, 0u, 0u, 0u, 0u);
             }
             // B_s side: this thread copies chunk (2 g + a_h) of feature row a_row
@@ -920,7 +1035,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 const uint32_t base = x_tile0 + ls * C::L_BLOCK;
                 const uint32_t ng = min(4u, n_gran - lb * 4);
                 // the block's ninth arrival comes from the TMA producer when it fetches B_s, else from here
-                if (td == 0 && !p.b_pool_strided) mbar_arrive(BAR_LFULL + 8 * ls);
+                if (td == 0 && leader && !p.b_pool_strided) mbar_arrive(BAR_LFULL + 8 * ls);
                 if (!p.b_pool_strided)
 #pragma unroll
                 for (uint32_t g = 0; g < 4; ++g) {
@@ -962,7 +1077,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 if (prof) w_group += (unsigned long long)(clock64() - t_g0);
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(BAR_LFULL + 8 * cs);
+                if (lane == 0) arrive_at_leader(lfull_at_leader + 8 * cs);
                 if (++cs == uint32_t(C::L_STAGES)) cs = 0;
                 if (lb + C::L_STAGES - 1 < n_lb) ok = issue_block(lb + C::L_STAGES - 1);
                 cp_async_commit();
@@ -986,10 +1101,12 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
     }
     tcgen05_fence_before();
-    __syncthreads();
+    __syncwarp();
+    // (pair: the other CTA's MMAs read this CTA's shared and tensor memory, and its warps arrive on this CTA's barriers)
+    if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
     if (warp == 1) {
         tcgen05_fence_after();
-        tmem_dealloc(tmem_acc, C::TMEM_COLS);
+        if constexpr (PAIR) tmem_dealloc_pair(tmem_acc, C::TMEM_COLS); else tmem_dealloc(tmem_acc, C::TMEM_COLS);
         if (prof && lane == 0) { prof_row[1] = (unsigned long long)(clock64() - t_entry); prof_row[8] = t_entry_ns; prof_row[9] = global_timer_ns(); }
     }
 }

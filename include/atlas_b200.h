@@ -63,6 +63,7 @@ extern "C" {
                                                tcgen05 path (-1 where that path does not take the shape; nothing else is
                                                substituted) and `ws` of ATLAS_B200_ACT_FP4_WS_BYTES(m, k) bytes, 256-byte
                                                aligned (-2 / -3 / -4 otherwise).  Weight scale bytes must not carry a sign bit. */
+#define ATLAS_B200_FLAG_NO_CTA_PAIR   32u   /* tcgen05 path: keep every CTA on its own (no two-CTA MMAs); for comparison runs */
 #define ATLAS_B200_ACT_FP4_WS_BYTES(m, k) \
     ((((size_t)(m) * ((k) / 2) + 255) / 256) * 256 + (size_t)(m) * ((k) / 16))
 
