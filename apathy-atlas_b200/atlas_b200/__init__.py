@@ -26,6 +26,11 @@ VARIANT_NONE, VARIANT_SIMT, VARIANT_TCGEN05 = 0, 1, 2
 FLAG_FORCE_SIMT, FLAG_FORCE_TCGEN05, FLAG_STAGED_LORA, FLAG_REUSE_SHRINK, FLAG_ACT_FP4, FLAG_NO_CTA_PAIR = 1, 2, 4, 8, 16, 32
 
 
+def lora_ws_bytes(m: int, max_loras: int, max_rank: int) -> int:
+    """Scratch that lets the shrink hand the LoRA K-steps' activation tiles to the fused kernel (ATLAS_B200_LORA_WS_BYTES)."""
+    return (m + 255) // 256 * 256 * min(max_loras, 256) * ((max_rank + 15) // 16) * 32
+
+
 def act_fp4_ws_bytes(m: int, k: int) -> int:
     """Scratch a FLAG_ACT_FP4 call needs in `ws` (ATLAS_B200_ACT_FP4_WS_BYTES): packed codes, then scale bytes."""
     return (m * (k // 2) + 255) // 256 * 256 + m * (k // 16)

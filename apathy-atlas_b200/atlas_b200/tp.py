@@ -72,12 +72,13 @@ class DeviceShard:
 
     def desc(self, y, extra_flags: int = 0, out_row_stride=None):
         lc = self.local_case
-        ws, ws_bytes = None, 0
+        # scratch: the FP4 activations (when asked for), then the LoRA activation tiles
+        ws_bytes = self.ab.lora_ws_bytes(lc.M, lc.max_loras, lc.max_rank)
         if extra_flags & self.ab.FLAG_ACT_FP4:
-            ws_bytes = self.ab.act_fp4_ws_bytes(lc.M, lc.K)
-            if getattr(self, "_ws", None) is None or self._ws.numel() < ws_bytes:
-                self._ws = self.torch.empty(ws_bytes, dtype=self.torch.uint8, device="cuda")
-            ws = self._ws
+            ws_bytes += (self.ab.act_fp4_ws_bytes(lc.M, lc.K) + 255) // 256 * 256
+        if getattr(self, "_ws", None) is None or self._ws.numel() < ws_bytes:
+            self._ws = self.torch.empty(ws_bytes, dtype=self.torch.uint8, device="cuda")
+        ws = self._ws
         return self.ab.make_linear_desc(ws=ws, ws_bytes=ws_bytes,
             x=self.x, m=lc.M, k=lc.K, n=lc.N, y=y, w_packed=self.packed, w_scale=self.scales, scale2=lc.scale2,
             w_bf16=self.w_bf16, seq_slot=self.seq_slot, route=self.pool.route(), lora_t=self.lora_t,

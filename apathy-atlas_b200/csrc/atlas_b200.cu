@@ -85,6 +85,11 @@ static bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem, con
 // ---------------------------------------------------------------------------------------------
 namespace ops {
 
+// tensor-core shrink where rows can be read with aligned 128-bit loads in whole 32-element chunks
+static bool shrink_takes_mma_path(const ShrinkParams& p) {
+    return (p.k_in % 32 == 0) && (p.x_row_stride % 8 == 0) && aligned(p.x, 16) && (p.seq_slot || aligned(p.a_uniform, 4));
+}
+
 static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool release_dependents = false) {
     p.release_dependents = release_dependents ? 1u : 0u;
     if (p.M == 0 || p.max_rank == 0) return ATLAS_B200_OK;
@@ -96,11 +101,11 @@ static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool
         cudaFuncSetAttribute(lora_shrink_mma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         carveout_set = true;
     }
-    // tensor-core shrink where rows can be read with aligned 128-bit loads in whole 32-element chunks
-    const bool mma_ok = (p.k_in % 32 == 0) && (p.x_row_stride % 8 == 0) && aligned(p.x, 16) &&
-                        (p.seq_slot || aligned(p.a_uniform, 4));
+    const bool mma_ok = shrink_takes_mma_path(p);
+    if (p.tile_out && !mma_ok) return ATLAS_B200_ERR_DIMS;      // tile output exists in the tensor-core shrink only
     if (mma_ok) {
-        dim3 grid(n_slots * SHM_KSPLIT, (p.max_rank + SHM_RANKS - 1) / SHM_RANKS, (p.M + SHM_CHUNK - 1) / SHM_CHUNK);
+        const uint32_t chunk = p.chunk ? p.chunk : uint32_t(SHM_CHUNK);
+        dim3 grid(n_slots * SHM_KSPLIT, (p.max_rank + SHM_RANKS - 1) / SHM_RANKS, (p.M + chunk - 1) / chunk);
         if (grid.y > 65535 || grid.z > 65535) return ATLAS_B200_ERR_LIMIT;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = grid;
@@ -225,8 +230,20 @@ static bool tc_eligible(const atlas_b200_linear_desc& d) {
 static size_t act_fp4_codes_bytes(const atlas_b200_linear_desc& d) { return (size_t(d.m) * (d.k / 2) + 255) / 256 * 256; }
 static size_t act_fp4_ws_bytes(const atlas_b200_linear_desc& d) { return act_fp4_codes_bytes(d) + size_t(d.m) * (d.k / 16); }
 
+// The B side of the adapter pool can be described as one 3-D tensor [max_loras][n][max_rank]
+static bool b_pool_is_strided(const atlas_b200_linear_desc& d) {
+    return d.seq_slot && d.b_pool_base && d.b_slot_stride && d.b_slot_stride % 16 == 0 && aligned(d.b_pool_base, 16) &&
+           d.max_rank % 8 == 0;
+}
+
+// Where the shrink's masked-t tiles live in `ws` (tiles == nullptr: the fused kernel builds them itself from lora_t)
+struct TTiles {
+    uint16_t* tiles = nullptr;
+    uint32_t cap = 0;          // blocks reserved per token tile
+};
+
 template <int MT, bool A4, bool PAIR>
-static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_shrink, cudaStream_t st) {
+static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_shrink, const TTiles& tt, cudaStream_t st) {
     using C = tc::Cfg<MT, A4, PAIR>;
     Runtime& rt = runtime();
     slot_idx += (A4 ? 5 : 0) + (PAIR ? 10 : 0);
@@ -236,7 +253,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
         if (e != cudaSuccess) return cuda_status(e);
         rt.tc_attr_set[slot_idx] = true;
     }
-    CUtensorMap map_x, map_w, map_s, map_b, map_xs;
+    CUtensorMap map_x, map_w, map_s, map_b, map_xs, map_t;
     if (A4) {
         // the quantised activations in `ws`, in the weights' own layout
         const uint8_t* codes = static_cast<const uint8_t*>(d.ws);
@@ -257,8 +274,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
         return ATLAS_B200_ERR_DIMS;
 
     // B side of the adapter pool as one 3-D tensor [max_loras][n][max_rank]: box = one granule of one slot
-    const bool b_strided = d.seq_slot && d.b_pool_base && d.b_slot_stride && d.b_slot_stride % 16 == 0 &&
-                           aligned(d.b_pool_base, 16) && d.max_rank % 8 == 0;
+    const bool b_strided = b_pool_is_strided(d);
     if (b_strided) {
         const cuuint64_t dims[3] = {d.max_rank, d.n, d.max_loras};
         const cuuint64_t strides[2] = {uint64_t(d.max_rank) * 2, uint64_t(d.b_slot_stride)};
@@ -272,9 +288,18 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
         map_b = map_s;   // never dereferenced
     }
     if (!A4) map_xs = map_s;   // never dereferenced
+    if (tt.tiles) {
+        // every masked-t tile is MT rows of 16 BF16; a CTA fetches the rows of the tokens it stages
+        const uint64_t rows = uint64_t((d.m + MT - 1) / MT) * tt.cap * MT;
+        if (!encode_2d(&map_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, tt.tiles, 16, rows, 32, 16, C::XROWS, CU_TENSOR_MAP_SWIZZLE_32B))
+            return ATLAS_B200_ERR_DIMS;
+    } else {
+        map_t = map_s;         // never dereferenced
+    }
 
     tc::Params p{};
     p.b_pool_strided = b_strided ? 1u : 0u;
+    p.t_tile_cap = tt.tiles ? tt.cap : 0u;
     p.seq_slot = d.seq_slot;
     p.a_table = d.a_table;
     p.b_table = d.b_table;
@@ -313,7 +338,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
     p.wait_for_shrink = after_shrink ? 1u : 0u;
-    return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>, map_x, map_w, map_s, map_b, map_xs, p));
+    return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>, map_x, map_w, map_s, map_b, map_xs, map_t, p));
 }
 
 static int validate_linear(const atlas_b200_linear_desc& d) {
@@ -358,24 +383,6 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
         if (rc) return rc;
     }
     if (use_tc) {
-        if (d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK)) {
-            // shrink first: t = scale_s / (scale2 * 2^8) * (A_s x), the unit of the MMA accumulator
-            ShrinkParams sp{};
-            sp.x = static_cast<const uint16_t*>(d.x);
-            sp.seq_slot = d.seq_slot;
-            sp.a_table = d.a_table;
-            sp.b_table = d.b_table;
-            sp.scale_table = d.scale_table;
-            sp.rank_table = d.rank_table;
-            sp.out = static_cast<uint16_t*>(d.lora_t);
-            sp.M = d.m; sp.k_in = d.k; sp.max_rank = d.max_rank; sp.x_row_stride = d.x_row_stride; sp.max_loras = d.max_loras;
-            sp.post = act_fp4 ? 1.0f / d.scale2 : 1.0f / (d.scale2 * kWeightPreScale);
-            // A small batch: let the main kernel start under the shrink.  A large one: the shrink is a
-            // sizeable grid that should have the whole machine first; the main kernel then follows it.
-            rc = launch_shrink(sp, d.max_loras, st, d.m <= 1024);
-            if (rc) return rc;
-        }
-        const bool after_shrink = d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK);
         // Token tile: the smallest power of two that covers m, at most 256 — then halved (down to 64)
         // while the grid would leave more than a quarter of the SMs without a CTA, e.g. for a
         // column shard of a wide layer: more, lighter CTAs finish sooner than few heavy ones.
@@ -383,19 +390,56 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
         while (mt < 256 && mt < d.m) mt <<= 1;
         const uint32_t f_tiles = (d.n + tc::FT - 1) / tc::FT;
         while (mt > 64 && f_tiles * ((d.m + mt - 1) / mt) * 4 < uint32_t(rt_sm_count()) * 3) mt >>= 1;
+
+        ShrinkParams sp{};
+        sp.x = static_cast<const uint16_t*>(d.x);
+        sp.seq_slot = d.seq_slot;
+        sp.a_table = d.a_table;
+        sp.b_table = d.b_table;
+        sp.scale_table = d.scale_table;
+        sp.rank_table = d.rank_table;
+        sp.out = static_cast<uint16_t*>(d.lora_t);
+        sp.M = d.m; sp.k_in = d.k; sp.max_rank = d.max_rank; sp.x_row_stride = d.x_row_stride; sp.max_loras = d.max_loras;
+        // t = scale_s / (scale2 * 2^8) * (A_s x), the unit of the MMA accumulator (no 2^8 with FP4 activations)
+        sp.post = act_fp4 ? 1.0f / d.scale2 : 1.0f / (d.scale2 * kWeightPreScale);
+
+        // Masked-t tiles: with scratch to put them in, the shrink writes the activation operand of every LoRA
+        // K-step once, in the layout the MMA reads, and the fused kernel's CTAs fetch it by TMA — instead of
+        // each CTA rebuilding the same tiles from lora_t.  Needs the strided pool (the TMA producer then feeds
+        // both LoRA operands) and the tensor-core shrink; otherwise the in-kernel build stays in use.
+        TTiles tt;
+        if (d.seq_slot && d.ws && b_pool_is_strided(d) && shrink_takes_mma_path(sp)) {
+            const size_t off = act_fp4 ? (act_fp4_ws_bytes(d) + 255) / 256 * 256 : 0;
+            const uint32_t cap = std::min(mt, d.max_loras) * ((d.max_rank + 15u) / 16u);
+            const size_t bytes = size_t((d.m + mt - 1) / mt) * cap * mt * 32;
+            if (aligned(d.ws, 256) && d.ws_bytes >= off + bytes && size_t((d.m + mt - 1) / mt) * cap * mt < (1ull << 31)) {
+                tt.tiles = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(d.ws) + off);
+                tt.cap = cap;
+                sp.tile_out = tt.tiles;
+                sp.tile_cap = cap;
+                sp.chunk = mt;
+            }
+        }
+        if (d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK)) {
+            // A small batch: let the main kernel start under the shrink.  A large one: the shrink is a
+            // sizeable grid that should have the whole machine first; the main kernel then follows it.
+            rc = launch_shrink(sp, d.max_loras, st, d.m <= 1024);
+            if (rc) return rc;
+        }
+        const bool after_shrink = d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK);
         // 128 and 256 tokens: pairs of CTAs issue their MMAs together (see tc::Cfg)
         const bool pair = mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR);
         if (act_fp4) {
-            if (mt == 16) rc = launch_tc<16, true, false>(d, 0, after_shrink, st);
-            else if (mt == 32) rc = launch_tc<32, true, false>(d, 1, after_shrink, st);
-            else if (mt == 64) rc = launch_tc<64, true, false>(d, 2, after_shrink, st);
-            else if (mt == 128) rc = pair ? launch_tc<128, true, true>(d, 3, after_shrink, st) : launch_tc<128, true, false>(d, 3, after_shrink, st);
-            else rc = pair ? launch_tc<256, true, true>(d, 4, after_shrink, st) : launch_tc<256, true, false>(d, 4, after_shrink, st);
-        } else if (mt == 16) rc = launch_tc<16, false, false>(d, 0, after_shrink, st);
-        else if (mt == 32) rc = launch_tc<32, false, false>(d, 1, after_shrink, st);
-        else if (mt == 64) rc = launch_tc<64, false, false>(d, 2, after_shrink, st);
-        else if (mt == 128) rc = pair ? launch_tc<128, false, true>(d, 3, after_shrink, st) : launch_tc<128, false, false>(d, 3, after_shrink, st);
-        else rc = pair ? launch_tc<256, false, true>(d, 4, after_shrink, st) : launch_tc<256, false, false>(d, 4, after_shrink, st);
+            if (mt == 16) rc = launch_tc<16, true, false>(d, 0, after_shrink, tt, st);
+            else if (mt == 32) rc = launch_tc<32, true, false>(d, 1, after_shrink, tt, st);
+            else if (mt == 64) rc = launch_tc<64, true, false>(d, 2, after_shrink, tt, st);
+            else if (mt == 128) rc = pair ? launch_tc<128, true, true>(d, 3, after_shrink, tt, st) : launch_tc<128, true, false>(d, 3, after_shrink, tt, st);
+            else rc = pair ? launch_tc<256, true, true>(d, 4, after_shrink, tt, st) : launch_tc<256, true, false>(d, 4, after_shrink, tt, st);
+        } else if (mt == 16) rc = launch_tc<16, false, false>(d, 0, after_shrink, tt, st);
+        else if (mt == 32) rc = launch_tc<32, false, false>(d, 1, after_shrink, tt, st);
+        else if (mt == 64) rc = launch_tc<64, false, false>(d, 2, after_shrink, tt, st);
+        else if (mt == 128) rc = pair ? launch_tc<128, false, true>(d, 3, after_shrink, tt, st) : launch_tc<128, false, false>(d, 3, after_shrink, tt, st);
+        else rc = pair ? launch_tc<256, false, true>(d, 4, after_shrink, tt, st) : launch_tc<256, false, false>(d, 4, after_shrink, tt, st);
         if (rc == ATLAS_B200_OK) t_last_variant = ATLAS_B200_VARIANT_TCGEN05;
         return rc;
     }

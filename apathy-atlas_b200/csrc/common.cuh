@@ -15,6 +15,7 @@ enum : uint32_t {
     STATUS_OK = 0,
     STATUS_SLOT_OUT_OF_RANGE = 1,   // seq_slot[i] >= max_loras
     STATUS_NEGATIVE_SCALE = 2,      // FP4-activation mode met a weight scale byte with its sign bit set; the sign was dropped
+    STATUS_TILE_CAPACITY = 3,       // the shrink met more (slot, granule) pairs in a token tile than its tile output reserves
     STATUS_WAIT_EXPIRED_PRODUCER = 0x100,
     STATUS_WAIT_EXPIRED_DEQUANT = 0x101,
     STATUS_WAIT_EXPIRED_MMA = 0x102,

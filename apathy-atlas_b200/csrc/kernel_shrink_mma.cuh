@@ -54,7 +54,8 @@ lora_shrink_mma_kernel(const ShrinkParams p) {
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t s = blockIdx.x / SHM_KSPLIT;
     const uint32_t j0 = blockIdx.y * SHM_RANKS;
-    const uint32_t m_base = blockIdx.z * SHM_CHUNK;
+    const uint32_t chunk = p.chunk ? p.chunk : uint32_t(SHM_CHUNK);
+    const uint32_t m_base = blockIdx.z * chunk;
 
     const uint16_t* A;
     float f = 1.0f;
@@ -72,13 +73,13 @@ lora_shrink_mma_kernel(const ShrinkParams p) {
 
     // ---- ordered list of this chunk's rows routed to slot s (two candidates per thread) ----
     uint32_t n_rows;
+    bool hit[2];
     {
-        bool hit[2];
         uint32_t ballot[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const uint32_t m = m_base + h * SHM_THREADS + tid;
-            hit[h] = (m < p.M) && (p.seq_slot ? (p.seq_slot[m] == int32_t(s)) : true);
+            hit[h] = (h * SHM_THREADS + tid < chunk) && (m < p.M) && (p.seq_slot ? (p.seq_slot[m] == int32_t(s)) : true);
             ballot[h] = __ballot_sync(0xFFFFFFFFu, hit[h]);
         }
         __shared__ uint32_t cnt[2][SHM_THREADS / 32];
@@ -105,6 +106,54 @@ lora_shrink_mma_kernel(const ShrinkParams p) {
 
     // ranks at or beyond the adapter's true rank are written as zeros and never read
     const bool any_live = j0 < rank;
+
+    // ---- tile output: where this (slot, granule) pair's block goes, and its zero rows ----
+    uint16_t* tile = nullptr;
+    if (p.tile_out) {
+        if (!any_live) return;                               // the pair is not in the tile's list (whole cluster leaves)
+        if (krank == 0) {
+            // pairs ahead of this one: every granule of every valid slot below s that occurs in the tile
+            __shared__ uint32_t present[SHM_THREADS];        // one bit per slot, 32 * 128 = 4096 slots
+            __shared__ uint32_t ahead[SHM_THREADS / 32];
+            present[tid] = 0u;
+            __syncthreads();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t idx = h * SHM_THREADS + tid, m = m_base + idx;
+                if (idx < chunk && m < p.M) {
+                    const int32_t s2 = p.seq_slot[m];
+                    if (s2 >= 0 && uint32_t(s2) < s && p.a_table[s2] != 0ull && (!p.b_table || p.b_table[s2] != 0ull))
+                        atomicOr(&present[uint32_t(s2) >> 5], 1u << (uint32_t(s2) & 31u));
+                }
+            }
+            __syncthreads();
+            uint32_t cnt = 0;
+            for (uint32_t w = present[tid]; w; w &= w - 1) {
+                const uint32_t s2 = tid * 32 + (__ffs(w) - 1);
+                const uint32_t r2 = p.rank_table ? min(p.rank_table[s2], p.max_rank) : p.max_rank;
+                cnt += (r2 + 15u) / 16u;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xFFFFFFFFu, cnt, o);
+            if (lane == 0) ahead[warp] = cnt;
+            __syncthreads();
+            const uint32_t q = ahead[0] + ahead[1] + ahead[2] + ahead[3] + blockIdx.y;
+            if (q < p.tile_cap) {
+                tile = p.tile_out + (size_t(blockIdx.z) * p.tile_cap + q) * chunk * 16;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t idx = h * SHM_THREADS + tid;
+                    if (idx < chunk && !hit[h]) {
+                        uint4* z = reinterpret_cast<uint4*>(tile + size_t(idx) * 16);
+                        z[0] = make_uint4(0u, 0u, 0u, 0u);
+                        z[1] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+            } else {
+                record_status(STATUS_TILE_CAPACITY);         // cannot happen with a capacity computed as documented
+            }
+        }
+    }
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t n_chunks = p.k_in / 32;
     const bool a_aligned = (reinterpret_cast<uintptr_t>(A) & 15u) == 0;
@@ -181,12 +230,13 @@ lora_shrink_mma_kernel(const ShrinkParams p) {
         if (krank == 0) {
             for (uint32_t i = tid; i < SHM_TOKENS * SHM_RANKS; i += SHM_THREADS) {
                 const uint32_t tok = i / SHM_RANKS, jr = i % SHM_RANKS;
-                if (r0 + tok < n_rows && j0 + jr < p.max_rank) {
+                if (r0 + tok < n_rows && (p.tile_out || j0 + jr < p.max_rank)) {
                     float v = 0.0f;
 #pragma unroll
                     for (int r = 0; r < SHM_KSPLIT; ++r) v += cluster.map_shared_rank(&part[0][0], r)[i];
-                    const uint32_t m = m_base + rows[r0 + tok];
-                    p.out[size_t(m) * p.max_rank + j0 + jr] = f32_to_bf16_bits((j0 + jr < rank) ? v * f : 0.0f);
+                    const uint16_t bits = f32_to_bf16_bits((j0 + jr < rank) ? v * f : 0.0f);
+                    if (p.tile_out) { if (tile) tile[size_t(rows[r0 + tok]) * 16 + jr] = bits; }
+                    else p.out[size_t(m_base + rows[r0 + tok]) * p.max_rank + j0 + jr] = bits;
                 }
             }
         }

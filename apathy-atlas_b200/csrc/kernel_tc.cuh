@@ -134,6 +134,8 @@ struct Params {
     uint16_t* y;
     uint32_t M, N, K, out_row_stride, max_loras, max_rank;
     float out_scale;               // scale2 * 2^8 (A16) or scale2 (A4)
+    uint32_t t_tile_cap;           // != 0: the shrink wrote masked-t tiles (ShrinkParams::tile_out) with this many blocks
+                                   //       reserved per token tile; they are fetched by TMA (map_t) and `t` is not read
     uint32_t b_pool_strided;       // B_s tiles can be fetched by TMA from a [max_loras][N][max_rank] strided pool
     uint32_t wait_for_shrink;      // launched as a programmatic dependent of the shrink: wait before reading t
     unsigned long long* profile;   // nullable: per-CTA wait/busy cycle counters (PROFILE_WORDS per CTA)
@@ -455,7 +457,8 @@ __device__ __forceinline__ void epilogue_columns(const Params& p, uint32_t tmem_
 }
 
 // map_x: activations (A16: BF16 [M, K]; A4: packed codes [M, K/2]); map_w / map_s: packed weight codes and
-// their scale bytes; map_b: the strided adapter pool's B side; map_xs: A4 only, activation scale bytes [M, K/16].
+// their scale bytes; map_b: the strided adapter pool's B side; map_xs: A4 only, activation scale bytes [M, K/16];
+// map_t: the shrink's masked-t tiles as rows of 16 BF16, when p.t_tile_cap != 0.
 template <int MT, bool A4, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
@@ -463,6 +466,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                             const __grid_constant__ CUtensorMap map_s,
                             const __grid_constant__ CUtensorMap map_b,
                             const __grid_constant__ CUtensorMap map_xs,
+                            const __grid_constant__ CUtensorMap map_t,
                             const Params p) {
     using C = Cfg<MT, A4, PAIR>;
     extern __shared__ uint8_t smem_raw[];
@@ -521,7 +525,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         mbar_init(BAR_LIST, 1);
         mbar_init(BAR_DRAINED, DEQ_WARPS);
         for (int i = 0; i < C::L_STAGES; ++i) {
-            mbar_init(BAR_LFULL + 8 * i, CTAS * DEQ_WARPS + 1);
+            mbar_init(BAR_LFULL + 8 * i, p.t_tile_cap ? 1u : CTAS * DEQ_WARPS + 1);
             mbar_init(BAR_LEMPTY + 8 * i, 1);
         }
         misc[1] = 0;
@@ -538,6 +542,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         tma_prefetch_desc(&map_s);
         if (p.b_pool_strided) tma_prefetch_desc(&map_b);
         if (A4) tma_prefetch_desc(&map_xs);
+        if (p.t_tile_cap) tma_prefetch_desc(&map_t);
     }
     tcgen05_fence_before();
     __syncwarp();
@@ -638,16 +643,24 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 const uint32_t n_gran = misc[1];
                 // the staging area may be overwritten once the expansion warps have seen every base MMA finish
                 if (n_gran && mbar_wait(BAR_DRAINED, 0, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER, 32)) {
+                    // masked-t tiles are the shrink grid's output: it must be complete before they are fetched
+                    if (p.t_tile_cap && p.wait_for_shrink) asm volatile("griddepcontrol.wait;" ::: "memory");
+                    const uint32_t t_row0 = blockIdx.y * p.t_tile_cap * uint32_t(MT) + cta_rank * uint32_t(C::XROWS);
                     uint32_t ls = 0, lph = 0;
                     for (uint32_t g0 = 0; g0 < n_gran; g0 += 4) {
                         if (!mbar_wait(BAR_LEMPTY + 8 * ls, lph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER)) break;
                         const uint32_t ng = min(4u, n_gran - g0);
                         const uint32_t base = x_tile0 + ls * C::L_BLOCK;
-                        if (leader) mbar_arrive_expect_tx(BAR_LFULL + 8 * ls, CTAS * ng * C::L_GRAN_A);
+                        if (leader) mbar_arrive_expect_tx(BAR_LFULL + 8 * ls, CTAS * ng * (C::L_GRAN_A + (p.t_tile_cap ? C::L_GRAN_T : 0)));
                         for (uint32_t g = 0; g < ng; ++g) {
                             const uint32_t e = gran[g0 + g];
                             if constexpr (PAIR) tma_load_3d_pair(base + g * C::L_GRAN_A, &map_b, int32_t((e & 3u) * 16u), int32_t(f0), int32_t(e >> 2), lfull_at_leader + 8 * ls);
                             else tma_load_3d(base + g * C::L_GRAN_A, &map_b, int32_t((e & 3u) * 16u), int32_t(f0), int32_t(e >> 2), BAR_LFULL + 8 * ls);
+                            if (p.t_tile_cap) {
+                                const int32_t row = int32_t(t_row0 + (g0 + g) * uint32_t(MT));
+                                if constexpr (PAIR) tma_load_2d_pair(base + C::L_TILE_A + g * C::L_GRAN_T, &map_t, 0, row, lfull_at_leader + 8 * ls);
+                                else tma_load_2d(base + C::L_TILE_A + g * C::L_GRAN_T, &map_t, 0, row, BAR_LFULL + 8 * ls);
+                            }
                         }
                         if (++ls == uint32_t(C::L_STAGES)) { ls = 0; lph ^= 1u; }
                     }
@@ -992,7 +1005,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             if (lane == 0) mbar_arrive(BAR_DRAINED);
             if (ok) ok = mbar_wait(BAR_DRAINED, 0, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT);
         }
-        if (ok && n_lb > 0) {
+        if (ok && n_lb > 0 && !p.t_tile_cap) {
             constexpr uint32_t XR = uint32_t(C::XROWS);     // this CTA builds the tile's token rows [cta_rank * XR, + XR)
             constexpr uint32_t T_TASKS = (XR * 2 + DEQ_THREADS - 1) / DEQ_THREADS;             // per granule
             // Masked-t side.  Task -> (row = task % MT, 16-byte chunk = task / MT): eight neighbouring lanes

@@ -145,6 +145,15 @@ struct ShrinkParams {
     uint32_t M, k_in, max_rank, x_row_stride, max_loras;
     float post;                     // 0 => unscaled output
     uint32_t release_dependents;    // let a programmatic dependent launch start while this grid runs
+    // Tile output (tensor-core shrink only; tile_out == nullptr: rows of `out` as above).  The token axis
+    // is cut into tiles of `chunk` tokens.  For every tile, the (slot, 16-rank granule) pairs that occur
+    // in it are numbered in ascending (slot, granule) order, and pair number q of tile i is written as a
+    // complete [chunk x 16] BF16 block at tile_out + ((i * tile_cap + q) * chunk) * 16: the shrink result
+    // in rows routed to the slot, zeros in every other row.  That is the activation operand of one LoRA
+    // K-step of the fused kernel, ready to be fetched by TMA.
+    uint16_t* tile_out;
+    uint32_t tile_cap;              // blocks reserved per tile
+    uint32_t chunk;                 // tokens scanned per CTA (<= 256); 0 = 256
 };
 
 __global__ void __launch_bounds__(SHRINK_THREADS)

@@ -63,6 +63,12 @@ extern "C" {
                                                tcgen05 path (-1 where that path does not take the shape; nothing else is
                                                substituted) and `ws` of ATLAS_B200_ACT_FP4_WS_BYTES(m, k) bytes, 256-byte
                                                aligned (-2 / -3 / -4 otherwise).  Weight scale bytes must not carry a sign bit. */
+/* Optional scratch that speeds up the LoRA part of the tcgen05 path: with at least this many bytes of `ws`
+ * (after the ATLAS_B200_ACT_FP4_WS_BYTES region, rounded up to 256, when that flag is set), 256-byte aligned, and a
+ * strided pool declared (b_pool_base / b_slot_stride), the shrink writes the LoRA K-steps' activation tiles there
+ * once per call and `lora_t` is left untouched; with less, every CTA builds them from `lora_t`.  Same results. */
+#define ATLAS_B200_LORA_WS_BYTES(m, max_loras, max_rank) \
+    ((((size_t)(m) + 255) / 256) * 256 * ((max_loras) < 256 ? (max_loras) : 256) * (((size_t)(max_rank) + 15) / 16) * 32)
 #define ATLAS_B200_FLAG_NO_CTA_PAIR   32u   /* tcgen05 path: keep every CTA on its own (no two-CTA MMAs); for comparison runs */
 #define ATLAS_B200_ACT_FP4_WS_BYTES(m, k) \
     ((((size_t)(m) * ((k) / 2) + 255) / 256) * 256 + (size_t)(m) * ((k) / 16))

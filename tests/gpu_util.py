@@ -62,13 +62,16 @@ class DeviceCase:
         self.lora_t = torch.zeros((case.M, case.max_rank), dtype=torch.int16, device="cuda")
         self.torch, self.atlas = torch, atlas
 
-    def run(self, *, lora=True, with_ranks=True, flags=0, fill=0x7FC0, strided=True):
+    def run(self, *, lora=True, with_ranks=True, flags=0, fill=0x7FC0, strided=True, lora_ws=False):
         """Returns (y bits [M, out_row_stride], variant). y is pre-filled with a NaN pattern."""
         torch, atlas, c = self.torch, self.atlas, self.case
         y = torch.full((c.M, self.out_row_stride), np.int16(np.uint16(fill).view(np.int16)), dtype=torch.int16, device="cuda")
         ws, ws_bytes = None, 0
         if flags & atlas.FLAG_ACT_FP4:
             ws_bytes = atlas.act_fp4_ws_bytes(c.M, c.K)
+        if lora_ws:                                        # room for the shrink's activation tiles (after the FP4 region)
+            ws_bytes = (ws_bytes + 255) // 256 * 256 + atlas.lora_ws_bytes(c.M, c.max_loras, c.max_rank)
+        if ws_bytes:
             ws = self.ws = torch.full((ws_bytes,), 0xA5, dtype=torch.uint8, device="cuda")
         d = atlas.make_linear_desc(ws=ws, ws_bytes=ws_bytes,
             x=self.x, m=c.M, k=c.K, n=c.N, y=y, w_packed=self.packed, w_scale=self.scales, scale2=c.scale2,
