@@ -239,7 +239,8 @@ static bool b_pool_is_strided(const atlas_b200_linear_desc& d) {
 // Where the shrink's masked-t tiles live in `ws` (tiles == nullptr: the fused kernel builds them itself from lora_t)
 struct TTiles {
     uint16_t* tiles = nullptr;
-    uint32_t cap = 0;          // blocks reserved per token tile
+    uint32_t cap = 0;          // blocks reserved per token tile (per half of one, for CTA pairs)
+    uint32_t part_rows = 0;    // rows of a block: the token tile, or half of it for CTA pairs
 };
 
 template <int MT, bool A4, bool PAIR>
@@ -289,9 +290,10 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     }
     if (!A4) map_xs = map_s;   // never dereferenced
     if (tt.tiles) {
-        // every masked-t tile is MT rows of 16 BF16; a CTA fetches the rows of the tokens it stages
-        const uint64_t rows = uint64_t((d.m + MT - 1) / MT) * tt.cap * MT;
-        if (!encode_2d(&map_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, tt.tiles, 16, rows, 32, 16, C::XROWS, CU_TENSOR_MAP_SWIZZLE_32B))
+        // the masked-t blocks are shared-memory images already: plain bytes, 256 to a row, one block per copy
+        static_assert(C::L_GRAN_T % 256 == 0, "a block is a whole number of 256-byte rows");
+        const uint64_t rows = uint64_t((d.m + MT - 1) / MT) * tt.cap * MT * 32 / 256;
+        if (!encode_2d(&map_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, tt.tiles, 256, rows, 256, 256, C::L_GRAN_T / 256, CU_TENSOR_MAP_SWIZZLE_NONE))
             return ATLAS_B200_ERR_DIMS;
     } else {
         map_t = map_s;         // never dereferenced
@@ -418,6 +420,7 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
                 sp.tile_out = tt.tiles;
                 sp.tile_cap = cap;
                 sp.chunk = mt;
+                sp.part_rows = tt.part_rows = (mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR)) ? mt / 2 : mt;
             }
         }
         if (d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK)) {

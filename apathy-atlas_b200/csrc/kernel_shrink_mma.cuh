@@ -139,12 +139,14 @@ lora_shrink_mma_kernel(const ShrinkParams p) {
             __syncthreads();
             const uint32_t q = ahead[0] + ahead[1] + ahead[2] + ahead[3] + blockIdx.y;
             if (q < p.tile_cap) {
-                tile = p.tile_out + (size_t(blockIdx.z) * p.tile_cap + q) * chunk * 16;
+                // part 0's block of this pair; part 1's lies tile_cap blocks further on
+                tile = p.tile_out + (size_t(blockIdx.z) * (chunk / p.part_rows) * p.tile_cap + q) * p.part_rows * 16;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const uint32_t idx = h * SHM_THREADS + tid;
                     if (idx < chunk && !hit[h]) {
-                        uint4* z = reinterpret_cast<uint4*>(tile + size_t(idx) * 16);
+                        const uint32_t part = idx / p.part_rows, r = idx % p.part_rows;
+                        uint4* z = reinterpret_cast<uint4*>(tile + (size_t(part) * p.tile_cap * p.part_rows + r) * 16);
                         z[0] = make_uint4(0u, 0u, 0u, 0u);
                         z[1] = make_uint4(0u, 0u, 0u, 0u);
                     }
@@ -235,7 +237,12 @@ lora_shrink_mma_kernel(const ShrinkParams p) {
 #pragma unroll
                     for (int r = 0; r < SHM_KSPLIT; ++r) v += cluster.map_shared_rank(&part[0][0], r)[i];
                     const uint16_t bits = f32_to_bf16_bits((j0 + jr < rank) ? v * f : 0.0f);
-                    if (p.tile_out) { if (tile) tile[size_t(rows[r0 + tok]) * 16 + jr] = bits; }
+                    if (p.tile_out) {
+                        if (tile) {
+                            const uint32_t idx = rows[r0 + tok], part = idx / p.part_rows, r = idx % p.part_rows;
+                            tile[(size_t(part) * p.tile_cap * p.part_rows + r) * 16 + (((jr >> 3) ^ ((r >> 2) & 1u)) << 3) + (jr & 7u)] = bits;
+                        }
+                    }
                     else p.out[size_t(m_base + rows[r0 + tok]) * p.max_rank + j0 + jr] = bits;
                 }
             }

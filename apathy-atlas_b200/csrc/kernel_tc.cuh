@@ -458,7 +458,7 @@ __device__ __forceinline__ void epilogue_columns(const Params& p, uint32_t tmem_
 
 // map_x: activations (A16: BF16 [M, K]; A4: packed codes [M, K/2]); map_w / map_s: packed weight codes and
 // their scale bytes; map_b: the strided adapter pool's B side; map_xs: A4 only, activation scale bytes [M, K/16];
-// map_t: the shrink's masked-t tiles as rows of 16 BF16, when p.t_tile_cap != 0.
+// map_t: the shrink's masked-t blocks as rows of 256 bytes, when p.t_tile_cap != 0.
 template <int MT, bool A4, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
@@ -645,7 +645,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 if (n_gran && mbar_wait(BAR_DRAINED, 0, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER, 32)) {
                     // masked-t tiles are the shrink grid's output: it must be complete before they are fetched
                     if (p.t_tile_cap && p.wait_for_shrink) asm volatile("griddepcontrol.wait;" ::: "memory");
-                    const uint32_t t_row0 = blockIdx.y * p.t_tile_cap * uint32_t(MT) + cta_rank * uint32_t(C::XROWS);
+                    // this CTA's blocks: [XROWS x 16] BF16 images, C::L_GRAN_T bytes each, consecutive in list order
+                    const uint32_t t_row0 = (blockIdx.y * CTAS + cta_rank) * p.t_tile_cap * uint32_t(C::L_GRAN_T / 256);
                     uint32_t ls = 0, lph = 0;
                     for (uint32_t g0 = 0; g0 < n_gran; g0 += 4) {
                         if (!mbar_wait(BAR_LEMPTY + 8 * ls, lph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER)) break;
@@ -657,7 +658,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                             if constexpr (PAIR) tma_load_3d_pair(base + g * C::L_GRAN_A, &map_b, int32_t((e & 3u) * 16u), int32_t(f0), int32_t(e >> 2), lfull_at_leader + 8 * ls);
                             else tma_load_3d(base + g * C::L_GRAN_A, &map_b, int32_t((e & 3u) * 16u), int32_t(f0), int32_t(e >> 2), BAR_LFULL + 8 * ls);
                             if (p.t_tile_cap) {
-                                const int32_t row = int32_t(t_row0 + (g0 + g) * uint32_t(MT));
+                                const int32_t row = int32_t(t_row0 + (g0 + g) * uint32_t(C::L_GRAN_T / 256));
                                 if constexpr (PAIR) tma_load_2d_pair(base + C::L_TILE_A + g * C::L_GRAN_T, &map_t, 0, row, lfull_at_leader + 8 * ls);
                                 else tma_load_2d(base + C::L_TILE_A + g * C::L_GRAN_T, &map_t, 0, row, BAR_LFULL + 8 * ls);
                             }

@@ -146,14 +146,18 @@ struct ShrinkParams {
     float post;                     // 0 => unscaled output
     uint32_t release_dependents;    // let a programmatic dependent launch start while this grid runs
     // Tile output (tensor-core shrink only; tile_out == nullptr: rows of `out` as above).  The token axis
-    // is cut into tiles of `chunk` tokens.  For every tile, the (slot, 16-rank granule) pairs that occur
-    // in it are numbered in ascending (slot, granule) order, and pair number q of tile i is written as a
-    // complete [chunk x 16] BF16 block at tile_out + ((i * tile_cap + q) * chunk) * 16: the shrink result
-    // in rows routed to the slot, zeros in every other row.  That is the activation operand of one LoRA
-    // K-step of the fused kernel, ready to be fetched by TMA.
+    // is cut into tiles of `chunk` tokens, each tile into parts of `part_rows` tokens (the whole tile, or
+    // halves for CTA pairs).  For every tile, the (slot, 16-rank granule) pairs that occur in it are
+    // numbered in ascending (slot, granule) order, and pair number q is written, for part h of tile i, as
+    // a complete [part_rows x 16] BF16 block at tile_out + (((i * parts + h) * tile_cap + q) * part_rows) * 16:
+    // the shrink result in rows routed to the slot, zeros in every other row, the two 16-byte halves of a
+    // row swapped where (row / 4) is odd.  That is the activation operand of one LoRA K-step of the fused
+    // kernel exactly as the MMA reads it from shared memory (K-major, 32-byte swizzle), so blocks are
+    // fetched as plain bytes and consecutive blocks with one copy.
     uint16_t* tile_out;
     uint32_t tile_cap;              // blocks reserved per tile
     uint32_t chunk;                 // tokens scanned per CTA (<= 256); 0 = 256
+    uint32_t part_rows;             // chunk or chunk / 2
 };
 
 __global__ void __launch_bounds__(SHRINK_THREADS)
