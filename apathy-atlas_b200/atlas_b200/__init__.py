@@ -65,6 +65,7 @@ class LinearDesc(C.Structure):
         ("y", C.c_void_p), ("out_row_stride", C.c_uint32), ("reserved0", C.c_uint32),
         ("lora_t", C.c_void_p), ("ws", C.c_void_p), ("ws_bytes", C.c_size_t),
         ("b_pool_base", C.c_void_p), ("b_slot_stride", C.c_size_t),
+        ("n_dest", C.c_uint32), ("y_col_offset", C.c_uint32), ("y_dest", C.c_void_p * 8),
     ]
 
 
@@ -249,7 +250,7 @@ def quantize_bf16_to_nvfp4(inp, packed, scales, scale2: float, n: int, k: int, s
 
 def make_linear_desc(*, x, m, k, n, y, w_packed=None, w_scale=None, scale2=1.0, w_bf16=None,
                      x_row_stride=None, out_row_stride=None, seq_slot=None, route: Optional[LoraRoute] = None,
-                     lora_t=None, flags=0, ws=None, ws_bytes=0) -> LinearDesc:
+                     lora_t=None, flags=0, ws=None, ws_bytes=0, y_dest=None, y_col_offset=0) -> LinearDesc:
     d = LinearDesc()
     d.x, d.m, d.k = _ptr(x), m, k
     d.x_row_stride = x_row_stride if x_row_stride is not None else k
@@ -267,6 +268,10 @@ def make_linear_desc(*, x, m, k, n, y, w_packed=None, w_scale=None, scale2=1.0, 
     d.y = _ptr(y)
     d.out_row_stride = out_row_stride if out_row_stride is not None else n
     d.ws, d.ws_bytes = _ptr(ws), ws_bytes
+    if y_dest is not None:                       # tensor-parallel placement: one gathered buffer per rank
+        d.n_dest, d.y_col_offset = len(y_dest), y_col_offset
+        for i, t in enumerate(y_dest):
+            d.y_dest[i] = _ptr(t)
     return d
 
 

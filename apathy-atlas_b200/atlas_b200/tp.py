@@ -70,7 +70,9 @@ class DeviceShard:
         self.pool.refresh_tables()
         self.lora_t = torch.zeros((lc.M, lc.max_rank), dtype=torch.int16, device="cuda")
 
-    def desc(self, y, extra_flags: int = 0, out_row_stride=None):
+    def desc(self, y, extra_flags: int = 0, out_row_stride=None, y_dest=None, y_col_offset=0):
+        """Call descriptor.  y_dest (a list of [M, out_row_stride] buffers, one per rank) makes the kernel store
+        this shard's columns into every one of them at y_col_offset instead of into `y`."""
         lc = self.local_case
         # scratch: the FP4 activations (when asked for), then the LoRA activation tiles
         ws_bytes = self.ab.lora_ws_bytes(lc.M, lc.max_loras, lc.max_rank)
@@ -79,7 +81,7 @@ class DeviceShard:
         if getattr(self, "_ws", None) is None or self._ws.numel() < ws_bytes:
             self._ws = self.torch.empty(ws_bytes, dtype=self.torch.uint8, device="cuda")
         ws = self._ws
-        return self.ab.make_linear_desc(ws=ws, ws_bytes=ws_bytes,
+        return self.ab.make_linear_desc(ws=ws, ws_bytes=ws_bytes, y_dest=y_dest, y_col_offset=y_col_offset,
             x=self.x, m=lc.M, k=lc.K, n=lc.N, y=y, w_packed=self.packed, w_scale=self.scales, scale2=lc.scale2,
             w_bf16=self.w_bf16, seq_slot=self.seq_slot, route=self.pool.route(), lora_t=self.lora_t,
             flags=extra_flags, out_row_stride=out_row_stride)

@@ -308,6 +308,15 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     p.rank_table = d.rank_table;
     p.t = static_cast<const uint16_t*>(d.lora_t);
     p.y = static_cast<uint16_t*>(d.y);
+    p.n_dest = d.n_dest ? d.n_dest : 1u;
+    p.y_col0 = d.n_dest ? d.y_col_offset : 0u;
+    bool rows_16b = d.out_row_stride % 8 == 0 && p.y_col0 % 8 == 0;
+    for (uint32_t r = 0; r < p.n_dest; ++r) {
+        p.y_dest[r] = static_cast<uint16_t*>(d.n_dest ? d.y_dest[r] : d.y);
+        rows_16b = rows_16b && aligned(p.y_dest[r], 16);
+    }
+    if (d.n_dest && !rows_16b) return ATLAS_B200_ERR_ALIGN;
+    p.staged_epilogue = rows_16b ? 1u : 0u;
     p.M = d.m; p.N = d.n; p.K = d.k; p.out_row_stride = d.out_row_stride;
     p.max_loras = d.max_loras; p.max_rank = d.max_rank;
     p.out_scale = A4 ? d.scale2 : d.scale2 * kWeightPreScale;
@@ -344,7 +353,11 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
 }
 
 static int validate_linear(const atlas_b200_linear_desc& d) {
-    if (!d.x || !d.y) return ATLAS_B200_ERR_NULL;
+    if (!d.x || (!d.y && !d.n_dest)) return ATLAS_B200_ERR_NULL;
+    if (d.n_dest > uint32_t(tc::MAX_DEST)) return ATLAS_B200_ERR_LIMIT;
+    for (uint32_t r = 0; r < d.n_dest; ++r)
+        if (!d.y_dest[r]) return ATLAS_B200_ERR_NULL;
+    if (d.n_dest && uint64_t(d.y_col_offset) + d.n > d.out_row_stride) return ATLAS_B200_ERR_DIMS;
     if (!d.w_bf16 && (!d.w_packed || !d.w_scale)) return ATLAS_B200_ERR_NULL;
     if (d.k == 0 || d.n == 0) return ATLAS_B200_ERR_DIMS;
     if (!d.w_bf16 && d.k % 16 != 0) return ATLAS_B200_ERR_DIMS;   // NVFP4 scale groups are 16 wide
@@ -367,6 +380,7 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
     const bool staged = (d.flags & ATLAS_B200_FLAG_STAGED_LORA) != 0;
     bool use_tc = !(d.flags & ATLAS_B200_FLAG_FORCE_SIMT) && !staged && tc_eligible(d);
     if (!use_tc && (d.flags & ATLAS_B200_FLAG_FORCE_TCGEN05)) return ATLAS_B200_ERR_DIMS;
+    if (!use_tc && d.n_dest) return ATLAS_B200_ERR_DIMS;          // placement into several buffers is the tcgen05 epilogue's
 
     const bool act_fp4 = (d.flags & ATLAS_B200_FLAG_ACT_FP4) != 0;
     if (act_fp4) {

@@ -55,10 +55,12 @@ constexpr int DEQ_GROUPS = 1;
 constexpr int DEQ_WARP0 = 6, DEQ_GROUP_WARPS = 8, DEQ_WARPS = 8 * DEQ_GROUPS, DEQ_THREADS = 32 * DEQ_WARPS;
 constexpr int NUM_THREADS = 32 * (DEQ_WARP0 + DEQ_WARPS);
 constexpr int EPI_WARP0 = 2, EPI_THREADS = 128;
+constexpr int EPI_WARPS = 4 + DEQ_WARPS;   // warps that take part in the epilogue: the list warps and the expansion warps
 constexpr int MAX_LORAS_TC = 4096;
 constexpr int MAX_RANK_TC = 64;
 constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;    // 1 s
 constexpr int PROFILE_WORDS = 16;
+constexpr int MAX_DEST = 8;            // tensor-parallel ranks whose output buffers one launch can store into
 #ifndef MMA_BACKOFF_NS
 #define MMA_BACKOFF_NS 32
 #endif                    // u64 words per CTA in the optional profile buffer
@@ -117,7 +119,7 @@ template <int MT, bool A4 = false, bool PAIR = false> struct Cfg {
     static constexpr int OFF_BITMAP = OFF_GRANB + MAX_GRANULES * 8;              // uint32[128]
     static constexpr int OFF_SCAN = OFF_BITMAP + (MAX_LORAS_TC / 32) * 4;        // uint32[8]
     static constexpr int OFF_BAR = OFF_SCAN + 64;                                // mbarriers
-    static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_STAGES + 3 + 2 * L_STAGES;
+    static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_STAGES + 4 + 2 * L_STAGES;
     static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;                      // tmem ptr, n_gran, abort
     static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;                      // + alignment slack
     static_assert(!PAIR || MT >= 128, "pairs are built for token tiles of 128 and 256");
@@ -132,8 +134,14 @@ struct Params {
     const uint32_t* rank_table;    // nullable
     const uint16_t* t;             // [M, max_rank] pre-scaled shrink result
     uint16_t* y;
+    // Output destinations.  One (y itself) normally.  As one column shard of a tensor-parallel layer the
+    // kernel can store its tile straight into every rank's gathered [M, out_row_stride] buffer, at columns
+    // y_col0 + f: y_dest[r] is rank r's buffer as mapped into this process (peer memory for r != own rank).
+    uint16_t* y_dest[MAX_DEST];
+    uint32_t n_dest, y_col0;
     uint32_t M, N, K, out_row_stride, max_loras, max_rank;
     float out_scale;               // scale2 * 2^8 (A16) or scale2 (A4)
+    uint32_t staged_epilogue;      // destination rows allow 16-byte stores: write the tile out through shared memory
     uint32_t t_tile_cap;           // != 0: the shrink wrote masked-t tiles (ShrinkParams::tile_out) with this many blocks
                                    //       reserved per token tile; they are fetched by TMA (map_t) and `t` is not read
     uint32_t b_pool_strided;       // B_s tiles can be fetched by TMA from a [max_loras][N][max_rank] strided pool
@@ -459,6 +467,60 @@ __device__ __forceinline__ void epilogue_columns(const Params& p, uint32_t tmem_
 // map_x: activations (A16: BF16 [M, K]; A4: packed codes [M, K/2]); map_w / map_s: packed weight codes and
 // their scale bytes; map_b: the strided adapter pool's B side; map_xs: A4 only, activation scale bytes [M, K/16];
 // map_t: the shrink's masked-t blocks as rows of 256 bytes, when p.t_tile_cap != 0.
+// Epilogue through shared memory: the warps first lay the tile down as [token][128 features] BF16 (256-byte
+// rows; the 16-byte chunks of odd rows rotated by four so that the two rows a store instruction touches
+// fall into different banks), meet on an mbarrier, then copy whole rows out with 16-byte stores — to every
+// destination buffer in turn.  `e_tid` = 0 .. 32 * EPI_WARPS - 1 numbers the participating threads.
+// Requires 16-byte aligned destination rows (checked by the caller); returns false if the wait expired.
+template <int MT>
+__device__ __forceinline__ bool epilogue_staged(const Params& p, uint32_t tmem_acc, uint32_t tile, uint32_t bar_epi,
+                                                volatile uint32_t* abort_flag, uint32_t q, uint32_t lane, uint32_t f0,
+                                                uint32_t m0, uint32_t part, uint32_t nparts, uint32_t e_tid) {
+    const float osc = p.out_scale;
+    const bool odd = lane & 1u;
+    const uint32_t fe = (q * 32u + lane) & ~1u;                  // even feature of this lane pair, within the tile
+#pragma unroll 1
+    for (uint32_t c0 = part * 16; c0 < uint32_t(MT); c0 += nparts * 16) {
+        uint32_t v[16];
+        tmem_ld16(tmem_acc + ((q * 32u) << 16) + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float a = __uint_as_float(v[2 * i]) * osc, b = __uint_as_float(v[2 * i + 1]) * osc;
+            const float got = __shfl_xor_sync(0xFFFFFFFFu, odd ? a : b, 1);
+            // even lane: token 2i, features (fe, fe+1); odd lane: token 2i+1, the same two features
+            const uint32_t row = c0 + 2 * i + (odd ? 1u : 0u);
+            const uint32_t w = odd ? pack_bf16x2(got, b) : pack_bf16x2(a, got);
+            const uint32_t chunk = (fe >> 3) ^ ((row & 1u) << 2);
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile + row * 256u + chunk * 16u + (fe & 7u) * 2u), "r"(w) : "memory");
+        }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_epi);
+    if (!mbar_wait(bar_epi, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE)) return false;
+    // rows out: 16 threads per row, one 16-byte chunk (8 features) each
+    const uint32_t j = e_tid & 15u;
+    const uint32_t f = f0 + j * 8u;
+    if (f >= p.N) return true;
+    const bool whole = f + 8u <= p.N;
+    for (uint32_t row = e_tid >> 4; row < uint32_t(MT); row += (32u * EPI_WARPS) >> 4) {
+        const uint32_t m = m0 + row;
+        if (m >= p.M) break;
+        const uint4 val = lds128(tile + row * 256u + ((j ^ ((row & 1u) << 2)) << 4));
+        const size_t at = size_t(m) * p.out_row_stride + p.y_col0 + f;
+        for (uint32_t r = 0; r < p.n_dest; ++r) {
+            uint16_t* dst = p.y_dest[r] + at;
+            if (whole) {
+                *reinterpret_cast<uint4*>(dst) = val;
+            } else {
+                const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
+                for (uint32_t e = 0; f + e < p.N; ++e) dst[e] = uint16_t(w4[e >> 1] >> (16u * (e & 1u)));
+            }
+        }
+    }
+    return true;
+}
+
 template <int MT, bool A4, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
@@ -494,6 +556,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     const uint32_t BAR_LFULL = BAR_LIST + 8;                           // [L_STAGES] LoRA operands -> MMA
     const uint32_t BAR_LEMPTY = BAR_LFULL + 8 * C::L_STAGES;           // [L_STAGES] MMA -> LoRA operand build
     const uint32_t BAR_DRAINED = BAR_LEMPTY + 8 * C::L_STAGES;         // every expansion warp is done with the staging area
+    const uint32_t BAR_EPI = BAR_DRAINED + 8;                          // every epilogue warp has put its part of the tile into shared memory
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + C::OFF_MISC);
     // misc[0] = TMEM base address, misc[1] = granule count, misc[2] = abort flag
     volatile uint32_t* abort_flag = misc + 2;
@@ -524,6 +587,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         mbar_init(BAR_ACC, 1);
         mbar_init(BAR_LIST, 1);
         mbar_init(BAR_DRAINED, DEQ_WARPS);
+        mbar_init(BAR_EPI, EPI_WARPS);
         for (int i = 0; i < C::L_STAGES; ++i) {
             mbar_init(BAR_LFULL + 8 * i, p.t_tile_cap ? 1u : CTAS * DEQ_WARPS + 1);
             mbar_init(BAR_LEMPTY + 8 * i, 1);
@@ -834,7 +898,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         if (mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 512)) {
             const long long t_epi = clock64();
             tcgen05_fence_after();
-            epilogue_columns<MT>(p, tmem_acc, warp & 3u, lane, f0, m0, 0, 1 + DEQ_WARPS / 4);
+            if (p.staged_epilogue) epilogue_staged<MT>(p, tmem_acc, x_tile0, BAR_EPI, abort_flag, warp & 3u, lane, f0, m0, 0, 1 + DEQ_WARPS / 4, te);
+            else epilogue_columns<MT>(p, tmem_acc, warp & 3u, lane, f0, m0, 0, 1 + DEQ_WARPS / 4);
             if (prof && te == 0) prof_row[7] = (unsigned long long)(clock64() - t_epi);
         }
     } else {
@@ -1104,7 +1169,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         // ---- join the epilogue ----
         if (ok && mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 64)) {
             tcgen05_fence_after();
-            epilogue_columns<MT>(p, tmem_acc, q, lane, f0, m0, 1 + ((warp - DEQ_WARP0) >> 2), 1 + DEQ_WARPS / 4);
+            if (p.staged_epilogue) epilogue_staged<MT>(p, tmem_acc, x_tile0, BAR_EPI, abort_flag, q, lane, f0, m0, 1 + ((warp - DEQ_WARP0) >> 2), 1 + DEQ_WARPS / 4, EPI_THREADS + td);
+            else epilogue_columns<MT>(p, tmem_acc, q, lane, f0, m0, 1 + ((warp - DEQ_WARP0) >> 2), 1 + DEQ_WARPS / 4);
         }
     }
 

@@ -162,6 +162,17 @@ typedef struct atlas_b200_linear_desc {
      * NULL / 0: B_s is read through b_table with ordinary loads (any placement, slower). */
     const void*     b_pool_base;
     size_t          b_slot_stride;
+    /* Optional: tensor-parallel output placement (n_dest == 0: the tile goes to `y` and nothing else).
+     * With n_dest = tp >= 1 this call is rank `r`'s column shard (n = N / tp) and stores its [m, n] result
+     * directly into columns [y_col_offset, y_col_offset + n) of every rank's gathered row-major buffer:
+     * y_dest[i] is rank i's [m, out_row_stride] buffer as mapped into THIS process (CUDA IPC / symmetric
+     * memory for i != r), out_row_stride >= N.  The stores replace the all-gather that follows a
+     * column-parallel linear (crates/spark-comm/src/nccl_backend/comm_impl.rs:130-145); the caller still
+     * synchronises the ranks before reading.  `y` is ignored.  Needs the tcgen05 path and 16-byte aligned
+     * rows (buffers 16-byte aligned, out_row_stride and y_col_offset multiples of 8), else -1 / -3. */
+    uint32_t        n_dest;
+    uint32_t        y_col_offset;
+    void*           y_dest[8];
 } atlas_b200_linear_desc;
 
 ATLAS_B200_API int atlas_b200_nvfp4_lora_linear(const atlas_b200_linear_desc* desc, void* stream);

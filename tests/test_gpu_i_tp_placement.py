@@ -1,0 +1,71 @@
+"""Output placement of the tcgen05 epilogue: through shared memory with 16-byte stores, directly, and into the
+gathered buffers of several tensor-parallel ranks (here: several buffers on the one GPU, standing in for peers)."""
+import numpy as np
+import pytest
+
+from gpu_util import DeviceCase, assert_close, bits_from_dev, ideal
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M,K,N", [(16, 256, 128), (100, 512, 200), (256, 256, 264), (300, 512, 384)])
+def test_direct_and_staged_stores_agree(cuda, atlas, oracle, M, K, N):
+    """A row stride that is not a multiple of 8 elements rules out 16-byte stores: same bits either way."""
+    from atlas_b200 import synth
+    case = synth.make_case("place", M=M, K=K, N=N, ranks=[16] * 4, max_rank=16, none_frac=0.2, scale2=0.02, b_std=0.1, seed=M + N)
+    y_staged, _ = DeviceCase(cuda, atlas, case, out_row_stride=N + 8).run(flags=atlas.FLAG_FORCE_TCGEN05)
+    y_direct, _ = DeviceCase(cuda, atlas, case, out_row_stride=N + 3).run(flags=atlas.FLAG_FORCE_TCGEN05)
+    assert np.array_equal(y_staged[:, :N], y_direct[:, :N])
+    assert (y_staged[:, N:] == 0x7FC0).all() and (y_direct[:, N:] == 0x7FC0).all()
+    assert_close(oracle, y_staged[:, :N], ideal(oracle, case), "staged")
+    assert atlas.device_status() == 0
+
+
+@pytest.mark.parametrize("tp", [2, 4])
+@pytest.mark.parametrize("act_fp4", [False, True])
+def test_column_shards_fill_every_ranks_buffer(cuda, atlas, oracle, tp, act_fp4):
+    from atlas_b200 import synth, tp as tpmod
+    M, K, N = 200, 512, 1024
+    case = synth.make_case("tp_place", M=M, K=K, N=N, ranks=[16, 32, 8, 32, 16], max_rank=32, none_frac=0.2,
+                           scale2=0.02, b_std=0.1, seed=tp)
+    mode = atlas.FLAG_FORCE_TCGEN05 | (atlas.FLAG_ACT_FP4 if act_fp4 else 0)
+    # the unsharded layer
+    whole = tpmod.DeviceShard(cuda, atlas, case, 1, 0)
+    y_ref = cuda.empty((M, N), dtype=cuda.bfloat16, device="cuda")
+    atlas.nvfp4_lora_linear(whole.desc(y_ref, extra_flags=mode))
+    # every rank's shard writes its columns into every rank's gathered buffer (row stride wider than N)
+    stride = N + 16
+    bufs = [cuda.full((M, stride), 0x7FC0, dtype=cuda.int16, device="cuda") for _ in range(tp)]
+    for r in range(tp):
+        sh = tpmod.DeviceShard(cuda, atlas, case, tp, r)
+        variant = atlas.nvfp4_lora_linear(sh.desc(None, extra_flags=mode, out_row_stride=stride, y_dest=bufs,
+                                                  y_col_offset=r * sh.n_local))
+        assert variant == atlas.VARIANT_TCGEN05
+    cuda.cuda.synchronize()
+    want = bits_from_dev(y_ref.view(cuda.int16))
+    for b in bufs:
+        got = bits_from_dev(b)
+        assert np.array_equal(got[:, :N], want)
+        assert (got[:, N:] == 0x7FC0).all()
+    assert_close(oracle, want, ideal(oracle, case, act_fp4=act_fp4), "unsharded")
+    assert atlas.device_status() == 0
+
+
+def test_placement_argument_errors(cuda, atlas, oracle):
+    from atlas_b200 import synth, tp as tpmod
+    case = synth.make_case("tp_err", M=32, K=256, N=256, ranks=[8], max_rank=8, seed=2)
+    sh = tpmod.DeviceShard(cuda, atlas, case, 2, 1)
+    bufs = [cuda.zeros((32, 256), dtype=cuda.int16, device="cuda") for _ in range(2)]
+    with pytest.raises(atlas.AtlasError) as e:      # columns beyond the row
+        atlas.nvfp4_lora_linear(sh.desc(None, out_row_stride=256, y_dest=bufs, y_col_offset=192))
+    assert e.value.status == -1
+    with pytest.raises(atlas.AtlasError) as e:      # rows that cannot take 16-byte stores
+        atlas.nvfp4_lora_linear(sh.desc(None, out_row_stride=260, y_dest=bufs, y_col_offset=128))
+    assert e.value.status == -3
+    with pytest.raises(atlas.AtlasError) as e:      # no CUDA-core form
+        atlas.nvfp4_lora_linear(sh.desc(None, extra_flags=atlas.FLAG_FORCE_SIMT, out_row_stride=256, y_dest=bufs, y_col_offset=128))
+    assert e.value.status == -1
+    with pytest.raises(atlas.AtlasError) as e:
+        atlas.nvfp4_lora_linear(sh.desc(None, out_row_stride=256, y_dest=bufs + [None], y_col_offset=128))
+    assert e.value.status == -4
+    cuda.cuda.synchronize()
