@@ -7,7 +7,10 @@ One step = one pass of the layer over one synthetic batch.  The default workload
 configuration 1 (NVFP4 base K=5120 N=17408, 256 tokens, 16 adapters of rank 32, 10 % of the tokens
 adapter-less).  With N > 1 (launched by torch.distributed.run, one rank per GPU) the same layer is
 split column-parallel over the ranks — W, its scales and every B_s by output rows; x and A_s
-replicated — and the shards are collected by one NCCL all-gather: strong scaling.
+replicated: strong scaling.  Every rank's kernel stores its output tiles straight into all ranks' gathered
+[M, N] buffers over NVLink (peer mappings from torch's symmetric memory), so the exchange overlaps the
+compute tile by tile and what remains of the collective is one device-side barrier; `--collective nccl`
+(or a box where the peer mapping cannot be made) runs the layer followed by one NCCL all-gather instead.
 
 Rank 0 prints one JSON line.  `value` is device-timed (CUDA events on the launching stream, L2
 flushed between steps, inputs resident in HBM); `e2e` runs the same call with host buffers, with the
@@ -153,7 +156,7 @@ def workload_config(args, case, tp):
     return {"workload": args.workload, "M": case.M, "K": case.K, "N": case.N, "base": "nvfp4" if case.packed is not None else "bf16",
             "adapters": sum(a is not None for a in case.adapters), "adapters_hit": hit, "max_rank": case.max_rank,
             "adapter_less_rows": int((case.seq_slot < 0).sum()), "activation_mode": "A4 (x quantised to NVFP4)" if getattr(args, "activations", "bf16") == "fp4" else "A16 (exact BF16 x)",
-            "parallelism": f"column-parallel tp{tp} + all-gather" if tp > 1 else "single GPU",
+            "parallelism": (f"column-parallel tp{tp}, " + getattr(args, "collective_used", "all-gather")) if tp > 1 else "single GPU",
             "l2": "flushed between timed steps"}
 
 
@@ -168,6 +171,8 @@ def main():
     ap.add_argument("--workload", default="config1", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="atlas_b200", choices=["atlas_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: fused = the kernel's epilogue stores into every rank's buffer; nccl = all-gather after it")
     ap.add_argument("--activations", default="bf16", choices=["bf16", "fp4"],
                     help="bf16: the layer as specified (exact activations); fp4: the opt-in W4A4 mode as the timed step")
     args = ap.parse_args()
@@ -179,6 +184,8 @@ def main():
         run_reference_arm(args, case)
         return
 
+    # peer mappings without an NVLink multicast object bound to them (plain loads and stores only)
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     import torch
     import atlas_b200 as ab
     ab.lib()                                      # fail loudly when the CUDA library is missing
@@ -204,10 +211,33 @@ def main():
     M, N, K, n_loc = case.M, case.N, case.K, shard.n_local
     y_loc = torch.empty((M, n_loc), dtype=torch.bfloat16, device=dev)
     y_all = torch.empty((tp, M, n_loc), dtype=torch.bfloat16, device=dev) if tp > 1 else None
+    # fused collective: every rank's [M, N] result buffer, mapped into every process
+    y_sym, sym_handle, collective_note = None, None, None
+    if tp > 1 and args.collective == "fused":
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            if hasattr(symm_mem, "enable_symm_mem_for_group"):
+                try:
+                    symm_mem.enable_symm_mem_for_group(dist.group.WORLD.group_name)
+                except Exception:
+                    pass
+            y_sym = symm_mem.empty((M, N), dtype=torch.bfloat16, device=dev)
+            sym_handle = symm_mem.rendezvous(y_sym, dist.group.WORLD)
+            peer_ptrs = [int(p) for p in sym_handle.buffer_ptrs]
+            assert len(peer_ptrs) == tp and all(peer_ptrs)
+        except Exception as e:                     # no peer mapping on this box: the NCCL path still measures the layer
+            collective_note = f"peer mapping unavailable ({type(e).__name__}: {e}); NCCL all-gather used"
+            y_sym, sym_handle = None, None
+        ok = torch.tensor([1 if sym_handle is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            y_sym, sym_handle = None, None
+    fused = sym_handle is not None
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > L2 (126 MB)
     mode = ab.FLAG_ACT_FP4 if args.activations == "fp4" else 0
-    desc = shard.desc(y_loc, extra_flags=mode)
-    desc_main_only = shard.desc(y_loc, extra_flags=mode | ab.FLAG_REUSE_SHRINK)
+    place = dict(y_dest=peer_ptrs, y_col_offset=rank * n_loc, out_row_stride=N) if fused else {}
+    desc = shard.desc(y_loc, extra_flags=mode, **place)
+    desc_main_only = shard.desc(y_loc, extra_flags=mode | ab.FLAG_REUSE_SHRINK, **place)
     # the other activation mode, timed beside the headline as a secondary figure
     other = 0 if mode else ab.FLAG_ACT_FP4
     desc_other = shard.desc(y_loc, extra_flags=other) if case.packed is not None and K % 256 == 0 else None
@@ -215,7 +245,9 @@ def main():
 
     def step():
         v = ab.nvfp4_lora_linear(desc, stream)
-        if tp > 1:
+        if fused:
+            sym_handle.barrier(channel=0)          # every rank's tiles have landed in every buffer
+        elif tp > 1:
             dist.all_gather_into_tensor(y_all.view(tp * M, n_loc), y_loc)
         return v
 
@@ -224,6 +256,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if fused:
+        y_sym.view(torch.int16).fill_(0x7FC0)       # NaN pattern: the warm-up must overwrite all of it
     variant = None
     for _ in range(args.warmup):
         flush.fill_(1)
@@ -234,6 +268,8 @@ def main():
         raise RuntimeError(f"device status word {status:#x} after warm-up")
     if variant != ab.VARIANT_TCGEN05 and case.packed is not None:
         raise RuntimeError("the tcgen05 path did not run for this workload")
+    if fused and not bool(torch.isfinite(y_sym.float()).all()):
+        raise RuntimeError("the gathered buffer still holds unwritten elements after the warm-up")
 
     # ---- device-timed steps ----
     sampler = ClockSampler(local_rank)
@@ -284,7 +320,7 @@ def main():
         shard.seq_slot.copy_(slot_host, non_blocking=True)
         step()
         if rank == 0:
-            y_host.copy_((y_all if tp > 1 else y_loc).view(torch.int16), non_blocking=True)
+            y_host.view(-1).copy_((y_sym if fused else (y_all if tp > 1 else y_loc)).view(torch.int16).view(-1), non_blocking=True)
         barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
     clocks = sampler.stop()
@@ -294,6 +330,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     step_ms, main_ms, e2e_ms, other_ms = [float(v) for v in t.tolist()]
 
+    args.collective_used = "tiles stored into every rank's buffer by the kernel + device barrier" if fused else "NCCL all-gather"
     if rank == 0:
         hbm_gbs, peak_kind = peaks()
         work = algorithmic_work(case)
@@ -319,6 +356,8 @@ def main():
             "gpu_launches": args.steps * (3 if mode else 2) + args.steps * (2 if mode else 1),
             "clocks": clocks,
         }
+        if collective_note:
+            line["collective_note"] = collective_note
         if desc_other is not None:
             line["other_activation_mode"] = {
                 "activations": "bf16" if mode else "fp4", "ms_per_step": other_ms, "value": M / (other_ms * 1e-3),
