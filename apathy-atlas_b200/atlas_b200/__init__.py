@@ -23,7 +23,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libatlas_b200.so")
 
 VARIANT_NONE, VARIANT_SIMT, VARIANT_TCGEN05 = 0, 1, 2
-FLAG_FORCE_SIMT, FLAG_FORCE_TCGEN05, FLAG_STAGED_LORA, FLAG_REUSE_SHRINK, FLAG_ACT_FP4, FLAG_NO_CTA_PAIR = 1, 2, 4, 8, 16, 32
+FLAG_FORCE_SIMT, FLAG_FORCE_TCGEN05, FLAG_STAGED_LORA, FLAG_REUSE_SHRINK, FLAG_ACT_FP4, FLAG_NO_CTA_PAIR, FLAG_NO_K_SPLIT = 1, 2, 4, 8, 16, 32, 64
 
 
 def lora_ws_bytes(m: int, max_loras: int, max_rank: int) -> int:
@@ -43,7 +43,8 @@ EXPORTS = (
     "atlas_b200_build_seq_slot", "atlas_b200_routed_prefill_slot_of", "atlas_b200_peft_scaling",
     "atlas_b200_module_dims", "atlas_b200_pool_slot_bytes", "atlas_b200_slot_base_offset",
     "atlas_b200_module_slot_offsets", "atlas_b200_pack_module", "atlas_b200_select_victim_slot",
-    "atlas_b200_device_status", "atlas_b200_last_variant", "atlas_b200_set_profile_buffer", "atlas_b200_version",
+    "atlas_b200_device_status", "atlas_b200_last_variant", "atlas_b200_last_launch_shape", "atlas_b200_set_profile_buffer",
+    "atlas_b200_version",
 )
 
 
@@ -294,6 +295,13 @@ def nvfp4_lora_linear_noalloc(desc: LinearDesc, stream=None) -> int:
     _check("atlas_b200_nvfp4_lora_linear_noalloc",
            lib().atlas_b200_nvfp4_lora_linear_noalloc(C.byref(desc), _stream_ptr(stream)))
     return lib().atlas_b200_last_variant()
+
+
+def last_launch_shape() -> dict:
+    """Token tile, pairing, K split and LoRA-tile source of this thread's most recent tcgen05 launch."""
+    out = (C.c_uint32 * 4)()
+    _check("atlas_b200_last_launch_shape", lib().atlas_b200_last_launch_shape(out))
+    return {"token_tile": out[0], "cta_pair": bool(out[1]), "k_split": out[2], "lora_tiles_from_shrink": bool(out[3])}
 
 
 def device_status(clear: bool = True) -> int:

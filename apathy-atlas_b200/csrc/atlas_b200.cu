@@ -25,6 +25,7 @@
 namespace atlas {
 
 static thread_local int t_last_variant = ATLAS_B200_VARIANT_NONE;
+static thread_local uint32_t t_last_shape[4] = {0, 0, 0, 0};
 static unsigned long long* g_profile_buf = nullptr;   // device buffer for per-CTA cycle counters (diagnostics)
 static size_t g_profile_words = 0;
 
@@ -244,7 +245,8 @@ struct TTiles {
 };
 
 template <int MT, bool A4, bool PAIR>
-static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_shrink, const TTiles& tt, cudaStream_t st) {
+static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_shrink, const TTiles& tt, uint32_t k_split,
+                     cudaStream_t st) {
     using C = tc::Cfg<MT, A4, PAIR>;
     Runtime& rt = runtime();
     slot_idx += (A4 ? 5 : 0) + (PAIR ? 10 : 0);
@@ -322,6 +324,39 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     p.out_scale = A4 ? d.scale2 : d.scale2 * kWeightPreScale;
     dim3 grid((d.n + tc::FT - 1) / tc::FT, (d.m + MT - 1) / MT);
     if (PAIR) grid.x = (grid.x + 1u) & ~1u;      // whole pairs: a CTA past the last feature loads zeros and stores nothing
+    // split K: k_split CTAs along z form a cluster (times two for pairs), share one tile and exchange partial sums;
+    // the receive area is ceil(chunks / k_split) 8 KB blocks from each of them
+    if (k_split > 1 && (k_split * (PAIR ? 2u : 1u) > 8u ||
+                        size_t(k_split) * ((MT / 16 + k_split - 1) / k_split) * 8192 > size_t(C::STAGING_BYTES)))
+        return ATLAS_B200_ERR_LIMIT;
+    // Only as many CTAs per tile as still lets every cluster be resident at once: clusters live inside one GPC, so
+    // fewer of them fit than the SM count suggests, and a second wave would cost more than the split saves.
+    // (An occupancy query per launch shape, answered by the runtime without touching the device; cached.)
+    static int active_clusters[20][9] = {};          // [kernel instance][k_split], 0 = not asked yet, -1 = query failed
+    while (k_split > 1) {
+        int& known = active_clusters[slot_idx][k_split];
+        if (known == 0) {
+            cudaLaunchConfig_t q{};
+            q.gridDim = dim3(grid.x, grid.y, k_split);
+            q.blockDim = dim3(tc::NUM_THREADS);
+            q.dynamicSmemBytes = C::SMEM_BYTES;
+            cudaLaunchAttribute qa[1];
+            qa[0].id = cudaLaunchAttributeClusterDimension;
+            qa[0].val.clusterDim.x = PAIR ? 2 : 1;
+            qa[0].val.clusterDim.y = 1;
+            qa[0].val.clusterDim.z = k_split;
+            q.attrs = qa;
+            q.numAttrs = 1;
+            int n = 0;
+            known = cudaOccupancyMaxActiveClusters(&n, tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>, &q) == cudaSuccess && n > 0 ? n : -1;
+            (void)cudaGetLastError();
+        }
+        if (known > 0 && size_t(grid.x / (PAIR ? 2 : 1)) * grid.y <= size_t(known)) break;
+        --k_split;
+    }
+    grid.z = k_split;
+    p.k_split = k_split;
+    t_last_shape[0] = MT; t_last_shape[1] = PAIR ? 1u : 0u; t_last_shape[2] = k_split; t_last_shape[3] = tt.tiles ? 1u : 0u;
     p.profile = (g_profile_buf && size_t(grid.x) * grid.y * tc::PROFILE_WORDS <= g_profile_words) ? g_profile_buf : nullptr;
     if (grid.y > 65535) return ATLAS_B200_ERR_LIMIT;
     // Launched as a programmatic dependent of the shrink that precedes it in the stream: its CTAs
@@ -334,11 +369,11 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     unsigned n_attr = 0;
-    if (PAIR) {
+    if (PAIR || k_split > 1) {
         attr[n_attr].id = cudaLaunchAttributeClusterDimension;
-        attr[n_attr].val.clusterDim.x = 2;
+        attr[n_attr].val.clusterDim.x = PAIR ? 2 : 1;
         attr[n_attr].val.clusterDim.y = 1;
-        attr[n_attr].val.clusterDim.z = 1;
+        attr[n_attr].val.clusterDim.z = k_split;
         ++n_attr;
     }
     if (after_shrink) {
@@ -405,7 +440,18 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
         uint32_t mt = 16;
         while (mt < 256 && mt < d.m) mt <<= 1;
         const uint32_t f_tiles = (d.n + tc::FT - 1) / tc::FT;
-        while (mt > 64 && f_tiles * ((d.m + mt - 1) / mt) * 4 < uint32_t(rt_sm_count()) * 3) mt >>= 1;
+        // Fewer tiles than half the SMs (a decode batch, a column shard): several CTAs share a tile, each
+        // contracting a share of K, rather than leaving SMs idle — a CTA's time is set by the weights it has
+        // to expand, which only a K split divides.  Clusters of at most 8 CTAs; whole 256-element stages.
+        uint32_t k_split = 1;
+        if (!(d.flags & ATLAS_B200_FLAG_NO_K_SPLIT)) {
+            const bool pair_here = mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR);
+            const uint32_t tiles = f_tiles * ((d.m + mt - 1) / mt);
+            const uint32_t fit = uint32_t(rt_sm_count()) / tiles;
+            k_split = std::max(1u, std::min(std::min(fit, pair_here ? 4u : 8u), d.k / uint32_t(tc::KRAW)));
+        }
+        if (k_split == 1)
+            while (mt > 64 && f_tiles * ((d.m + mt - 1) / mt) * 4 < uint32_t(rt_sm_count()) * 3) mt >>= 1;
 
         ShrinkParams sp{};
         sp.x = static_cast<const uint16_t*>(d.x);
@@ -447,16 +493,16 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
         // 128 and 256 tokens: pairs of CTAs issue their MMAs together (see tc::Cfg)
         const bool pair = mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR);
         if (act_fp4) {
-            if (mt == 16) rc = launch_tc<16, true, false>(d, 0, after_shrink, tt, st);
-            else if (mt == 32) rc = launch_tc<32, true, false>(d, 1, after_shrink, tt, st);
-            else if (mt == 64) rc = launch_tc<64, true, false>(d, 2, after_shrink, tt, st);
-            else if (mt == 128) rc = pair ? launch_tc<128, true, true>(d, 3, after_shrink, tt, st) : launch_tc<128, true, false>(d, 3, after_shrink, tt, st);
-            else rc = pair ? launch_tc<256, true, true>(d, 4, after_shrink, tt, st) : launch_tc<256, true, false>(d, 4, after_shrink, tt, st);
-        } else if (mt == 16) rc = launch_tc<16, false, false>(d, 0, after_shrink, tt, st);
-        else if (mt == 32) rc = launch_tc<32, false, false>(d, 1, after_shrink, tt, st);
-        else if (mt == 64) rc = launch_tc<64, false, false>(d, 2, after_shrink, tt, st);
-        else if (mt == 128) rc = pair ? launch_tc<128, false, true>(d, 3, after_shrink, tt, st) : launch_tc<128, false, false>(d, 3, after_shrink, tt, st);
-        else rc = pair ? launch_tc<256, false, true>(d, 4, after_shrink, tt, st) : launch_tc<256, false, false>(d, 4, after_shrink, tt, st);
+            if (mt == 16) rc = launch_tc<16, true, false>(d, 0, after_shrink, tt, k_split, st);
+            else if (mt == 32) rc = launch_tc<32, true, false>(d, 1, after_shrink, tt, k_split, st);
+            else if (mt == 64) rc = launch_tc<64, true, false>(d, 2, after_shrink, tt, k_split, st);
+            else if (mt == 128) rc = pair ? launch_tc<128, true, true>(d, 3, after_shrink, tt, k_split, st) : launch_tc<128, true, false>(d, 3, after_shrink, tt, k_split, st);
+            else rc = pair ? launch_tc<256, true, true>(d, 4, after_shrink, tt, k_split, st) : launch_tc<256, true, false>(d, 4, after_shrink, tt, k_split, st);
+        } else if (mt == 16) rc = launch_tc<16, false, false>(d, 0, after_shrink, tt, k_split, st);
+        else if (mt == 32) rc = launch_tc<32, false, false>(d, 1, after_shrink, tt, k_split, st);
+        else if (mt == 64) rc = launch_tc<64, false, false>(d, 2, after_shrink, tt, k_split, st);
+        else if (mt == 128) rc = pair ? launch_tc<128, false, true>(d, 3, after_shrink, tt, k_split, st) : launch_tc<128, false, false>(d, 3, after_shrink, tt, k_split, st);
+        else rc = pair ? launch_tc<256, false, true>(d, 4, after_shrink, tt, k_split, st) : launch_tc<256, false, false>(d, 4, after_shrink, tt, k_split, st);
         if (rc == ATLAS_B200_OK) t_last_variant = ATLAS_B200_VARIANT_TCGEN05;
         return rc;
     }
@@ -626,6 +672,12 @@ int atlas_b200_device_status(uint32_t* out_word, int clear) {
 }
 
 int atlas_b200_last_variant(void) { return t_last_variant; }
+
+int atlas_b200_last_launch_shape(uint32_t out[4]) {
+    if (!out) return ATLAS_B200_ERR_NULL;
+    for (int i = 0; i < 4; ++i) out[i] = t_last_shape[i];
+    return ATLAS_B200_OK;
+}
 
 int atlas_b200_set_profile_buffer(void* device_buffer, size_t n_words) {
     g_profile_buf = static_cast<unsigned long long*>(device_buffer);

@@ -141,6 +141,9 @@ struct Params {
     uint32_t n_dest, y_col0;
     uint32_t M, N, K, out_row_stride, max_loras, max_rank;
     float out_scale;               // scale2 * 2^8 (A16) or scale2 (A4)
+    uint32_t k_split;              // >= 1: CTAs (clusters along grid z) that share one output tile, each contracting a
+                                   //       share of K and of the LoRA K blocks; partial tiles are summed over
+                                   //       distributed shared memory
     uint32_t staged_epilogue;      // destination rows allow 16-byte stores: write the tile out through shared memory
     uint32_t t_tile_cap;           // != 0: the shrink wrote masked-t tiles (ShrinkParams::tile_out) with this many blocks
                                    //       reserved per token tile; they are fetched by TMA (map_t) and `t` is not read
@@ -361,9 +364,9 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 // When every MMA issued so far has completed, arrive on mbarrier `bar`; the pair form arrives on the
 // barrier at that shared-memory offset in BOTH CTAs of the pair.
 template <bool PAIR = false>
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
+__device__ __forceinline__ void umma_commit(uint32_t bar, uint32_t pair_mask = 3u) {
     if constexpr (PAIR) {
-        const uint16_t both = 3;
+        const uint16_t both = uint16_t(pair_mask);     // the pair's two ranks within the cluster
         asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                      ::"r"(bar), "h"(both) : "memory");
     } else {
@@ -521,6 +524,61 @@ __device__ __forceinline__ bool epilogue_staged(const Params& p, uint32_t tmem_a
     return true;
 }
 
+// Split-K epilogue, first half: this CTA's partial tile goes, 16 token columns at a time, to the CTA of the
+// cluster that owns those columns (chunk c belongs to CTA c % ks), as raw FP32 accumulators into that CTA's
+// receive area [source CTA][its chunk][column][128 features] at the start of its staging memory.
+template <int MT>
+__device__ __forceinline__ void split_send(uint32_t tmem_acc, uint32_t recv0, uint32_t ks, uint32_t kz, uint32_t cta_rank,
+                                           uint32_t ctas, uint32_t q, uint32_t lane, uint32_t part, uint32_t nparts) {
+    const uint32_t lc_n = (uint32_t(MT) / 16u + ks - 1u) / ks;          // chunks an owner can hold per source
+    for (uint32_t c = part; c < uint32_t(MT) / 16u; c += nparts) {
+        uint32_t v[16];
+        tmem_ld16(tmem_acc + ((q * 32u) << 16) + c * 16u, v);
+        tmem_ld_wait();
+        const uint32_t owner = c % ks, lc = c / ks;
+        const uint32_t dst = map_to_cta(recv0 + (((kz * lc_n + lc) * 16u) * 128u + q * 32u + lane) * 4u, cta_rank + ctas * owner);
+#pragma unroll
+        for (uint32_t i = 0; i < 16; ++i)
+            asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(dst + i * 512u), "r"(v[i]) : "memory");
+    }
+}
+
+// Second half: the owner adds the ks partial tiles of its columns in source order, scales, converts and stores.
+template <int MT>
+__device__ __forceinline__ void split_reduce_store(const Params& p, uint32_t recv0, uint32_t ks, uint32_t kz, uint32_t f0,
+                                                   uint32_t m0, uint32_t e_tid) {
+    const uint32_t lc_n = (uint32_t(MT) / 16u + ks - 1u) / ks;
+    const uint32_t n_chunks = uint32_t(MT) / 16u;
+    const uint32_t mine = n_chunks > kz ? (n_chunks - kz + ks - 1u) / ks : 0u;      // chunks kz, kz + ks, ...
+    const float osc = p.out_scale;
+    for (uint32_t unit = e_tid; unit < mine * 256u; unit += 32u * EPI_WARPS) {
+        const uint32_t j = unit & 15u, i = (unit >> 4) & 15u, lc = unit >> 8;
+        const uint32_t m = m0 + (lc * ks + kz) * 16u + i, f = f0 + j * 8u;
+        if (m >= p.M || f >= p.N) continue;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (uint32_t z = 0; z < ks; ++z) {
+            const uint32_t at = recv0 + ((((z * lc_n + lc) * 16u + i) * 128u) + j * 8u) * 4u;
+            const uint4 a = lds128(at), b = lds128(at + 16u);
+            acc[0] += __uint_as_float(a.x); acc[1] += __uint_as_float(a.y); acc[2] += __uint_as_float(a.z); acc[3] += __uint_as_float(a.w);
+            acc[4] += __uint_as_float(b.x); acc[5] += __uint_as_float(b.y); acc[6] += __uint_as_float(b.z); acc[7] += __uint_as_float(b.w);
+        }
+        uint4 val;
+        val.x = pack_bf16x2(acc[0] * osc, acc[1] * osc); val.y = pack_bf16x2(acc[2] * osc, acc[3] * osc);
+        val.z = pack_bf16x2(acc[4] * osc, acc[5] * osc); val.w = pack_bf16x2(acc[6] * osc, acc[7] * osc);
+        const size_t at = size_t(m) * p.out_row_stride + p.y_col0 + f;
+        const bool whole = p.staged_epilogue && f + 8u <= p.N;
+        for (uint32_t r = 0; r < p.n_dest; ++r) {
+            uint16_t* dst = p.y_dest[r] + at;
+            if (whole) {
+                *reinterpret_cast<uint4*>(dst) = val;
+            } else {
+                const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
+                for (uint32_t e = 0; e < 8u && f + e < p.N; ++e) dst[e] = uint16_t(w4[e >> 1] >> (16u * (e & 1u)));
+            }
+        }
+    }
+}
+
 template <int MT, bool A4, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
@@ -562,14 +620,23 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     volatile uint32_t* abort_flag = misc + 2;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    bool acc_ready = false;                              // split K: this warp saw the accumulator complete
     const uint32_t f0 = blockIdx.x * FT;
     const uint32_t m0 = blockIdx.y * MT;
-    // a pair = the two CTAs of a cluster (neighbouring feature tiles); its first CTA issues the MMAs for both
-    const uint32_t cta_rank = PAIR ? cluster_cta_rank() : 0u;
+    constexpr uint32_t CTAS = PAIR ? 2u : 1u;
+    const uint32_t ks = p.k_split, kz = blockIdx.z;      // split K: CTAs per output tile, and which of them this is
+    // a pair = two CTAs with neighbouring feature tiles (x and x + 1 in a cluster); its first CTA issues the MMAs for both
+    const uint32_t cta_rank = PAIR ? (blockIdx.x & 1u) : 0u;
+    const uint32_t leader_rank = CTAS * kz;              // rank, within the cluster, of this pair's first CTA
+    const uint32_t pair_mask = 3u << (2u * kz);
     const bool leader = cta_rank == 0u;
     const uint32_t mx0 = m0 + cta_rank * C::XROWS;       // first token row whose activations this CTA stages
-    constexpr uint32_t CTAS = PAIR ? 2u : 1u;
-    const uint32_t num_kb = A4 ? p.K / KRAW : (p.K + KB - 1) / KB;     // pipeline steps of the base K loop
+    // This CTA's share of the contraction (all of it unless p.k_split > 1): whole raw stages of 256 K elements.
+    const uint32_t total_kb = A4 ? p.K / KRAW : (p.K + KB - 1) / KB;
+    const uint32_t total_raw = A4 ? total_kb : (total_kb + 3u) / 4u;
+    const uint32_t raw_lo = kz * total_raw / ks, raw_hi = (kz + 1u) * total_raw / ks;
+    const uint32_t kb_lo = A4 ? raw_lo : 4u * raw_lo;
+    const uint32_t num_kb = (A4 ? raw_hi : min(4u * raw_hi, total_kb)) - kb_lo;      // pipeline steps of the base K loop
     const bool prof = p.profile != nullptr;
     const long long t_entry = clock64();
     const uint64_t t_entry_ns = prof ? global_timer_ns() : 0;
@@ -614,8 +681,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
     tcgen05_fence_after();
     // barriers the MMA thread waits on live in the pair's first CTA; everyone else arrives there
-    const uint32_t full_at_leader = PAIR ? map_to_cta(BAR_FULL, 0u) : BAR_FULL;
-    const uint32_t lfull_at_leader = PAIR ? map_to_cta(BAR_LFULL, 0u) : BAR_LFULL;
+    const uint32_t full_at_leader = PAIR ? map_to_cta(BAR_FULL, leader_rank) : BAR_FULL;
+    const uint32_t lfull_at_leader = PAIR ? map_to_cta(BAR_LFULL, leader_rank) : BAR_LFULL;
     auto arrive_at_leader = [&](uint32_t bar_at_leader) {
         if constexpr (PAIR) mbar_arrive_cluster(bar_at_leader); else mbar_arrive(bar_at_leader);
     };
@@ -633,7 +700,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             for (uint32_t it = 0; it < num_kb; ++it) {
                 if (!mbar_wait(BAR_EMPTY + 8 * s, ph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER, 32)) break;
                 const uint32_t st = smem_base + s * C::S4_BYTES;
-                const uint32_t kk = (it + rot) % num_kb;
+                const uint32_t kk = kb_lo + (it + rot) % num_kb;
                 mbar_arrive_expect_tx(BAR_FULL_RAW + 8 * s, RAW_SCALE_BYTES + MT * 16);
                 tma_load_2d(st + C::S4_WS, &map_s, int32_t(kk * (KRAW / 16)), int32_t(f0), BAR_FULL_RAW + 8 * s);
                 tma_load_2d(st + C::S4_XS, &map_xs, int32_t(kk * (KRAW / 16)), int32_t(m0), BAR_FULL_RAW + 8 * s);
@@ -664,7 +731,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     const uint32_t rs = ri % C::RAW_STAGES, rph = (ri / C::RAW_STAGES) & 1u;
                     if (mbar_try_wait(BAR_EMPTY_RAW + 8 * rs, rph ^ 1u)) {
                         mbar_arrive_expect_tx(BAR_FULL_RAW + 8 * rs, RAW_PACKED_BYTES + RAW_SCALE_BYTES);
-                        const uint32_t rk = (ri + rot_raw) % num_raw;
+                        const uint32_t rk = raw_lo + (ri + rot_raw) % num_raw;
                         tma_load_2d(rawp0 + rs * RAW_PACKED_BYTES, &map_w, int32_t(rk * (KRAW / 2)), int32_t(f0), BAR_FULL_RAW + 8 * rs);
                         tma_load_2d(raws0 + rs * RAW_SCALE_BYTES, &map_s, int32_t(rk * (KRAW / 16)), int32_t(f0), BAR_FULL_RAW + 8 * rs);
                         ++ri;
@@ -675,7 +742,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
                     if (mbar_try_wait(BAR_EMPTY + 8 * s, ph ^ 1u)) {
                         if (leader) mbar_arrive_expect_tx(BAR_FULL + 8 * s, CTAS * C::X_TILE_BYTES);
-                        const uint32_t kb = (it + 4u * rot_raw) % num_kb;
+                        const uint32_t kb = kb_lo + (it + 4u * rot_raw) % num_kb;
                         if constexpr (PAIR) tma_load_2d_pair(x_tile0 + s * C::X_TILE_BYTES, &map_x, int32_t(kb * KB), int32_t(mx0), full_at_leader + 8 * s);
                         else tma_load_2d(x_tile0 + s * C::X_TILE_BYTES, &map_x, int32_t(kb * KB), int32_t(m0), BAR_FULL + 8 * s);
                         ++it;
@@ -712,7 +779,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     // this CTA's blocks: [XROWS x 16] BF16 images, C::L_GRAN_T bytes each, consecutive in list order
                     const uint32_t t_row0 = (blockIdx.y * CTAS + cta_rank) * p.t_tile_cap * uint32_t(C::L_GRAN_T / 256);
                     uint32_t ls = 0, lph = 0;
-                    for (uint32_t g0 = 0; g0 < n_gran; g0 += 4) {
+                    for (uint32_t g0 = 4 * kz; g0 < n_gran; g0 += 4 * ks) {      // this CTA's share of the LoRA K blocks
                         if (!mbar_wait(BAR_LEMPTY + 8 * ls, lph ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER)) break;
                         const uint32_t ng = min(4u, n_gran - g0);
                         const uint32_t base = x_tile0 + ls * C::L_BLOCK;
@@ -762,7 +829,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i)   // 64 k = 32 bytes along the swizzled 128-byte row
                         umma_nvfp4_ss<PAIR>(tmem_acc, wa + 2 * i, xb + 2 * i, idesc4, sf + 4 * i, sf + 16 + 4 * C::XSF_BLOCKS * i, acc | i);
-                    umma_commit<PAIR>(bar_empty);
+                    umma_commit<PAIR>(bar_empty, pair_mask);
                     acc = 1u;
                     bar_full += 8; bar_empty += 8; st += C::S4_BYTES; sf += C::SF_COLS;
                     if (++s == uint32_t(C::STAGES)) { s = 0; ph ^= 1u; bar_full = BAR_FULL; bar_empty = BAR_EMPTY; st = smem_base; sf = tmem_a0; }
@@ -788,7 +855,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 ready = mbar_try_wait(n_full, n_ph);
                 umma_bf16_ts<PAIR>(tmem_acc, a_tmem + 16, b_desc + 4, idesc, 1u);
                 umma_bf16_ts<PAIR>(tmem_acc, a_tmem + 24, b_desc + 6, idesc, 1u);
-                umma_commit<PAIR>(bar_empty);
+                umma_commit<PAIR>(bar_empty, pair_mask);
                 acc = 1u;
                 bar_full = n_full; bar_empty = n_empty; a_tmem = n_a; b_desc = n_b; ph = n_ph;
             }
@@ -800,7 +867,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 // LoRA K blocks: both operands are shared-memory tiles in their own ring
                 const uint32_t n_gran = misc[1];
                 uint32_t ls = 0, lph = 0;
-                for (uint32_t g0 = 0; g0 < n_gran; g0 += 4) {
+                for (uint32_t g0 = 4 * kz; g0 < n_gran; g0 += 4 * ks) {
                     ok = mbar_wait_timed(BAR_LFULL + 8 * ls, lph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full, MMA_BACKOFF_NS);
                     if (!ok) break;
                     tcgen05_fence_after();
@@ -809,11 +876,11 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     const uint64_t lb_ = make_kmajor_sw32_desc(x_tile0 + ls * C::L_BLOCK + C::L_TILE_A);
                     for (uint32_t k = 0; k < ksteps; ++k)   // one granule = one 16-wide K step with its own pair of tiles
                         umma_bf16_ss<PAIR>(tmem_acc, la + k * (C::L_GRAN_A >> 4), lb_ + k * (C::L_GRAN_T >> 4), idesc, 1u);
-                    umma_commit<PAIR>(BAR_LEMPTY + 8 * ls);
+                    umma_commit<PAIR>(BAR_LEMPTY + 8 * ls, pair_mask);
                     if (++ls == uint32_t(C::L_STAGES)) { ls = 0; lph ^= 1u; }
                 }
             }
-            if (ok) umma_commit<PAIR>(BAR_ACC);
+            if (ok) umma_commit<PAIR>(BAR_ACC, pair_mask);
             if (prof) { prof_row[0] = w_full + ((unsigned long long)(t_begin - t_entry) << 32); prof_row[2] = (unsigned long long)(clock64() - t_begin); }
         }
         __syncwarp();
@@ -898,7 +965,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         if (mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 512)) {
             const long long t_epi = clock64();
             tcgen05_fence_after();
-            if (p.staged_epilogue) epilogue_staged<MT>(p, tmem_acc, x_tile0, BAR_EPI, abort_flag, warp & 3u, lane, f0, m0, 0, 1 + DEQ_WARPS / 4, te);
+            if (ks > 1) acc_ready = true;                   // split K: the tile is finished by the whole cluster, below
+            else if (p.staged_epilogue) epilogue_staged<MT>(p, tmem_acc, x_tile0, BAR_EPI, abort_flag, warp & 3u, lane, f0, m0, 0, 1 + DEQ_WARPS / 4, te);
             else epilogue_columns<MT>(p, tmem_acc, warp & 3u, lane, f0, m0, 0, 1 + DEQ_WARPS / 4);
             if (prof && te == 0) prof_row[7] = (unsigned long long)(clock64() - t_epi);
         }
@@ -1134,7 +1202,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     for (int32_t g = 0; g < 4; ++g) {
                         const uint32_t k = uint32_t(d + g);
                         if (k < t_ng[u]) cp_async_16_zfill(base + g * C::L_GRAN_T + t_dst[u], t_src[u] + 16 * k, 16u);
-                        else if (uint32_t(d + g - 4 * C::L_STAGES) < t_ng[u]) sts128(base + g * C::L_GRAN_T + t_dst[u], 0u, 0u, 0u, 0u);
+                        else if (uint32_t(d + g - 4 * C::L_STAGES * int32_t(ks)) < t_ng[u]) sts128(base + g * C::L_GRAN_T + t_dst[u], 0u, 0u, 0u, 0u);
                     }
                 }
                 if (++ls == uint32_t(C::L_STAGES)) { ls = 0; lph ^= 1u; }
@@ -1143,14 +1211,15 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             };
             // one cp.async group per block, issued L_STAGES - 1 blocks ahead (empty groups past the end
             // keep "group index == block index")
+            // (this CTA's blocks are kz, kz + ks, ...: local block i is block kz + i * ks of the tile)
             for (uint32_t i = 0; ok && i + 1 < uint32_t(C::L_STAGES); ++i) {
-                if (i < n_lb) ok = issue_block(i);
+                if (kz + i * ks < n_lb) ok = issue_block(kz + i * ks);
                 cp_async_commit();
             }
             // Hand block lb over first, refill afterwards: the refill waits for the MMA to release a
             // stage, and must not stand between finished copies and the MMA that is waiting for them.
             uint32_t cs = 0;
-            for (uint32_t lb = 0; ok && lb < n_lb; ++lb) {
+            for (uint32_t i = 0; ok && kz + i * ks < n_lb; ++i) {
                 const long long t_g0 = prof ? clock64() : 0;
                 cp_async_wait_group<C::L_STAGES - 2>();      // groups 0 .. lb + L_STAGES - 2 are committed: lb is done
                 if (prof) w_group += (unsigned long long)(clock64() - t_g0);
@@ -1158,7 +1227,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 __syncwarp();
                 if (lane == 0) arrive_at_leader(lfull_at_leader + 8 * cs);
                 if (++cs == uint32_t(C::L_STAGES)) cs = 0;
-                if (lb + C::L_STAGES - 1 < n_lb) ok = issue_block(lb + C::L_STAGES - 1);
+                if (kz + (i + C::L_STAGES - 1) * ks < n_lb) ok = issue_block(kz + (i + C::L_STAGES - 1) * ks);
                 cp_async_commit();
             }
             cp_async_wait_group<0>();
@@ -1169,9 +1238,25 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         // ---- join the epilogue ----
         if (ok && mbar_wait(BAR_ACC, 0, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 64)) {
             tcgen05_fence_after();
-            if (p.staged_epilogue) epilogue_staged<MT>(p, tmem_acc, x_tile0, BAR_EPI, abort_flag, q, lane, f0, m0, 1 + ((warp - DEQ_WARP0) >> 2), 1 + DEQ_WARPS / 4, EPI_THREADS + td);
+            if (ks > 1) acc_ready = true;
+            else if (p.staged_epilogue) epilogue_staged<MT>(p, tmem_acc, x_tile0, BAR_EPI, abort_flag, q, lane, f0, m0, 1 + ((warp - DEQ_WARP0) >> 2), 1 + DEQ_WARPS / 4, EPI_THREADS + td);
             else epilogue_columns<MT>(p, tmem_acc, q, lane, f0, m0, 1 + ((warp - DEQ_WARP0) >> 2), 1 + DEQ_WARPS / 4);
         }
+    }
+
+    // ================================ split K: the cluster finishes the tile =================================
+    if (ks > 1) {
+        tcgen05_fence_before();
+        __syncwarp();
+        cluster_sync_all();                                  // every CTA's MMAs are done: staging areas may receive
+        tcgen05_fence_after();
+        if (warp >= EPI_WARP0) {
+            const uint32_t part = warp < DEQ_WARP0 ? 0u : 1u + ((warp - DEQ_WARP0) >> 2);
+            if (acc_ready) split_send<MT>(tmem_acc, x_tile0, ks, kz, cta_rank, CTAS, warp & 3u, lane, part, 1 + DEQ_WARPS / 4);
+        }
+        __syncwarp();
+        cluster_sync_all();                                  // all partial tiles have arrived
+        if (warp >= EPI_WARP0 && acc_ready) split_reduce_store<MT>(p, x_tile0, ks, kz, f0, m0, tid - EPI_WARP0 * 32);
     }
 
     // ========================================= teardown ==========================================

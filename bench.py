@@ -263,6 +263,7 @@ def main():
         flush.fill_(1)
         variant = step()
     barrier()
+    launch_shape = ab.last_launch_shape()
     status = ab.device_status()
     if status != 0:
         raise RuntimeError(f"device status word {status:#x} after warm-up")
@@ -353,6 +354,7 @@ def main():
             "e2e": {"value": M / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": int(x_host.numel() * 2 + slot_host.numel() * 4),
                     "d2h_bytes_per_step": int(y_host.numel() * 2), "ms_per_step": e2e_ms},
+            "launch_shape": launch_shape,
             "gpu_launches": args.steps * (3 if mode else 2) + args.steps * (2 if mode else 1),
             "clocks": clocks,
         }

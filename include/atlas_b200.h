@@ -70,6 +70,7 @@ extern "C" {
 #define ATLAS_B200_LORA_WS_BYTES(m, max_loras, max_rank) \
     ((((size_t)(m) + 255) / 256) * 256 * ((max_loras) < 256 ? (max_loras) : 256) * (((size_t)(max_rank) + 15) / 16) * 32)
 #define ATLAS_B200_FLAG_NO_CTA_PAIR   32u   /* tcgen05 path: keep every CTA on its own (no two-CTA MMAs); for comparison runs */
+#define ATLAS_B200_FLAG_NO_K_SPLIT    64u   /* tcgen05 path: one CTA per output tile even when that leaves SMs idle; for comparison runs */
 #define ATLAS_B200_ACT_FP4_WS_BYTES(m, k) \
     ((((size_t)(m) * ((k) / 2) + 255) / 256) * 256 + (size_t)(m) * ((k) / 16))
 
@@ -245,6 +246,10 @@ ATLAS_B200_API int atlas_b200_select_victim_slot(const size_t* slot_index, const
 ATLAS_B200_API int atlas_b200_device_status(uint32_t* out_word, int clear);
 /* Kernel family chosen by the most recent fused / base call on this thread. */
 ATLAS_B200_API int atlas_b200_last_variant(void);
+/* Launch shape of the most recent tcgen05 call on this thread (launcher audit, no counterpart in the reference):
+ * out[0] = token tile, out[1] = 1 if CTAs were paired for two-CTA MMAs, out[2] = CTAs per output tile (K split),
+ * out[3] = 1 if the LoRA activation tiles came from the shrink through `ws`. */
+ATLAS_B200_API int atlas_b200_last_launch_shape(uint32_t out[4]);
 /* Per-CTA cycle counters of the tcgen05 kernel, the counterpart of the reference's per-phase timers
  * (crates/spark-model/src/layers/qwen3_attention/trait_impl/multi_seq/mod.rs:125-141).  While a device
  * buffer of `n_words` u64 is set (16 words per CTA, CTA index = blockIdx.y * gridDim.x + blockIdx.x) each
