@@ -45,7 +45,7 @@ struct Runtime {
     bool sm100 = false;
     int sm_count = 148;
     EncodeTiledFn encode = nullptr;
-    bool tc_attr_set[21] = {};        // token tiles 16..256 x {A16, A4} x {single CTA, CTA pair}; the two-per-SM form
+    bool tc_attr_set[20] = {};        // token tiles 16..256 x {A16, A4} x {single CTA, CTA pair}
 };
 
 static Runtime& runtime() {
@@ -244,15 +244,14 @@ struct TTiles {
     uint32_t part_rows = 0;    // rows of a block: the token tile, or half of it for CTA pairs
 };
 
-template <int MT, bool A4, bool PAIR, int OCC = 1>
+template <int MT, bool A4, bool PAIR>
 static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_shrink, const TTiles& tt, uint32_t k_split,
                      cudaStream_t st) {
-    using C = tc::Cfg<MT, A4, PAIR, OCC>;
+    using C = tc::Cfg<MT, A4, PAIR>;
     Runtime& rt = runtime();
     slot_idx += (A4 ? 5 : 0) + (PAIR ? 10 : 0);
-    if (OCC == 2) slot_idx = 20;
     if (!rt.tc_attr_set[slot_idx]) {
-        cudaError_t e = cudaFuncSetAttribute(tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR, OCC>,
+        cudaError_t e = cudaFuncSetAttribute(tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return cuda_status(e);
         rt.tc_attr_set[slot_idx] = true;
@@ -333,7 +332,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     // Only as many CTAs per tile as still lets every cluster be resident at once: clusters live inside one GPC, so
     // fewer of them fit than the SM count suggests, and a second wave would cost more than the split saves.
     // (An occupancy query per launch shape, answered by the runtime without touching the device; cached.)
-    static int active_clusters[21][9] = {};          // [kernel instance][k_split], 0 = not asked yet, -1 = query failed
+    static int active_clusters[20][9] = {};          // [kernel instance][k_split], 0 = not asked yet, -1 = query failed
     while (k_split > 1) {
         int& known = active_clusters[slot_idx][k_split];
         if (known == 0) {
@@ -349,7 +348,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
             q.attrs = qa;
             q.numAttrs = 1;
             int n = 0;
-            known = cudaOccupancyMaxActiveClusters(&n, tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR, OCC>, &q) == cudaSuccess && n > 0 ? n : -1;
+            known = cudaOccupancyMaxActiveClusters(&n, tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>, &q) == cudaSuccess && n > 0 ? n : -1;
             (void)cudaGetLastError();
         }
         if (known > 0 && size_t(grid.x / (PAIR ? 2 : 1)) * grid.y <= size_t(known)) break;
@@ -385,7 +384,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
     p.wait_for_shrink = after_shrink ? 1u : 0u;
-    return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR, OCC>, map_x, map_w, map_s, map_b, map_xs, map_t, p));
+    return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>, map_x, map_w, map_s, map_b, map_xs, map_t, p));
 }
 
 static int validate_linear(const atlas_b200_linear_desc& d) {
@@ -453,11 +452,6 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
         }
         if (k_split == 1)
             while (mt > 64 && f_tiles * ((d.m + mt - 1) / mt) * 4 < uint32_t(rt_sm_count()) * 3) mt >>= 1;
-        // FP4 activations over many waves of tiles: 128-token tiles with two CTAs per SM, so that one CTA's LoRA
-        // blocks, epilogue and start-up run under the other's main loop (see tc::Cfg)
-        const bool two_per_sm = act_fp4 && k_split == 1 && mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR) &&
-                                f_tiles * ((d.m + 127) / 128) >= 2u * uint32_t(rt_sm_count());
-        if (two_per_sm) mt = 128;
 
         ShrinkParams sp{};
         sp.x = static_cast<const uint16_t*>(d.x);
@@ -502,7 +496,6 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
             if (mt == 16) rc = launch_tc<16, true, false>(d, 0, after_shrink, tt, k_split, st);
             else if (mt == 32) rc = launch_tc<32, true, false>(d, 1, after_shrink, tt, k_split, st);
             else if (mt == 64) rc = launch_tc<64, true, false>(d, 2, after_shrink, tt, k_split, st);
-            else if (mt == 128 && two_per_sm) rc = launch_tc<128, true, true, 2>(d, 3, after_shrink, tt, k_split, st);
             else if (mt == 128) rc = pair ? launch_tc<128, true, true>(d, 3, after_shrink, tt, k_split, st) : launch_tc<128, true, false>(d, 3, after_shrink, tt, k_split, st);
             else rc = pair ? launch_tc<256, true, true>(d, 4, after_shrink, tt, k_split, st) : launch_tc<256, true, false>(d, 4, after_shrink, tt, k_split, st);
         } else if (mt == 16) rc = launch_tc<16, false, false>(d, 0, after_shrink, tt, k_split, st);

@@ -75,11 +75,7 @@ constexpr int MAX_DEST = 8;            // tensor-parallel ranks whose output buf
 // weight operand and their accumulator, but holds only HALF of the token tile's activation operand in
 // shared memory; the tensor cores of the pair exchange the halves.  That halves the shared-memory traffic
 // of the activation operand, which is what bounds the single-CTA form at 128 and 256 tokens.
-//
-// OCC = 2 (A4 pairs with 128-token tiles only) halves a CTA's footprint — shared memory, tensor memory, registers —
-// so that two CTAs share an SM: while one is in its LoRA blocks, epilogue, exit or start-up, the other keeps the
-// tensor pipe busy.  That is how a grid of many waves hides per-tile overhead without a persistent tile loop.
-template <int MT, bool A4 = false, bool PAIR = false, int OCC = 1> struct Cfg {
+template <int MT, bool A4 = false, bool PAIR = false> struct Cfg {
     static constexpr int XROWS = PAIR ? MT / 2 : MT;                       // token rows of the tile this CTA stages
     static constexpr int X_TILE_BYTES = XROWS * KB * 2;
     // A4: one stage = packed W [128 x 128 B] | packed x [MT x 128 B] | W scale bytes [128 x 16] | x scale bytes [MT x 16]
@@ -88,8 +84,7 @@ template <int MT, bool A4 = false, bool PAIR = false, int OCC = 1> struct Cfg {
     static constexpr int S4_WS = S4_X + XROWS * 128;
     static constexpr int S4_XS = S4_WS + RAW_SCALE_BYTES;
     static constexpr int S4_BYTES = ((S4_XS + MT * 16) + 1023) / 1024 * 1024;
-    static constexpr int S4_BUDGET = OCC == 2 ? 86 * 1024 : 200 * 1024;
-    static constexpr int S4_STAGES = S4_BUDGET / S4_BYTES > 8 ? 8 : S4_BUDGET / S4_BYTES;
+    static constexpr int S4_STAGES = (200 * 1024) / S4_BYTES > 8 ? 8 : (200 * 1024) / S4_BYTES;
     static constexpr int STAGES = A4 ? S4_STAGES : (XROWS >= 256 ? 5 : (XROWS >= 128 ? 6 : 8));
     // raw weight stages in flight: small token tiles leave shared memory free, and they are the
     // HBM-bound shapes that need many bytes in flight per SM
@@ -128,8 +123,6 @@ template <int MT, bool A4 = false, bool PAIR = false, int OCC = 1> struct Cfg {
     static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;                      // tmem ptr, n_gran, abort
     static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;                      // + alignment slack
     static_assert(!PAIR || MT >= 128, "pairs are built for token tiles of 128 and 256");
-    static_assert(OCC == 1 || (OCC == 2 && A4 && PAIR && MT == 128), "two CTAs per SM: FP4 activations, pairs, 128 tokens");
-    static_assert(OCC == 1 || (TMEM_COLS <= 256 && SMEM_BYTES <= 112 * 1024), "two CTAs must fit one SM");
     static_assert(TMEM_NEEDED <= 512, "tensor memory budget");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
@@ -586,8 +579,8 @@ __device__ __forceinline__ void split_reduce_store(const Params& p, uint32_t rec
     }
 }
 
-template <int MT, bool A4, bool PAIR, int OCC>
-__global__ void __launch_bounds__(NUM_THREADS, OCC)
+template <int MT, bool A4, bool PAIR>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
 nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                             const __grid_constant__ CUtensorMap map_w,
                             const __grid_constant__ CUtensorMap map_s,
@@ -595,7 +588,7 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                             const __grid_constant__ CUtensorMap map_xs,
                             const __grid_constant__ CUtensorMap map_t,
                             const Params p) {
-    using C = Cfg<MT, A4, PAIR, OCC>;
+    using C = Cfg<MT, A4, PAIR>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));

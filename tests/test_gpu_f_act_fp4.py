@@ -140,3 +140,4 @@ def test_signed_weight_scale_is_reported(cuda, atlas, oracle):
     case.scales[5, 3] &= 0x7F
     assert_close(oracle, y, ideal(oracle, case, lora=False, act_fp4=True), "sign dropped")
     assert atlas.device_status() == 0
+
