@@ -69,3 +69,30 @@ def test_placement_argument_errors(cuda, atlas, oracle):
         atlas.nvfp4_lora_linear(sh.desc(None, out_row_stride=256, y_dest=bufs + [None], y_col_offset=128))
     assert e.value.status == -4
     cuda.cuda.synchronize()
+
+
+def test_eighth_of_configuration_1_shape(cuda, atlas, oracle):
+    """The column shard an 8-rank split of configuration 1 gives one rank: 17 feature tiles (an odd number, so the
+    last CTA pair is half empty), 256 tokens, few tiles for the GPU (split K inside clusters of 2 x k_split CTAs),
+    results stored into eight gathered buffers."""
+    from atlas_b200 import synth, tp as tpmod
+    M, K, N, tp_n = 256, 1024, 17408, 8
+    case = synth.make_case("eighth", M=M, K=K, N=N, ranks=[32] * 16, max_rank=32, none_frac=0.1, scale2=0.02, b_std=0.1, seed=8)
+    r = 5
+    sh = tpmod.DeviceShard(cuda, atlas, case, tp_n, r)
+    assert sh.n_local == 2176
+    bufs = [cuda.full((M, N), 0x7FC0, dtype=cuda.int16, device="cuda") for _ in range(tp_n)]
+    atlas.nvfp4_lora_linear(sh.desc(None, out_row_stride=N, y_dest=bufs, y_col_offset=r * sh.n_local))
+    cuda.cuda.synchronize()
+    shape = atlas.last_launch_shape()
+    assert shape["token_tile"] == 256 and shape["cta_pair"] and shape["k_split"] >= 2
+    lo, hi = r * sh.n_local, (r + 1) * sh.n_local
+    rows = np.arange(0, M, 5).astype(np.uint32)
+    cols = np.arange(lo, hi, 7).astype(np.uint32)
+    want = ideal(oracle, case, rows=rows, cols=cols)
+    first = bits_from_dev(bufs[0])
+    assert_close(oracle, first[np.ix_(rows, cols)], want, "shard 5 of 8")
+    assert (first[:, :lo] == 0x7FC0).all() and (first[:, hi:] == 0x7FC0).all()
+    for b in bufs[1:]:
+        assert np.array_equal(bits_from_dev(b), first)
+    assert atlas.device_status() == 0
