@@ -197,8 +197,6 @@ int apply_lora_delta(const void* x, const void* a, const void* b, float scale, v
 static int launch_simt_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
     SimtLinearParams p{};
     p.x = static_cast<const uint16_t*>(d.x);
-    p.w_packed = static_cast<const uint8_t*>(d.w_packed);
-    p.w_scale = static_cast<const uint8_t*>(d.w_scale);
     p.w_bf16 = static_cast<const uint16_t*>(d.w_bf16);
     p.y = static_cast<uint16_t*>(d.y);
     p.M = d.m; p.N = d.n; p.K = d.k; p.x_row_stride = d.x_row_stride; p.out_row_stride = d.out_row_stride;

@@ -1,38 +1,46 @@
-// The fused NVFP4 + multi-LoRA linear for sm_100a: TMA-staged tiles, in-kernel E2M1 x E4M3 ->
-// BF16 expansion, tcgen05.mma (kind::f16, BF16 x BF16 -> FP32) into a TMEM accumulator, and the
-// LoRA expand appended as extra K-steps of the same accumulator so y is written exactly once.
+// The fused NVFP4 + multi-LoRA linear for sm_100a: TMA-staged tiles, tcgen05.mma into a TMEM accumulator,
+// and the LoRA expand appended as extra K-steps of the same accumulator so y is written exactly once.
 //
-// Orientation ("swap-AB"): the MMA's M dimension (128 TMEM lanes) is a block of 128 OUTPUT
+// Orientation ("swap-AB"): the MMA's M dimension (128 TMEM lanes per CTA) is a block of 128 OUTPUT
 // FEATURES, its N dimension (TMEM columns) a tile of MT TOKENS, MT in {16..256}.  A decode batch
 // of 16-64 tokens therefore still fills the 128-lane datapath, and a 256-token tile gives the
 // 128 x 256 x 16 instruction shape.
 //
-//   acc[f, m]  = sum_k  W'[f,k] * x[m,k]                      base: W' = E2M1*E4M3*2^-8 (exact BF16)
-//              + sum_g  B_{s_g}[f, j_g..j_g+16) * T_g[m, :]   LoRA: one 16-wide K-step per granule
-//   y[m, f]    = bf16(acc[f,m] * scale2 * 2^8)
+//   acc[f, m]  = sum_k  W'[f,k] * x[m,k]                      base, A16: W' = E2M1*E4M3*2^-8 (exact BF16), kind::f16
+//                                                             base, A4: E2M1 x E2M1 with E4M3 block scales of both
+//                                                             sides in tensor memory, kind::mxf4nvf4.block_scale
+//              + sum_g  B_{s_g}[f, j_g..j_g+16) * T_g[m, :]   LoRA: one 16-wide kind::f16 K-step per granule
+//   y[m, f]    = bf16(acc[f,m] * scale2 [* 2^8])
 //
 // A granule g is 16 consecutive ranks of one adapter slot that occurs in the token tile; T_g[m,:]
-// is row m of the pre-scaled shrink result t (see lora_shrink_grouped_kernel) where seq_slot[m]
-// equals the granule's slot and zero elsewhere, so adapters never mix across tokens.  Granules
-// are ordered by slot, four to a 64-wide K block; zeros add exactly, so a token's result does not
-// depend on which other tokens share its tile.
+// is row m of the pre-scaled shrink result t where seq_slot[m] equals the granule's slot and zero
+// elsewhere, so adapters never mix across tokens.  Granules are ordered by slot, four to a K block;
+// zeros add exactly, so a token's result does not depend on which other tokens share its tile.
+// The masked tiles either arrive ready-made from the shrink kernel (Params::t_tile_cap) or are built
+// here from t.
 //
-// Operand placement: the weight operand (MMA "A", 128 features x 16 k per instruction) is written
+// Operand placement, A16: the weight operand (MMA "A", 128 features x 16 k per instruction) is written
 // by the expansion warps straight into TENSOR MEMORY (tcgen05.st) and read from there by the MMA;
-// only the activation operand lives in shared memory.  Shared-memory bandwidth is what bounds this
-// kernel (TMA writes + MMA operand reads + raw-code reads all share it), and a BF16 weight tile
-// that is written to and read back from shared memory every K block costs a third of it.
+// only the activation operand lives in shared memory.  A4: both operands are the packed tiles in
+// shared memory as TMA delivers them; the warps only carry scale bytes to tensor memory.
+//
+// Launch shapes: one CTA per tile; or pairs of CTAs (clusters of 2 along x) issuing cta_group::2 MMAs
+// with half of the activation tile each (Cfg::PAIR); and, times that, k_split CTAs along z sharing one
+// tile's contraction and exchanging partial sums over distributed shared memory.
 //
 // Warp roles (14 warps, 448 threads):
-//   warp 0        TMA producer: x tiles (SWIZZLE_128B) and raw weight stages (packed codes with
-//                 SWIZZLE_128B + scale bytes) through mbarrier rings
-//   warp 1        TMEM allocation, tcgen05.mma issue, tcgen05.commit
+//   warp 0        TMA producer: activation tiles, raw weight stages (packed codes + scale bytes),
+//                 LoRA operand tiles, each through its own mbarrier ring
+//   warp 1        TMEM allocation, tcgen05.mma issue, tcgen05.commit (in a pair: the first CTA's thread
+//                 issues for both)
 //   warps 2-5     build the tile's granule list while the main loop runs; then the epilogue
-//   warps 6-13    expand raw NVFP4 into the BF16 weight operand (TMEM); build the LoRA operands;
-//                 then join the epilogue: tcgen05.ld -> scale -> BF16 -> global
+//   warps 6-13    A16: expand raw NVFP4 into the BF16 weight operand (TMEM); A4: scale bytes -> TMEM;
+//                 build the LoRA operands where the shrink has not; then join the epilogue:
+//                 tcgen05.ld -> scale -> BF16 -> shared-memory tile -> 16-byte row stores
 //
-// Every wait is bounded: on expiry the waiter records a status code, raises the CTA's abort
-// flag, and all roles fall through to a common teardown that frees TMEM.
+// Every mbarrier wait is bounded: on expiry the waiter records a status code, raises the CTA's abort
+// flag, and all roles fall through to a common teardown that frees TMEM; cluster barriers are placed
+// where every thread of every CTA passes on every path.
 #pragma once
 
 #include <cuda.h>
@@ -644,7 +652,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
 
     if (tid == 0) {
         for (int i = 0; i < C::STAGES; ++i) {
-            mbar_init(BAR_FULL + 8 * i, CTAS * DEQ_GROUP_WARPS + 1);     // used in the pair's first CTA only
+            // A16: every expansion warp of the pair writes part of a stage; A4: the four warps of one half do
+            mbar_init(BAR_FULL + 8 * i, CTAS * (A4 ? DEQ_GROUP_WARPS / 2 : DEQ_GROUP_WARPS) + 1);     // used in the pair's first CTA only
             mbar_init(BAR_EMPTY + 8 * i, 1);
         }
         for (int i = 0; i < C::RAW_STAGES; ++i) {
@@ -991,14 +1000,19 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             // Block scales, shared memory -> registers -> TMEM.  The warp of quadrant q writes lanes
             // [32 q, +32); the MMA wants every quadrant to hold the same 32 x 4-column image (lane l:
             // rows l, l+32, l+64, l+96 of the 128-row block), so the four warps of a half write the same
-            // values.  half 0 moves the weight scales, half 1 the activation scales.
+            // values.  The halves take alternate stages (both operands' scales), so that one stage's
+            // load -> store -> wait chain runs under the other's.
             s = 0;
             for (uint32_t it = 0; ok && it < num_kb; ++it) {
+                if ((it & 1u) != half) {
+                    if (++s == uint32_t(C::STAGES)) { s = 0; ph ^= 1u; }
+                    continue;
+                }
                 ok = mbar_wait_timed(BAR_FULL_RAW + 8 * s, ph, abort_flag, STATUS_WAIT_EXPIRED_DEQUANT, prof, w_raw);
                 if (!ok) break;
                 const uint32_t st = smem_base + s * C::S4_BYTES;
                 const uint32_t sf = tmem_a0 + lane_base + s * C::SF_COLS;
-                if (half == 0) {
+                {
                     uint32_t r[16];
                     uint32_t neg = 0;
 #pragma unroll
@@ -1016,7 +1030,8 @@ nvfp4_lora_linear_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     }
                     if (neg & 0x80808080u) record_status(STATUS_NEGATIVE_SCALE);
                     tmem_st16(sf, r);
-                } else if constexpr (C::XSF_BLOCKS == 1) {
+                }
+                if constexpr (C::XSF_BLOCKS == 1) {
                     uint32_t r[16];                           // column = 4 i + c
 #pragma unroll
                     for (uint32_t c = 0; c < 4; ++c) {
