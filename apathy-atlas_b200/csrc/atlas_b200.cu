@@ -91,7 +91,8 @@ static bool shrink_takes_mma_path(const ShrinkParams& p) {
     return (p.k_in % 32 == 0) && (p.x_row_stride % 8 == 0) && aligned(p.x, 16) && (p.seq_slot || aligned(p.a_uniform, 4));
 }
 
-static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool release_dependents = false) {
+static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool release_dependents = false,
+                         bool dependent_leaves_sms_free = false) {
     p.release_dependents = release_dependents ? 1u : 0u;
     if (p.M == 0 || p.max_rank == 0) return ATLAS_B200_OK;
     // Same shared-memory carve-out as the tcgen05 kernel, so that kernel's CTAs can become resident
@@ -106,7 +107,14 @@ static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool
     if (p.tile_out && !mma_ok) return ATLAS_B200_ERR_DIMS;      // tile output exists in the tensor-core shrink only
     if (mma_ok) {
         const uint32_t chunk = p.chunk ? p.chunk : uint32_t(SHM_CHUNK);
-        dim3 grid(n_slots * SHM_KSPLIT, (p.max_rank + SHM_RANKS - 1) / SHM_RANKS, (p.M + chunk - 1) / chunk);
+        // CTAs per (slot, granule, chunk) sharing K: 8 for the sake of loads in flight; fewer when the dependent kernel
+        // runs beside this grid on a part of the machine only (a decode batch) and this grid would otherwise be so
+        // large that the dependent's CTAs find no room until it has drained
+        const size_t items = size_t(n_slots) * ((p.max_rank + SHM_RANKS - 1) / SHM_RANKS) * ((p.M + chunk - 1) / chunk);
+        uint32_t ksplit = SHM_KSPLIT;
+        while (release_dependents && dependent_leaves_sms_free && ksplit > 2 && items * ksplit > size_t(rt_sm_count()) * 4) ksplit >>= 1;
+        p.ksplit = ksplit;
+        dim3 grid(n_slots * ksplit, (p.max_rank + SHM_RANKS - 1) / SHM_RANKS, (p.M + chunk - 1) / chunk);
         if (grid.y > 65535 || grid.z > 65535) return ATLAS_B200_ERR_LIMIT;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = grid;
@@ -114,7 +122,7 @@ static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool
         cfg.stream = st;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;      // SHM_KSPLIT CTAs along x share one (slot, ranks, chunk)
-        attr[0].val.clusterDim.x = SHM_KSPLIT;
+        attr[0].val.clusterDim.x = ksplit;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
@@ -197,6 +205,8 @@ int apply_lora_delta(const void* x, const void* a, const void* b, float scale, v
 static int launch_simt_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
     SimtLinearParams p{};
     p.x = static_cast<const uint16_t*>(d.x);
+    p.w_packed = static_cast<const uint8_t*>(d.w_packed);
+    p.w_scale = static_cast<const uint8_t*>(d.w_scale);
     p.w_bf16 = static_cast<const uint16_t*>(d.w_bf16);
     p.y = static_cast<uint16_t*>(d.y);
     p.M = d.m; p.N = d.n; p.K = d.k; p.x_row_stride = d.x_row_stride; p.out_row_stride = d.out_row_stride;
@@ -484,7 +494,8 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
         if (d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK)) {
             // A small batch: let the main kernel start under the shrink.  A large one: the shrink is a
             // sizeable grid that should have the whole machine first; the main kernel then follows it.
-            rc = launch_shrink(sp, d.max_loras, st, d.m <= 1024);
+            const uint32_t main_ctas = f_tiles * ((d.m + mt - 1) / mt) * k_split;
+            rc = launch_shrink(sp, d.max_loras, st, d.m <= 1024, main_ctas * 3 <= uint32_t(rt_sm_count()) * 2);
             if (rc) return rc;
         }
         const bool after_shrink = d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK);

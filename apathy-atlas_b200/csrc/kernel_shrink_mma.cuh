@@ -33,7 +33,7 @@ constexpr int SHM_THREADS = 128;
 constexpr int SHM_RANKS = 16;     // ranks per CTA (two n-tiles of 8)
 constexpr int SHM_TOKENS = 32;    // tokens per pass (two m-tiles of 16)
 constexpr int SHM_CHUNK = 256;    // tokens scanned per CTA
-constexpr int SHM_KSPLIT = 8;     // CTAs per cluster, splitting K
+constexpr int SHM_KSPLIT = 8;     // CTAs per cluster, splitting K, at most (the launch picks 1, 2, 4 or 8: ShrinkParams::ksplit)
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -51,8 +51,9 @@ lora_shrink_mma_kernel(const ShrinkParams p) {
     if (p.release_dependents) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     cg::cluster_group cluster = cg::this_cluster();
     const uint32_t krank = cluster.block_rank();            // this CTA's share of K
+    const uint32_t ksplit = p.ksplit;                       // = the cluster's size
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t s = blockIdx.x / SHM_KSPLIT;
+    const uint32_t s = blockIdx.x / ksplit;
     const uint32_t j0 = blockIdx.y * SHM_RANKS;
     const uint32_t chunk = p.chunk ? p.chunk : uint32_t(SHM_CHUNK);
     const uint32_t m_base = blockIdx.z * chunk;
@@ -66,6 +67,7 @@ lora_shrink_mma_kernel(const ShrinkParams p) {
         if (p.b_table && p.b_table[s] == 0ull) return;
         A = reinterpret_cast<const uint16_t*>(a_addr);
         if (p.rank_table) rank = min(p.rank_table[s], p.max_rank);
+        if (p.tile_out && j0 >= rank) return;               // no such granule in any tile's list (whole cluster leaves)
         if (p.post != 0.0f) f = p.scale_table[s] * p.post;
     } else {
         A = p.a_uniform;
@@ -185,7 +187,7 @@ lora_shrink_mma_kernel(const ShrinkParams p) {
             for (int nt = 0; nt < 2; ++nt) ar[nt] = A + size_t(min(j0 + nt * 8 + g, p.max_rank - 1)) * p.k_in + 8 * t;
 
 #pragma unroll 2
-            for (uint32_t c = krank + SHM_KSPLIT * warp; c < n_chunks; c += SHM_KSPLIT * (SHM_THREADS / 32)) {
+            for (uint32_t c = krank + ksplit * warp; c < n_chunks; c += ksplit * (SHM_THREADS / 32)) {
                 uint4 xv[2][2], av[2];
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt)
@@ -234,8 +236,7 @@ lora_shrink_mma_kernel(const ShrinkParams p) {
                 const uint32_t tok = i / SHM_RANKS, jr = i % SHM_RANKS;
                 if (r0 + tok < n_rows && (p.tile_out || j0 + jr < p.max_rank)) {
                     float v = 0.0f;
-#pragma unroll
-                    for (int r = 0; r < SHM_KSPLIT; ++r) v += cluster.map_shared_rank(&part[0][0], r)[i];
+                    for (uint32_t r = 0; r < ksplit; ++r) v += cluster.map_shared_rank(&part[0][0], r)[i];
                     const uint16_t bits = f32_to_bf16_bits((j0 + jr < rank) ? v * f : 0.0f);
                     if (p.tile_out) {
                         if (tile) {

@@ -93,7 +93,7 @@ template <int MT, bool A4 = false, bool PAIR = false> struct Cfg {
     static constexpr int S4_XS = S4_WS + RAW_SCALE_BYTES;
     static constexpr int S4_BYTES = ((S4_XS + MT * 16) + 1023) / 1024 * 1024;
     static constexpr int S4_STAGES = (200 * 1024) / S4_BYTES > 8 ? 8 : (200 * 1024) / S4_BYTES;
-    static constexpr int STAGES = A4 ? S4_STAGES : (XROWS >= 256 ? 5 : (XROWS >= 128 ? 6 : 8));
+    static constexpr int STAGES = A4 ? S4_STAGES : (XROWS >= 256 ? 5 : 8);
     // raw weight stages in flight: small token tiles leave shared memory free, and they are the
     // HBM-bound shapes that need many bytes in flight per SM
     static constexpr int RAW_STAGES = A4 ? STAGES : (XROWS >= 256 ? 2 : (XROWS >= 128 ? 4 : 6));

@@ -158,6 +158,7 @@ struct ShrinkParams {
     uint32_t tile_cap;              // blocks reserved per tile
     uint32_t chunk;                 // tokens scanned per CTA (<= 256); 0 = 256
     uint32_t part_rows;             // chunk or chunk / 2
+    uint32_t ksplit;                // tensor-core shrink: CTAs per cluster sharing K (set by the launcher)
 };
 
 __global__ void __launch_bounds__(SHRINK_THREADS)

@@ -4,7 +4,7 @@ library's replacements for them."""
 import numpy as np
 import pytest
 
-from gpu_util import RefModule, assert_close, bits_from_dev, device_pool, host_pool, ref_available, to_dev
+from gpu_util import DeviceCase, RefModule, assert_close, bits_from_dev, device_pool, host_pool, ref_available, to_dev
 
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not ref_available(), reason="oracle/_ref cubins not built")]
 
@@ -78,3 +78,66 @@ def test_reference_w4a16_gemm_equals_oracle_and_library(cuda, atlas, oracle):
     atlas.w4a16_gemm(x, dp, ds, float(np.float32(0.01)), c_lib, M, N, K)
     torch.cuda.synchronize()
     assert_close(oracle, bits_from_dev(c_lib), oracle.bf16_to_f32(bits_from_dev(c_ref)), "library vs reference gemm")
+
+
+def test_reference_launch_sequence_on_configuration_1(cuda, atlas, oracle, capsys):
+    """The reference's own three launches for this layer (w4a16_gemm, lora_bgmv_shrink, lora_bgmv_expand_fold), compiled
+    unchanged for sm_100a, at the size of benchmark configuration 1: same result as this library's reference-rounding
+    mode, and how long the sequence takes on this GPU next to the fused call (printed; run with -s to read it)."""
+    torch = cuda
+    from atlas_b200 import synth
+    case = synth.baseline_config(1)
+    M, K, N, max_rank = case.M, case.K, case.N, case.max_rank
+    dc = DeviceCase(torch, atlas, case)
+    pool = dc.pool
+    gemm, bgmv = RefModule("w4a16_gemm"), RefModule("lora_bgmv")
+    out_ref = torch.zeros((M, N), dtype=torch.int16, device="cuda")
+    xa_ref = torch.zeros((M, max_rank), dtype=torch.int16, device="cuda")
+
+    def reference_sequence():
+        gemm.launch("w4a16_gemm", ((N + 63) // 64, (M + 63) // 64, 1), (128, 1, 1),
+                    [dc.x.data_ptr(), dc.packed.data_ptr(), dc.scales.data_ptr(), float(case.scale2), out_ref.data_ptr(),
+                     u32(M), u32(N), u32(K)], stream=torch.cuda.current_stream().cuda_stream)
+        bgmv.launch("lora_bgmv_shrink", ((max_rank + 3) // 4, M, 1), (256, 1, 1),
+                    [dc.x.data_ptr(), dc.seq_slot.data_ptr(), pool.a_table.data_ptr(), xa_ref.data_ptr(),
+                     u32(M), u32(max_rank), u32(K), u32(K)], stream=torch.cuda.current_stream().cuda_stream)
+        bgmv.launch("lora_bgmv_expand_fold", ((N + 3) // 4, M, 1), (256, 1, 1),
+                    [xa_ref.data_ptr(), dc.seq_slot.data_ptr(), pool.b_table.data_ptr(), pool.scale_table.data_ptr(),
+                     out_ref.data_ptr(), u32(M), u32(N), u32(max_rank), u32(N)], stream=torch.cuda.current_stream().cuda_stream)
+
+    reference_sequence()
+    torch.cuda.synchronize()
+    y_staged, _ = dc.run(flags=atlas.FLAG_STAGED_LORA)                   # this library, the reference's rounding boundaries
+    ref = bits_from_dev(out_ref)
+    assert_close(oracle, y_staged, oracle.bf16_to_f32(ref), "library (reference rounding) vs reference kernels")
+    y_fused, variant = dc.run(lora_ws=True)
+    assert variant == atlas.VARIANT_TCGEN05
+    none = case.seq_slot < 0
+    got, want = oracle.bf16_to_f32(y_fused), oracle.bf16_to_f32(ref)
+    assert_close(oracle, y_fused[none], want[none], "fused vs reference kernels, adapter-less rows")
+    # adapted rows differ by the reference's extra roundings (base -> BF16 before the fold): within a few BF16 ulps
+    assert np.abs(got - want).max() <= 4e-2 * np.abs(want).max()
+
+    def timed(fn, n=20):
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for a, b in ev:
+            flush.fill_(1)
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        return float(np.median([a.elapsed_time(b) for a, b in ev])) * 1e3
+
+    y = torch.empty((M, N), dtype=torch.int16, device="cuda")
+    ws_bytes = atlas.lora_ws_bytes(M, case.max_loras, max_rank)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    d = atlas.make_linear_desc(x=dc.x, m=M, k=K, n=N, y=y, w_packed=dc.packed, w_scale=dc.scales, scale2=case.scale2,
+                               seq_slot=dc.seq_slot, route=pool.route(True, True), lora_t=dc.lora_t, ws=ws, ws_bytes=ws_bytes)
+    t_ref = timed(reference_sequence)
+    t_lib = timed(lambda: atlas.nvfp4_lora_linear(d))
+    with capsys.disabled():
+        print(f"\n[configuration 1 on this GPU] reference kernels (3 launches): {t_ref:.1f} us; fused call: {t_lib:.1f} us; "
+              f"ratio {t_ref / t_lib:.1f}x")
+    assert t_lib < t_ref
+    assert atlas.device_status() == 0
