@@ -253,8 +253,9 @@ struct TTiles {
 };
 
 template <int MT, bool A4, bool PAIR>
-static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_shrink, const TTiles& tt, uint32_t k_split,
-                     cudaStream_t st) {
+static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, const ShrinkParams* shrink, const TTiles& tt,
+                     uint32_t k_split, cudaStream_t st) {
+    const bool after_shrink = shrink != nullptr;     // the shrink is launched from here, once the launch shape is final
     using C = tc::Cfg<MT, A4, PAIR>;
     Runtime& rt = runtime();
     slot_idx += (A4 ? 5 : 0) + (PAIR ? 10 : 0);
@@ -365,6 +366,13 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, bool after_s
     grid.z = k_split;
     p.k_split = k_split;
     t_last_shape[0] = MT; t_last_shape[1] = PAIR ? 1u : 0u; t_last_shape[2] = k_split; t_last_shape[3] = tt.tiles ? 1u : 0u;
+    if (shrink) {
+        // A small batch: let this kernel start under the shrink.  A large one: the shrink is a sizeable grid that
+        // should have the whole machine first; this kernel then follows it.
+        const uint32_t main_ctas = grid.x * grid.y * grid.z;
+        const int rc = launch_shrink(*shrink, d.max_loras, st, d.m <= 1024, main_ctas * 3 <= uint32_t(rt_sm_count()) * 2);
+        if (rc) return rc;
+    }
     p.profile = (g_profile_buf && size_t(grid.x) * grid.y * tc::PROFILE_WORDS <= g_profile_words) ? g_profile_buf : nullptr;
     if (grid.y > 65535) return ATLAS_B200_ERR_LIMIT;
     // Launched as a programmatic dependent of the shrink that precedes it in the stream: its CTAs
@@ -491,27 +499,20 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
                 sp.part_rows = tt.part_rows = (mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR)) ? mt / 2 : mt;
             }
         }
-        if (d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK)) {
-            // A small batch: let the main kernel start under the shrink.  A large one: the shrink is a
-            // sizeable grid that should have the whole machine first; the main kernel then follows it.
-            const uint32_t main_ctas = f_tiles * ((d.m + mt - 1) / mt) * k_split;
-            rc = launch_shrink(sp, d.max_loras, st, d.m <= 1024, main_ctas * 3 <= uint32_t(rt_sm_count()) * 2);
-            if (rc) return rc;
-        }
-        const bool after_shrink = d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK);
+        const ShrinkParams* shrink = (d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK)) ? &sp : nullptr;
         // 128 and 256 tokens: pairs of CTAs issue their MMAs together (see tc::Cfg)
         const bool pair = mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR);
         if (act_fp4) {
-            if (mt == 16) rc = launch_tc<16, true, false>(d, 0, after_shrink, tt, k_split, st);
-            else if (mt == 32) rc = launch_tc<32, true, false>(d, 1, after_shrink, tt, k_split, st);
-            else if (mt == 64) rc = launch_tc<64, true, false>(d, 2, after_shrink, tt, k_split, st);
-            else if (mt == 128) rc = pair ? launch_tc<128, true, true>(d, 3, after_shrink, tt, k_split, st) : launch_tc<128, true, false>(d, 3, after_shrink, tt, k_split, st);
-            else rc = pair ? launch_tc<256, true, true>(d, 4, after_shrink, tt, k_split, st) : launch_tc<256, true, false>(d, 4, after_shrink, tt, k_split, st);
-        } else if (mt == 16) rc = launch_tc<16, false, false>(d, 0, after_shrink, tt, k_split, st);
-        else if (mt == 32) rc = launch_tc<32, false, false>(d, 1, after_shrink, tt, k_split, st);
-        else if (mt == 64) rc = launch_tc<64, false, false>(d, 2, after_shrink, tt, k_split, st);
-        else if (mt == 128) rc = pair ? launch_tc<128, false, true>(d, 3, after_shrink, tt, k_split, st) : launch_tc<128, false, false>(d, 3, after_shrink, tt, k_split, st);
-        else rc = pair ? launch_tc<256, false, true>(d, 4, after_shrink, tt, k_split, st) : launch_tc<256, false, false>(d, 4, after_shrink, tt, k_split, st);
+            if (mt == 16) rc = launch_tc<16, true, false>(d, 0, shrink, tt, k_split, st);
+            else if (mt == 32) rc = launch_tc<32, true, false>(d, 1, shrink, tt, k_split, st);
+            else if (mt == 64) rc = launch_tc<64, true, false>(d, 2, shrink, tt, k_split, st);
+            else if (mt == 128) rc = pair ? launch_tc<128, true, true>(d, 3, shrink, tt, k_split, st) : launch_tc<128, true, false>(d, 3, shrink, tt, k_split, st);
+            else rc = pair ? launch_tc<256, true, true>(d, 4, shrink, tt, k_split, st) : launch_tc<256, true, false>(d, 4, shrink, tt, k_split, st);
+        } else if (mt == 16) rc = launch_tc<16, false, false>(d, 0, shrink, tt, k_split, st);
+        else if (mt == 32) rc = launch_tc<32, false, false>(d, 1, shrink, tt, k_split, st);
+        else if (mt == 64) rc = launch_tc<64, false, false>(d, 2, shrink, tt, k_split, st);
+        else if (mt == 128) rc = pair ? launch_tc<128, false, true>(d, 3, shrink, tt, k_split, st) : launch_tc<128, false, false>(d, 3, shrink, tt, k_split, st);
+        else rc = pair ? launch_tc<256, false, true>(d, 4, shrink, tt, k_split, st) : launch_tc<256, false, false>(d, 4, shrink, tt, k_split, st);
         if (rc == ATLAS_B200_OK) t_last_variant = ATLAS_B200_VARIANT_TCGEN05;
         return rc;
     }
