@@ -252,6 +252,53 @@ struct TTiles {
     uint32_t part_rows = 0;    // rows of a block: the token tile, or half of it for CTA pairs
 };
 
+// How many clusters of (PAIR ? 2 : 1) x 1 x k_split CTAs of one kernel instance can be resident at once.  Clusters live
+// inside one GPC, so fewer fit than the SM count suggests.  An occupancy query, answered by the runtime without touching
+// the device; asked once per shape.  -1: the query failed.
+template <int MT, bool A4, bool PAIR>
+static int tc_active_clusters(int slot_idx, uint32_t k_split) {
+    using C = tc::Cfg<MT, A4, PAIR>;
+    Runtime& rt = runtime();
+    slot_idx += (A4 ? 5 : 0) + (PAIR ? 10 : 0);
+    static int known[20][9] = {};                   // 0 = not asked yet
+    if (k_split > 8) return -1;
+    if (known[slot_idx][k_split] == 0) {
+        if (!rt.tc_attr_set[slot_idx]) {
+            if (cudaFuncSetAttribute(tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     C::SMEM_BYTES) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return -1;
+            }
+            rt.tc_attr_set[slot_idx] = true;
+        }
+        cudaLaunchConfig_t q{};
+        q.gridDim = dim3(PAIR ? 2 : 1, 1, k_split);
+        q.blockDim = dim3(tc::NUM_THREADS);
+        q.dynamicSmemBytes = C::SMEM_BYTES;
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = PAIR ? 2 : 1;
+        qa[0].val.clusterDim.y = 1;
+        qa[0].val.clusterDim.z = k_split;
+        q.attrs = qa;
+        q.numAttrs = 1;
+        int n = 0;
+        known[slot_idx][k_split] =
+            cudaOccupancyMaxActiveClusters(&n, tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>, &q) == cudaSuccess && n > 0 ? n : -1;
+        (void)cudaGetLastError();
+    }
+    return known[slot_idx][k_split];
+}
+
+static int tc_active_clusters_of(uint32_t mt, bool a4, bool pair, uint32_t k_split) {
+#define ATLAS_OCC(MT_, I_) \
+    if (mt == MT_) return a4 ? (pair ? tc_active_clusters<MT_, true, (MT_ >= 128)>(I_, k_split) : tc_active_clusters<MT_, true, false>(I_, k_split)) \
+                             : (pair ? tc_active_clusters<MT_, false, (MT_ >= 128)>(I_, k_split) : tc_active_clusters<MT_, false, false>(I_, k_split));
+    ATLAS_OCC(16, 0) ATLAS_OCC(32, 1) ATLAS_OCC(64, 2) ATLAS_OCC(128, 3) ATLAS_OCC(256, 4)
+#undef ATLAS_OCC
+    return -1;
+}
+
 template <int MT, bool A4, bool PAIR>
 static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, const ShrinkParams* shrink, const TTiles& tt,
                      uint32_t k_split, cudaStream_t st) {
@@ -338,31 +385,6 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, const Shrink
     if (k_split > 1 && (k_split * (PAIR ? 2u : 1u) > 8u ||
                         size_t(k_split) * ((MT / 16 + k_split - 1) / k_split) * 8192 > size_t(C::STAGING_BYTES)))
         return ATLAS_B200_ERR_LIMIT;
-    // Only as many CTAs per tile as still lets every cluster be resident at once: clusters live inside one GPC, so
-    // fewer of them fit than the SM count suggests, and a second wave would cost more than the split saves.
-    // (An occupancy query per launch shape, answered by the runtime without touching the device; cached.)
-    static int active_clusters[20][9] = {};          // [kernel instance][k_split], 0 = not asked yet, -1 = query failed
-    while (k_split > 1) {
-        int& known = active_clusters[slot_idx][k_split];
-        if (known == 0) {
-            cudaLaunchConfig_t q{};
-            q.gridDim = dim3(grid.x, grid.y, k_split);
-            q.blockDim = dim3(tc::NUM_THREADS);
-            q.dynamicSmemBytes = C::SMEM_BYTES;
-            cudaLaunchAttribute qa[1];
-            qa[0].id = cudaLaunchAttributeClusterDimension;
-            qa[0].val.clusterDim.x = PAIR ? 2 : 1;
-            qa[0].val.clusterDim.y = 1;
-            qa[0].val.clusterDim.z = k_split;
-            q.attrs = qa;
-            q.numAttrs = 1;
-            int n = 0;
-            known = cudaOccupancyMaxActiveClusters(&n, tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>, &q) == cudaSuccess && n > 0 ? n : -1;
-            (void)cudaGetLastError();
-        }
-        if (known > 0 && size_t(grid.x / (PAIR ? 2 : 1)) * grid.y <= size_t(known)) break;
-        --k_split;
-    }
     grid.z = k_split;
     p.k_split = k_split;
     t_last_shape[0] = MT; t_last_shape[1] = PAIR ? 1u : 0u; t_last_shape[2] = k_split; t_last_shape[3] = tt.tiles ? 1u : 0u;
@@ -460,14 +482,25 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
         // contracting a share of K, rather than leaving SMs idle — a CTA's time is set by the weights it has
         // to expand, which only a K split divides.  Clusters of at most 8 CTAs; whole 256-element stages.
         uint32_t k_split = 1;
+        bool pair = mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR);    // pairs of CTAs issue their MMAs together (see tc::Cfg)
         if (!(d.flags & ATLAS_B200_FLAG_NO_K_SPLIT)) {
-            const bool pair_here = mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR);
-            const uint32_t tiles = f_tiles * ((d.m + mt - 1) / mt);
-            const uint32_t fit = uint32_t(rt_sm_count()) / tiles;
-            k_split = std::max(1u, std::min(std::min(fit, pair_here ? 4u : 8u), d.k / uint32_t(tc::KRAW)));
+            const uint32_t m_tiles = (d.m + mt - 1) / mt;
+            const uint32_t fit = uint32_t(rt_sm_count()) / (f_tiles * m_tiles);
+            k_split = std::max(1u, std::min(std::min(fit, 8u), d.k / uint32_t(tc::KRAW)));
+            // ... but only as many as still lets every cluster be resident at once (a second wave would cost more than the
+            // split saves), preferring the shape with pairs, then the one without, then a smaller split
+            const bool may_pair = pair;
+            for (; k_split > 1; --k_split) {
+                if (may_pair && k_split <= 4 &&
+                    tc_active_clusters_of(mt, act_fp4, true, k_split) >= int(((f_tiles + 1) / 2) * m_tiles)) { pair = true; break; }
+                if (tc_active_clusters_of(mt, act_fp4, false, k_split) >= int(f_tiles * m_tiles)) { pair = false; break; }
+            }
+            if (k_split == 1) pair = may_pair;
         }
-        if (k_split == 1)
+        if (k_split == 1) {
             while (mt > 64 && f_tiles * ((d.m + mt - 1) / mt) * 4 < uint32_t(rt_sm_count()) * 3) mt >>= 1;
+            pair = mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR);
+        }
 
         ShrinkParams sp{};
         sp.x = static_cast<const uint16_t*>(d.x);
@@ -496,12 +529,10 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
                 sp.tile_out = tt.tiles;
                 sp.tile_cap = cap;
                 sp.chunk = mt;
-                sp.part_rows = tt.part_rows = (mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR)) ? mt / 2 : mt;
+                sp.part_rows = tt.part_rows = pair ? mt / 2 : mt;
             }
         }
         const ShrinkParams* shrink = (d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK)) ? &sp : nullptr;
-        // 128 and 256 tokens: pairs of CTAs issue their MMAs together (see tc::Cfg)
-        const bool pair = mt >= 128 && !(d.flags & ATLAS_B200_FLAG_NO_CTA_PAIR);
         if (act_fp4) {
             if (mt == 16) rc = launch_tc<16, true, false>(d, 0, shrink, tt, k_split, st);
             else if (mt == 32) rc = launch_tc<32, true, false>(d, 1, shrink, tt, k_split, st);

@@ -1,13 +1,15 @@
 // Tensor-core LoRA shrink:  t[m, j] = f(s) * sum_k x[m,k] * A_s[j,k],  s = seq_slot[m].
 //
-// A CLUSTER of SHM_KSPLIT CTAs (4 warps each) owns (adapter slot s, 16 consecutive ranks = one granule
-// of the fused layer, a chunk of 256 tokens).  Every CTA scans the chunk's seq_slot entries for the
-// rows routed to s and walks them 32 at a time.  K is split in interleaved 32-element chunks over the
-// cluster's CTAs and their warps (the op is bound by memory latency, so what matters is how many
-// loads are in flight); each warp multiplies its chunks with mma.sync.m16n8k16 (BF16 in, FP32
-// accumulate), a CTA adds its four partial tiles in shared memory, and the cluster's first CTA adds
-// the CTAs' tiles over distributed shared memory — always in the same order, so results do not
-// depend on timing.
+// A CLUSTER of 1..SHM_KSPLIT CTAs (4 warps each; ShrinkParams::ksplit, chosen at launch) owns (adapter slot s, 16
+// consecutive ranks = one granule of the fused layer, a chunk of tokens = that layer's token tile).  Every CTA
+// scans the chunk's seq_slot entries for the rows routed to s and walks them 32 at a time.  K is split in
+// interleaved 32-element chunks over the cluster's CTAs and their warps (the op is bound by memory latency, so
+// what matters is how many loads are in flight); each warp multiplies its chunks with mma.sync.m16n8k16 (BF16
+// in, FP32 accumulate), a CTA adds its four partial tiles in shared memory, and the cluster's first CTA adds
+// the CTAs' tiles over distributed shared memory — always in the same order, so results do not depend on timing.
+//
+// The result goes either to rows of t [M, max_rank], or (ShrinkParams::tile_out) to complete masked blocks in
+// the layout the fused kernel's MMA reads, see ShrinkParams.
 //
 // Operand fragments are loaded straight from global memory with 128-bit loads: the thread with
 // (group g, quad lane t) reads 8 consecutive K elements at k = 32*chunk + 8*t of row g (and g+8) of

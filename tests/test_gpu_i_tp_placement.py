@@ -73,7 +73,7 @@ def test_placement_argument_errors(cuda, atlas, oracle):
 
 def test_eighth_of_configuration_1_shape(cuda, atlas, oracle):
     """The column shard an 8-rank split of configuration 1 gives one rank: 17 feature tiles (an odd number, so the
-    last CTA pair is half empty), 256 tokens, few tiles for the GPU (split K inside clusters of 2 x k_split CTAs),
+    last CTA pair, where pairs are used, is half empty), 256 tokens, few tiles for the GPU (split K inside clusters),
     results stored into eight gathered buffers."""
     from atlas_b200 import synth, tp as tpmod
     M, K, N, tp_n = 256, 1024, 17408, 8
@@ -85,7 +85,7 @@ def test_eighth_of_configuration_1_shape(cuda, atlas, oracle):
     atlas.nvfp4_lora_linear(sh.desc(None, out_row_stride=N, y_dest=bufs, y_col_offset=r * sh.n_local))
     cuda.cuda.synchronize()
     shape = atlas.last_launch_shape()
-    assert shape["token_tile"] == 256 and shape["cta_pair"] and shape["k_split"] >= 2
+    assert shape["token_tile"] == 256 and shape["k_split"] >= 2
     lo, hi = r * sh.n_local, (r + 1) * sh.n_local
     rows = np.arange(0, M, 5).astype(np.uint32)
     cols = np.arange(lo, hi, 7).astype(np.uint32)
