@@ -71,16 +71,16 @@ def test_placement_argument_errors(cuda, atlas, oracle):
     cuda.cuda.synchronize()
 
 
-def test_eighth_of_configuration_1_shape(cuda, atlas, oracle):
-    """The column shard an 8-rank split of configuration 1 gives one rank: 17 feature tiles (an odd number, so the
-    last CTA pair, where pairs are used, is half empty), 256 tokens, few tiles for the GPU (split K inside clusters),
-    results stored into eight gathered buffers."""
+@pytest.mark.parametrize("tp_n,K,r", [(8, 1024, 5), (4, 768, 2), (2, 1280, 1)])
+def test_shards_of_configuration_1_shape(cuda, atlas, oracle, tp_n, K, r):
+    """The column shard a tp_n-rank split of configuration 1 gives one rank (tp_n = 8: 17 feature tiles, an odd number, so
+    the last CTA pair, where pairs are used, is half empty), 256 tokens, few tiles for the GPU (split K inside clusters,
+    among them a three-way split of a 256-token tile), results stored into tp_n gathered buffers."""
     from atlas_b200 import synth, tp as tpmod
-    M, K, N, tp_n = 256, 1024, 17408, 8
-    case = synth.make_case("eighth", M=M, K=K, N=N, ranks=[32] * 16, max_rank=32, none_frac=0.1, scale2=0.02, b_std=0.1, seed=8)
-    r = 5
+    M, N = 256, 17408
+    case = synth.make_case("shard", M=M, K=K, N=N, ranks=[32] * 16, max_rank=32, none_frac=0.1, scale2=0.02, b_std=0.1, seed=tp_n)
     sh = tpmod.DeviceShard(cuda, atlas, case, tp_n, r)
-    assert sh.n_local == 2176
+    assert sh.n_local == N // tp_n
     bufs = [cuda.full((M, N), 0x7FC0, dtype=cuda.int16, device="cuda") for _ in range(tp_n)]
     atlas.nvfp4_lora_linear(sh.desc(None, out_row_stride=N, y_dest=bufs, y_col_offset=r * sh.n_local))
     cuda.cuda.synchronize()
@@ -91,7 +91,7 @@ def test_eighth_of_configuration_1_shape(cuda, atlas, oracle):
     cols = np.arange(lo, hi, 7).astype(np.uint32)
     want = ideal(oracle, case, rows=rows, cols=cols)
     first = bits_from_dev(bufs[0])
-    assert_close(oracle, first[np.ix_(rows, cols)], want, "shard 5 of 8")
+    assert_close(oracle, first[np.ix_(rows, cols)], want, f"shard {r} of {tp_n}")
     assert (first[:, :lo] == 0x7FC0).all() and (first[:, hi:] == 0x7FC0).all()
     for b in bufs[1:]:
         assert np.array_equal(bits_from_dev(b), first)
