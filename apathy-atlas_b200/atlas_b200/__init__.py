@@ -24,11 +24,12 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libatlas_b200.so")
 
 VARIANT_NONE, VARIANT_SIMT, VARIANT_TCGEN05 = 0, 1, 2
 FLAG_FORCE_SIMT, FLAG_FORCE_TCGEN05, FLAG_STAGED_LORA, FLAG_REUSE_SHRINK, FLAG_ACT_FP4, FLAG_NO_CTA_PAIR, FLAG_NO_K_SPLIT = 1, 2, 4, 8, 16, 32, 64
+FLAG_NO_PERSISTENT, FLAG_TWO_TILE_PASS = 128, 256
 
 
 def lora_ws_bytes(m: int, max_loras: int, max_rank: int) -> int:
     """Scratch that lets the shrink hand the LoRA K-steps' activation tiles to the fused kernel (ATLAS_B200_LORA_WS_BYTES)."""
-    return (m + 255) // 256 * 256 * min(max_loras, 256) * ((max_rank + 15) // 16) * 32
+    return ((m + 255) // 256 * 256 + 256) * min(max_loras, 256) * ((max_rank + 15) // 16) * 32
 
 
 def act_fp4_ws_bytes(m: int, k: int) -> int:
@@ -42,8 +43,9 @@ EXPORTS = (
     "atlas_b200_nvfp4_lora_linear", "atlas_b200_nvfp4_lora_linear_noalloc", "atlas_b200_column_shard",
     "atlas_b200_build_seq_slot", "atlas_b200_routed_prefill_slot_of", "atlas_b200_peft_scaling",
     "atlas_b200_module_dims", "atlas_b200_pool_slot_bytes", "atlas_b200_slot_base_offset",
-    "atlas_b200_module_slot_offsets", "atlas_b200_pack_module", "atlas_b200_select_victim_slot",
-    "atlas_b200_device_status", "atlas_b200_last_variant", "atlas_b200_last_launch_shape", "atlas_b200_set_profile_buffer",
+    "atlas_b200_module_slot_offsets", "atlas_b200_pack_module", "atlas_b200_build_route_tables", "atlas_b200_select_victim_slot",
+    "atlas_b200_device_status", "atlas_b200_last_variant", "atlas_b200_last_launch_shape", "atlas_b200_last_persistent_shape",
+    "atlas_b200_set_profile_buffer",
     "atlas_b200_version",
 )
 
@@ -110,6 +112,7 @@ def lib() -> C.CDLL:
     L.atlas_b200_slot_base_offset.restype = sz
     L.atlas_b200_module_slot_offsets.argtypes = [C.POINTER(ModelDims), sz, sz, C.c_int, C.POINTER(sz), C.POINTER(sz)]
     L.atlas_b200_pack_module.argtypes = [C.POINTER(ModelDims), sz, sz, C.c_int, vp, vp, sz, vp]
+    L.atlas_b200_build_route_tables.argtypes = [C.POINTER(ModelDims), sz, sz, C.c_int, C.c_uint64, sz, vp, vp, vp]
     L.atlas_b200_select_victim_slot.argtypes = [C.POINTER(sz), C.POINTER(C.c_uint8), C.POINTER(sz),
                                                 C.POINTER(C.c_uint64), sz]
     L.atlas_b200_device_status.argtypes = [C.POINTER(u32), C.c_int]
@@ -301,7 +304,10 @@ def last_launch_shape() -> dict:
     """Token tile, pairing, K split and LoRA-tile source of this thread's most recent tcgen05 launch."""
     out = (C.c_uint32 * 4)()
     _check("atlas_b200_last_launch_shape", lib().atlas_b200_last_launch_shape(out))
-    return {"token_tile": out[0], "cta_pair": bool(out[1]), "k_split": out[2], "lora_tiles_from_shrink": bool(out[3])}
+    per = (C.c_uint32 * 2)()
+    _check("atlas_b200_last_persistent_shape", lib().atlas_b200_last_persistent_shape(per))
+    return {"token_tile": out[0], "cta_pair": bool(out[1]), "k_split": out[2], "lora_tiles_from_shrink": bool(out[3]),
+            "persistent_tiles_per_pass": per[0], "persistent_cta_pairs": per[1]}
 
 
 def device_status(clear: bool = True) -> int:

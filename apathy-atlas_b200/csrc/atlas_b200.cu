@@ -19,13 +19,14 @@
 
 #include "common.cuh"
 #include "kernel_tc.cuh"
+#include "kernel_tc_persist.cuh"
 #include "kernels_simt.cuh"
 #include "kernel_shrink_mma.cuh"
 
 namespace atlas {
 
 static thread_local int t_last_variant = ATLAS_B200_VARIANT_NONE;
-static thread_local uint32_t t_last_shape[4] = {0, 0, 0, 0};
+static thread_local uint32_t t_last_shape[6] = {0, 0, 0, 0, 0, 0};
 static unsigned long long* g_profile_buf = nullptr;   // device buffer for per-CTA cycle counters (diagnostics)
 static size_t g_profile_words = 0;
 
@@ -41,33 +42,50 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-struct Runtime {
+// What the launcher learns about a device and the per-device settings it has applied.  Function attributes
+// (opt-in shared memory, carve-out) and occupancy answers belong to a device, so everything here is kept per
+// device ordinal and created under a lock the first time that device is current in a call.
+constexpr int kMaxDevices = 64;
+constexpr int kPersistKernels = 3;
+struct DeviceState {
+    bool ready = false;
     bool sm100 = false;
     int sm_count = 148;
-    EncodeTiledFn encode = nullptr;
     bool tc_attr_set[20] = {};        // token tiles 16..256 x {A16, A4} x {single CTA, CTA pair}
+    int known_clusters[20][9] = {};   // resident clusters per kernel instance and K split; 0 = not asked yet
+    bool persist_attr_set[kPersistKernels] = {};
+    int persist_clusters[kPersistKernels] = {};
+    bool carveout_set = false;
 };
+static DeviceState g_dev[kMaxDevices];
+static std::mutex g_dev_mutex;
+static EncodeTiledFn g_encode = nullptr;
 
-static Runtime& runtime() {
-    static Runtime rt;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return;
+// state of the current device; nullptr when there is none (no driver, ordinal out of range)
+static DeviceState* device_state() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { (void)cudaGetLastError(); return nullptr; }
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DeviceState& st = g_dev[dev];
+    if (!st.ready) {
         int major = 0;
         cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-        rt.sm100 = (major == 10);
-        cudaDeviceGetAttribute(&rt.sm_count, cudaDevAttrMultiProcessorCount, dev);
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            rt.encode = reinterpret_cast<EncodeTiledFn>(fn);
-    });
-    return rt;
+        st.sm100 = (major == 10);
+        cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (st.sm_count <= 0) st.sm_count = 148;
+        if (!g_encode) {
+            void* fn = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+                q == cudaDriverEntryPointSuccess)
+                g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+        }
+        st.ready = true;
+    }
+    return &st;
 }
 
-static int rt_sm_count() { return runtime().sm_count > 0 ? runtime().sm_count : 148; }
+static int rt_sm_count() { DeviceState* st = device_state(); return st ? st->sm_count : 148; }
 
 static bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem, const void* base, uint64_t inner,
                       uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
@@ -77,7 +95,7 @@ static bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem, con
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
     (void)elem;
-    return runtime().encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    return g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                             swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -97,11 +115,11 @@ static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool
     if (p.M == 0 || p.max_rank == 0) return ATLAS_B200_OK;
     // Same shared-memory carve-out as the tcgen05 kernel, so that kernel's CTAs can become resident
     // next to this grid's instead of waiting for the SMs to drain and be reconfigured.
-    static bool carveout_set = false;
-    if (!carveout_set) {
+    DeviceState* dst = device_state();
+    if (dst && !dst->carveout_set) {
         cudaFuncSetAttribute(lora_shrink_grouped_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         cudaFuncSetAttribute(lora_shrink_mma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        carveout_set = true;
+        dst->carveout_set = true;
     }
     const bool mma_ok = shrink_takes_mma_path(p);
     if (p.tile_out && !mma_ok) return ATLAS_B200_ERR_DIMS;      // tile output exists in the tensor-core shrink only
@@ -219,8 +237,8 @@ static int launch_simt_linear(const atlas_b200_linear_desc& d, cudaStream_t st) 
 
 // Shapes the tcgen05 path takes.  Everything here is a property of host-visible arguments.
 static bool tc_eligible(const atlas_b200_linear_desc& d) {
-    Runtime& rt = runtime();
-    if (!rt.sm100 || !rt.encode) return false;
+    DeviceState* dst = device_state();
+    if (!dst || !dst->sm100 || !g_encode) return false;
     if (d.w_bf16) return false;                                   // dense base: CUDA-core path
     if (d.k % tc::KRAW != 0) return false;                        // TMA row strides of codes and scales: 16-byte multiples
     if (d.x_row_stride % 8 != 0) return false;
@@ -252,24 +270,102 @@ struct TTiles {
     uint32_t part_rows = 0;    // rows of a block: the token tile, or half of it for CTA pairs
 };
 
+// The six tensor maps of a tcgen05 launch.  `xrows` = token rows of an activation tile one CTA stages, `mt` = token
+// tile, `l_gran_t` = bytes of one masked-t block as the shrink writes it ([part_rows x 16] BF16).
+struct TcMaps { CUtensorMap x, w, s, b, xs, t; };
+
+static int encode_tc_maps(const atlas_b200_linear_desc& d, bool a4, uint32_t xrows, uint32_t mt, uint32_t l_gran_t,
+                          const TTiles& tt, TcMaps& m) {
+    if (a4) {
+        // the quantised activations in `ws`, in the weights' own layout
+        const uint8_t* codes = static_cast<const uint8_t*>(d.ws);
+        if (!encode_2d(&m.x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, d.k / 2, d.m, d.k / 2, tc::KRAW / 2, xrows,
+                       CU_TENSOR_MAP_SWIZZLE_128B))
+            return ATLAS_B200_ERR_DIMS;
+        if (!encode_2d(&m.xs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes + act_fp4_codes_bytes(d), d.k / 16, d.m, d.k / 16,
+                       tc::KRAW / 16, mt, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return ATLAS_B200_ERR_DIMS;
+    } else if (!encode_2d(&m.x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.x, d.k, d.m, uint64_t(d.x_row_stride) * 2, tc::KB, xrows,
+                          CU_TENSOR_MAP_SWIZZLE_128B))
+        return ATLAS_B200_ERR_DIMS;
+    if (!encode_2d(&m.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.w_packed, d.k / 2, d.n, d.k / 2, tc::KRAW / 2, tc::FT,
+                   CU_TENSOR_MAP_SWIZZLE_128B))
+        return ATLAS_B200_ERR_DIMS;
+    if (!encode_2d(&m.s, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.w_scale, d.k / 16, d.n, d.k / 16, tc::KRAW / 16, tc::FT,
+                   CU_TENSOR_MAP_SWIZZLE_NONE))
+        return ATLAS_B200_ERR_DIMS;
+
+    // B side of the adapter pool as one 3-D tensor [max_loras][n][max_rank]: box = one granule of one slot
+    if (b_pool_is_strided(d)) {
+        const cuuint64_t dims[3] = {d.max_rank, d.n, d.max_loras};
+        const cuuint64_t strides[2] = {uint64_t(d.max_rank) * 2, uint64_t(d.b_slot_stride)};
+        const cuuint32_t box[3] = {16, tc::FT, 1};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        if (g_encode(&m.b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(d.b_pool_base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return ATLAS_B200_ERR_DIMS;
+    } else {
+        m.b = m.s;   // never dereferenced
+    }
+    if (!a4) m.xs = m.s;   // never dereferenced
+    if (tt.tiles) {
+        // the masked-t blocks are shared-memory images already: plain bytes, 256 to a row, one block per copy
+        const uint64_t rows = uint64_t((d.m + mt - 1) / mt) * tt.cap * mt * 32 / 256;
+        if (l_gran_t % 256 != 0 ||
+            !encode_2d(&m.t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, tt.tiles, 256, rows, 256, 256, l_gran_t / 256, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return ATLAS_B200_ERR_DIMS;
+    } else {
+        m.t = m.s;         // never dereferenced
+    }
+    return ATLAS_B200_OK;
+}
+
+// the launch constants both tcgen05 kernels share
+static int fill_tc_params(const atlas_b200_linear_desc& d, bool a4, bool b_strided, const TTiles& tt, tc::Params& p) {
+    p.b_pool_strided = b_strided ? 1u : 0u;
+    p.t_tile_cap = tt.tiles ? tt.cap : 0u;
+    p.seq_slot = d.seq_slot;
+    p.a_table = d.a_table;
+    p.b_table = d.b_table;
+    p.rank_table = d.rank_table;
+    p.t = static_cast<const uint16_t*>(d.lora_t);
+    p.y = static_cast<uint16_t*>(d.y);
+    p.n_dest = d.n_dest ? d.n_dest : 1u;
+    p.y_col0 = d.n_dest ? d.y_col_offset : 0u;
+    bool rows_16b = d.out_row_stride % 8 == 0 && p.y_col0 % 8 == 0;
+    for (uint32_t r = 0; r < p.n_dest; ++r) {
+        p.y_dest[r] = static_cast<uint16_t*>(d.n_dest ? d.y_dest[r] : d.y);
+        rows_16b = rows_16b && aligned(p.y_dest[r], 16);
+    }
+    if (d.n_dest && !rows_16b) return ATLAS_B200_ERR_ALIGN;
+    p.staged_epilogue = rows_16b ? 1u : 0u;
+    p.M = d.m; p.N = d.n; p.K = d.k; p.out_row_stride = d.out_row_stride;
+    p.max_loras = d.max_loras; p.max_rank = d.max_rank;
+    p.out_scale = a4 ? d.scale2 : d.scale2 * kWeightPreScale;
+    p.k_split = 1;
+    return ATLAS_B200_OK;
+}
+
 // How many clusters of (PAIR ? 2 : 1) x 1 x k_split CTAs of one kernel instance can be resident at once.  Clusters live
 // inside one GPC, so fewer fit than the SM count suggests.  An occupancy query, answered by the runtime without touching
 // the device; asked once per shape.  -1: the query failed.
 template <int MT, bool A4, bool PAIR>
 static int tc_active_clusters(int slot_idx, uint32_t k_split) {
     using C = tc::Cfg<MT, A4, PAIR>;
-    Runtime& rt = runtime();
+    DeviceState* dst = device_state();
+    if (!dst) return -1;
     slot_idx += (A4 ? 5 : 0) + (PAIR ? 10 : 0);
-    static int known[20][9] = {};                   // 0 = not asked yet
+    int (&known)[20][9] = dst->known_clusters;
     if (k_split > 8) return -1;
     if (known[slot_idx][k_split] == 0) {
-        if (!rt.tc_attr_set[slot_idx]) {
+        if (!dst->tc_attr_set[slot_idx]) {
             if (cudaFuncSetAttribute(tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      C::SMEM_BYTES) != cudaSuccess) {
                 (void)cudaGetLastError();
                 return -1;
             }
-            rt.tc_attr_set[slot_idx] = true;
+            dst->tc_attr_set[slot_idx] = true;
         }
         cudaLaunchConfig_t q{};
         q.gridDim = dim3(PAIR ? 2 : 1, 1, k_split);
@@ -304,80 +400,28 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, const Shrink
                      uint32_t k_split, cudaStream_t st) {
     const bool after_shrink = shrink != nullptr;     // the shrink is launched from here, once the launch shape is final
     using C = tc::Cfg<MT, A4, PAIR>;
-    Runtime& rt = runtime();
+    DeviceState* dst = device_state();
+    if (!dst) return ATLAS_B200_ERR_ARCH;
     slot_idx += (A4 ? 5 : 0) + (PAIR ? 10 : 0);
-    if (!rt.tc_attr_set[slot_idx]) {
+    if (!dst->tc_attr_set[slot_idx]) {
         cudaError_t e = cudaFuncSetAttribute(tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return cuda_status(e);
-        rt.tc_attr_set[slot_idx] = true;
+        dst->tc_attr_set[slot_idx] = true;
     }
-    CUtensorMap map_x, map_w, map_s, map_b, map_xs, map_t;
-    if (A4) {
-        // the quantised activations in `ws`, in the weights' own layout
-        const uint8_t* codes = static_cast<const uint8_t*>(d.ws);
-        if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, d.k / 2, d.m, d.k / 2, tc::KRAW / 2, C::XROWS,
-                       CU_TENSOR_MAP_SWIZZLE_128B))
-            return ATLAS_B200_ERR_DIMS;
-        if (!encode_2d(&map_xs, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes + act_fp4_codes_bytes(d), d.k / 16, d.m, d.k / 16,
-                       tc::KRAW / 16, MT, CU_TENSOR_MAP_SWIZZLE_NONE))
-            return ATLAS_B200_ERR_DIMS;
-    } else if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.x, d.k, d.m, uint64_t(d.x_row_stride) * 2, tc::KB, C::XROWS,
-                          CU_TENSOR_MAP_SWIZZLE_128B))
-        return ATLAS_B200_ERR_DIMS;
-    if (!encode_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.w_packed, d.k / 2, d.n, d.k / 2, tc::KRAW / 2, tc::FT,
-                   CU_TENSOR_MAP_SWIZZLE_128B))
-        return ATLAS_B200_ERR_DIMS;
-    if (!encode_2d(&map_s, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d.w_scale, d.k / 16, d.n, d.k / 16, tc::KRAW / 16, tc::FT,
-                   CU_TENSOR_MAP_SWIZZLE_NONE))
-        return ATLAS_B200_ERR_DIMS;
-
-    // B side of the adapter pool as one 3-D tensor [max_loras][n][max_rank]: box = one granule of one slot
+    TcMaps maps;
     const bool b_strided = b_pool_is_strided(d);
-    if (b_strided) {
-        const cuuint64_t dims[3] = {d.max_rank, d.n, d.max_loras};
-        const cuuint64_t strides[2] = {uint64_t(d.max_rank) * 2, uint64_t(d.b_slot_stride)};
-        const cuuint32_t box[3] = {16, tc::FT, 1};
-        const cuuint32_t estr[3] = {1, 1, 1};
-        if (rt.encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(d.b_pool_base), dims, strides, box, estr,
-                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return ATLAS_B200_ERR_DIMS;
-    } else {
-        map_b = map_s;   // never dereferenced
+    {
+        const int rc = encode_tc_maps(d, A4, C::XROWS, MT, C::L_GRAN_T, tt, maps);
+        if (rc) return rc;
     }
-    if (!A4) map_xs = map_s;   // never dereferenced
-    if (tt.tiles) {
-        // the masked-t blocks are shared-memory images already: plain bytes, 256 to a row, one block per copy
-        static_assert(C::L_GRAN_T % 256 == 0, "a block is a whole number of 256-byte rows");
-        const uint64_t rows = uint64_t((d.m + MT - 1) / MT) * tt.cap * MT * 32 / 256;
-        if (!encode_2d(&map_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, tt.tiles, 256, rows, 256, 256, C::L_GRAN_T / 256, CU_TENSOR_MAP_SWIZZLE_NONE))
-            return ATLAS_B200_ERR_DIMS;
-    } else {
-        map_t = map_s;         // never dereferenced
-    }
+    const CUtensorMap &map_x = maps.x, &map_w = maps.w, &map_s = maps.s, &map_b = maps.b, &map_xs = maps.xs, &map_t = maps.t;
 
     tc::Params p{};
-    p.b_pool_strided = b_strided ? 1u : 0u;
-    p.t_tile_cap = tt.tiles ? tt.cap : 0u;
-    p.seq_slot = d.seq_slot;
-    p.a_table = d.a_table;
-    p.b_table = d.b_table;
-    p.rank_table = d.rank_table;
-    p.t = static_cast<const uint16_t*>(d.lora_t);
-    p.y = static_cast<uint16_t*>(d.y);
-    p.n_dest = d.n_dest ? d.n_dest : 1u;
-    p.y_col0 = d.n_dest ? d.y_col_offset : 0u;
-    bool rows_16b = d.out_row_stride % 8 == 0 && p.y_col0 % 8 == 0;
-    for (uint32_t r = 0; r < p.n_dest; ++r) {
-        p.y_dest[r] = static_cast<uint16_t*>(d.n_dest ? d.y_dest[r] : d.y);
-        rows_16b = rows_16b && aligned(p.y_dest[r], 16);
+    {
+        const int rc = fill_tc_params(d, A4, b_strided, tt, p);
+        if (rc) return rc;
     }
-    if (d.n_dest && !rows_16b) return ATLAS_B200_ERR_ALIGN;
-    p.staged_epilogue = rows_16b ? 1u : 0u;
-    p.M = d.m; p.N = d.n; p.K = d.k; p.out_row_stride = d.out_row_stride;
-    p.max_loras = d.max_loras; p.max_rank = d.max_rank;
-    p.out_scale = A4 ? d.scale2 : d.scale2 * kWeightPreScale;
     dim3 grid((d.n + tc::FT - 1) / tc::FT, (d.m + MT - 1) / MT);
     if (PAIR) grid.x = (grid.x + 1u) & ~1u;      // whole pairs: a CTA past the last feature loads zeros and stores nothing
     // split K: k_split CTAs along z form a cluster (times two for pairs), share one tile and exchange partial sums;
@@ -388,6 +432,7 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, const Shrink
     grid.z = k_split;
     p.k_split = k_split;
     t_last_shape[0] = MT; t_last_shape[1] = PAIR ? 1u : 0u; t_last_shape[2] = k_split; t_last_shape[3] = tt.tiles ? 1u : 0u;
+    t_last_shape[4] = 0u; t_last_shape[5] = 0u;
     if (shrink) {
         // A small batch: let this kernel start under the shrink.  A large one: the shrink is a sizeable grid that
         // should have the whole machine first; this kernel then follows it.
@@ -423,6 +468,101 @@ static int launch_tc(const atlas_b200_linear_desc& d, int slot_idx, const Shrink
     cfg.numAttrs = n_attr;
     p.wait_for_shrink = after_shrink ? 1u : 0u;
     return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_kernel<MT, A4, PAIR>, map_x, map_w, map_s, map_b, map_xs, map_t, p));
+}
+
+// ---- the persistent form (kernel_tc_persist.cuh): one cluster of two CTAs per pair of SMs, a static tile loop ----
+// instance index: 0 = <256, 1, A16>, 1 = <256, 1, A4>, 2 = <192, 2, A16>
+template <int MT, int G, bool A4>
+static int persist_resident_clusters(int idx) {
+    using C = tc::PCfg<MT, G, A4>;
+    DeviceState* dst = device_state();
+    if (!dst) return -1;
+    if (dst->persist_clusters[idx] == 0) {
+        if (!dst->persist_attr_set[idx]) {
+            if (cudaFuncSetAttribute(tc::nvfp4_lora_linear_tc_persistent_kernel<MT, G, A4>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return -1;
+            }
+            dst->persist_attr_set[idx] = true;
+        }
+        cudaLaunchConfig_t q{};
+        q.gridDim = dim3(2, 1, 1);
+        q.blockDim = dim3(tc::P_NUM_THREADS);
+        q.dynamicSmemBytes = C::SMEM_BYTES;
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = 2;
+        qa[0].val.clusterDim.y = 1;
+        qa[0].val.clusterDim.z = 1;
+        q.attrs = qa;
+        q.numAttrs = 1;
+        int n = 0;
+        dst->persist_clusters[idx] =
+            cudaOccupancyMaxActiveClusters(&n, tc::nvfp4_lora_linear_tc_persistent_kernel<MT, G, A4>, &q) == cudaSuccess && n > 0 ? n : -1;
+        (void)cudaGetLastError();
+    }
+    return dst->persist_clusters[idx];
+}
+
+// tiles of one launch: pairs of feature tiles x token passes
+template <int MT, int G>
+static uint32_t persist_tiles(const atlas_b200_linear_desc& d) {
+    const uint32_t n_fpairs = ((d.n + tc::FT - 1) / tc::FT + 1) / 2;
+    const uint32_t n_passes = (d.m + MT * G - 1) / (MT * G);
+    return n_fpairs * n_passes;
+}
+
+template <int MT, int G, bool A4>
+static int launch_tc_persist(const atlas_b200_linear_desc& d, int idx, const ShrinkParams* shrink, const TTiles& tt, cudaStream_t st) {
+    using C = tc::PCfg<MT, G, A4>;
+    const int clusters = persist_resident_clusters<MT, G, A4>(idx);
+    if (clusters <= 0) return ATLAS_B200_ERR_DIMS;
+    TcMaps maps;
+    {
+        const int rc = encode_tc_maps(d, A4, C::XROWS, MT, C::L_GRAN_T, tt, maps);
+        if (rc) return rc;
+    }
+    tc::Params p{};
+    {
+        const int rc = fill_tc_params(d, A4, b_pool_is_strided(d), tt, p);
+        if (rc) return rc;
+    }
+    if (!p.staged_epilogue) return ATLAS_B200_ERR_ALIGN;
+    tc::PParams pp{};
+    pp.n_fpairs = ((d.n + tc::FT - 1) / tc::FT + 1) / 2;
+    pp.n_passes = (d.m + MT * G - 1) / (MT * G);
+    pp.n_tiles = pp.n_fpairs * pp.n_passes;
+    const uint32_t pairs = std::min<uint32_t>(uint32_t(clusters), pp.n_tiles);
+    t_last_shape[0] = MT; t_last_shape[1] = 1u; t_last_shape[2] = 1u; t_last_shape[3] = tt.tiles ? 1u : 0u;
+    t_last_shape[4] = uint32_t(G); t_last_shape[5] = pairs;
+    if (shrink) {
+        const int rc = launch_shrink(*shrink, d.max_loras, st, d.m <= 1024, false);
+        if (rc) return rc;
+    }
+    p.profile = (g_profile_buf && size_t(pairs) * 2 * tc::PROFILE_WORDS <= g_profile_words) ? g_profile_buf : nullptr;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(pairs * 2, 1, 1);
+    cfg.blockDim = dim3(tc::P_NUM_THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    unsigned n_attr = 0;
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 2;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+    if (shrink) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    p.wait_for_shrink = shrink ? 1u : 0u;
+    return cuda_status(cudaLaunchKernelEx(&cfg, tc::nvfp4_lora_linear_tc_persistent_kernel<MT, G, A4>, maps.x, maps.w, maps.s, maps.b,
+                                          maps.xs, maps.t, p, pp));
 }
 
 static int validate_linear(const atlas_b200_linear_desc& d) {
@@ -532,7 +672,50 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
                 sp.part_rows = tt.part_rows = pair ? mt / 2 : mt;
             }
         }
+        // Many tiles per SM pair (a prefill batch): the persistent form, whose operand rings run across tile
+        // boundaries and whose row stores overlap the next tile's K loop.  It takes 256-token tiles of CTA pairs
+        // without a K split, 16-byte aligned destination rows, and LoRA operands that both come by TMA.
+        bool persistent = mt == 256 && pair && k_split == 1 && !(d.flags & ATLAS_B200_FLAG_NO_PERSISTENT) &&
+                          (!d.seq_slot || b_pool_is_strided(d)) && d.out_row_stride % 8 == 0 &&
+                          (d.n_dest ? d.y_col_offset % 8 == 0 : aligned(d.y, 16));
+        for (uint32_t r = 0; persistent && r < d.n_dest; ++r) persistent = aligned(d.y_dest[r], 16);
+        // two token tiles of 192 per pass (the expanded weight operand is used twice) where the batch has several passes
+        const bool two_tiles = persistent && !act_fp4 && (d.flags & ATLAS_B200_FLAG_TWO_TILE_PASS) && d.m >= 768;
+        if (persistent) {
+            const int clusters = act_fp4 ? persist_resident_clusters<256, 1, true>(1)
+                                         : (two_tiles ? persist_resident_clusters<192, 2, false>(2) : persist_resident_clusters<256, 1, false>(0));
+            const uint32_t tiles = two_tiles ? persist_tiles<192, 2>(d) : persist_tiles<256, 1>(d);
+            persistent = clusters > 0 && tiles >= 2u * uint32_t(clusters);
+        }
+        const uint32_t mt_tiles = (persistent && two_tiles) ? 192u : mt;     // token tile of the shrink's masked-t blocks
+        if (persistent && d.seq_slot) {
+            TTiles t2;
+            ShrinkParams sp2 = sp;
+            sp2.tile_out = nullptr;
+            if (d.ws && shrink_takes_mma_path(sp)) {
+                const size_t off = act_fp4 ? (act_fp4_ws_bytes(d) + 255) / 256 * 256 : 0;
+                const uint32_t cap = std::min(mt_tiles, d.max_loras) * ((d.max_rank + 15u) / 16u);
+                const size_t n_t = (d.m + mt_tiles - 1) / mt_tiles;
+                const size_t bytes = n_t * cap * mt_tiles * 32;
+                if (aligned(d.ws, 256) && d.ws_bytes >= off + bytes && n_t * cap * mt_tiles < (1ull << 31)) {
+                    t2.tiles = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(d.ws) + off);
+                    t2.cap = cap;
+                    sp2.tile_out = t2.tiles;
+                    sp2.tile_cap = cap;
+                    sp2.chunk = mt_tiles;
+                    sp2.part_rows = t2.part_rows = mt_tiles / 2;
+                }
+            }
+            if (t2.tiles) { tt = t2; sp = sp2; } else persistent = false;
+        }
         const ShrinkParams* shrink = (d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK)) ? &sp : nullptr;
+        if (persistent) {
+            if (act_fp4) rc = launch_tc_persist<256, 1, true>(d, 1, shrink, tt, st);
+            else if (two_tiles) rc = launch_tc_persist<192, 2, false>(d, 2, shrink, tt, st);
+            else rc = launch_tc_persist<256, 1, false>(d, 0, shrink, tt, st);
+            if (rc == ATLAS_B200_OK) t_last_variant = ATLAS_B200_VARIANT_TCGEN05;
+            return rc;
+        }
         if (act_fp4) {
             if (mt == 16) rc = launch_tc<16, true, false>(d, 0, shrink, tt, k_split, st);
             else if (mt == 32) rc = launch_tc<32, true, false>(d, 1, shrink, tt, k_split, st);
@@ -631,7 +814,7 @@ int atlas_b200_quantize_bf16_to_nvfp4(const void* in_bf16, void* packed, void* s
     if (!in_bf16 || !packed || !scales) return ATLAS_B200_ERR_NULL;
     if (k % 16 != 0) return ATLAS_B200_ERR_DIMS;
     const size_t groups = size_t(n) * (k / 16);
-    const unsigned blocks = unsigned(std::min<size_t>((groups + 255) / 256, 148 * 16));
+    const unsigned blocks = unsigned(std::min<size_t>((groups + 255) / 256, size_t(rt_sm_count()) * 16));
     const uint32_t vec = aligned(in_bf16, 16) && aligned(packed, 8) && k % 16 == 0;
     quantize_nvfp4_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(in_bf16), static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales), scale2, n, k, k, vec);
@@ -661,7 +844,6 @@ static __device__ __align__(256) uint16_t g_static_lora_t[ATLAS_B200_STATIC_SCRA
 namespace atlas {
 // In host code `g_static_lora_t` names a host-side shadow of the symbol, not device memory, so the
 // device address is asked for once per device, with that device current, and cached.
-static constexpr int kMaxDevices = 64;
 static void* g_static_scratch_addr[kMaxDevices] = {};
 static std::mutex g_static_scratch_mutex;
 
@@ -717,6 +899,13 @@ int atlas_b200_last_variant(void) { return t_last_variant; }
 int atlas_b200_last_launch_shape(uint32_t out[4]) {
     if (!out) return ATLAS_B200_ERR_NULL;
     for (int i = 0; i < 4; ++i) out[i] = t_last_shape[i];
+    return ATLAS_B200_OK;
+}
+
+int atlas_b200_last_persistent_shape(uint32_t out[2]) {
+    if (!out) return ATLAS_B200_ERR_NULL;
+    out[0] = t_last_shape[4];
+    out[1] = t_last_shape[5];
     return ATLAS_B200_OK;
 }
 

@@ -118,6 +118,22 @@ int atlas_b200_pack_module(const atlas_b200_model_dims* cfg, size_t max_rank, si
     return ATLAS_B200_OK;
 }
 
+int atlas_b200_build_route_tables(const atlas_b200_model_dims* cfg, size_t max_rank, size_t layer_ordinal, int module,
+                                  uint64_t pool_base, size_t max_loras, const uint8_t* present,
+                                  uint64_t* a_table, uint64_t* b_table) {
+    if (!cfg || !a_table || !b_table) return ATLAS_B200_ERR_NULL;
+    size_t a_off = 0, b_off = 0;
+    const int st = atlas_b200_module_slot_offsets(cfg, max_rank, layer_ordinal, module, &a_off, &b_off);
+    if (st != ATLAS_B200_OK) return st;
+    const size_t slot_bytes = atlas_b200_pool_slot_bytes(cfg, max_rank);
+    for (size_t s = 0; s < max_loras; ++s) {
+        const bool on = pool_base != 0 && (!present || present[s]);
+        a_table[s] = on ? pool_base + s * slot_bytes + a_off : 0;     // 0 = base only for this slot
+        b_table[s] = on ? pool_base + s * slot_bytes + b_off : 0;
+    }
+    return ATLAS_B200_OK;
+}
+
 int atlas_b200_select_victim_slot(const size_t* slot_index, const uint8_t* filled, const size_t* ref_count,
                                   const uint64_t* last_used, size_t count) {
     if (count && (!slot_index || !filled || !ref_count || !last_used)) return ATLAS_B200_ERR_NULL;

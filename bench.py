@@ -1,22 +1,28 @@
 #!/usr/bin/env python
 """Benchmark of the fused NVFP4 + multi-LoRA linear layer.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload config1] [--impl reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload config3-layer] [--impl reference]
 
-One step = one pass of the layer over one synthetic batch.  The default workload is benchmark
-configuration 1 (NVFP4 base K=5120 N=17408, 256 tokens, 16 adapters of rank 32, 10 % of the tokens
-adapter-less).  With N > 1 (launched by torch.distributed.run, one rank per GPU) the same layer is
-split column-parallel over the ranks — W, its scales and every B_s by output rows; x and A_s
-replicated: strong scaling.  Every rank's kernel stores its output tiles straight into all ranks' gathered
-[M, N] buffers over NVLink (peer mappings from torch's symmetric memory), so the exchange overlaps the
-compute tile by tile and what remains of the collective is one device-side barrier; `--collective nccl`
-(or a box where the peer mapping cannot be made) runs the layer followed by one NCCL all-gather instead.
+One step = one pass of every projection of the workload over one synthetic token batch, one fused call
+(shrink + tcgen05 kernel) per projection.  The default workload is the 8B-shape multi-adapter prefill layer:
+q/k/v/o/gate/up/down NVFP4 linears of a Llama-3-8B-shaped layer (hidden 4096, intermediate 14336, GQA 32/8,
+head_dim 128), 8192 tokens in 32 contiguous segments of random length, 8 adapters of rank 64 on all seven
+projections, the adapters in one slot-major pool laid out as the reference lays its pool out.  Other workloads:
+config4-mlp (70B-shaped gate/up/down, 512 tokens, 128 adapters of rank 16 with Zipf ids), config2-qkv (decode batch,
+q/k/v LoRA modules into column segments of one fused-QKV output) and the single linears config0..config4.
 
-Rank 0 prints one JSON line.  `value` is device-timed (CUDA events on the launching stream, L2
-flushed between steps, inputs resident in HBM); `e2e` runs the same call with host buffers, with the
-H2D copy of the step's inputs and the D2H copy of its result inside the timed region.
-`--impl reference` times the CPU oracle (a scalar restatement of the reference's arithmetic — the
-reference itself is Rust + GB10 CUDA and has no CPU build of this path) on a bounded sample.
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every projection is split column-parallel over
+the ranks — W, its scales and every B_s by output rows; x, A_s and seq_slot replicated: strong scaling.  Every
+rank's kernel stores its output tiles straight into all ranks' gathered [M, N] buffers over NVLink (peer
+mappings from torch's symmetric memory), so the exchange overlaps the compute tile by tile and what remains of
+the collective is one device-side barrier per step; `--collective nccl` (or a box where the peer mapping cannot
+be made) runs the projections followed by one NCCL all-gather each instead.
+
+Rank 0 prints one JSON line.  `value` is device-timed (CUDA events on the launching stream, L2 flushed between
+steps, inputs resident in HBM); `e2e` runs the same calls with host buffers, with the H2D copies of the step's
+inputs and the D2H copies of its results inside the timed region.  `--impl reference` times the CPU oracle (a
+scalar restatement of the reference's launch sequence — the reference itself is Rust + GB10 CUDA and has no CPU
+build of this path) on a bounded row sample with all host threads.
 """
 import argparse
 import json
@@ -34,10 +40,17 @@ import numpy as np
 
 METRIC = "NVFP4+multi-LoRA linear tokens/s"
 FP4_PEAK_TFLOPS = 9000.0          # B200 dense NVFP4, nominal (no measured figure on this pool)
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the tcgen05 kernel, from the ncu captures
-# summarised under profiles/ (per workload; None where no capture exists)
-NCU_TRAFFIC_BYTES = {"config1": 72.9e6}
-WORKLOADS = {"config0": 0, "config1": 1, "config2": 2, "config3": 3, "config4": 4}
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel instance, from the ncu captures
+# summarised under profiles/ (per workload and activation mode; absent = no capture)
+NCU_TRAFFIC_BYTES = {("config1", "bf16"): 72.9e6}
+WORKLOADS = {
+    "config3-layer": dict(kind="layer", idx=3),
+    "config4-mlp": dict(kind="layer", idx=4),
+    "config2-qkv": dict(kind="layer", idx=2, fused_out=True),
+    "config0": dict(kind="single", idx=0), "config1": dict(kind="single", idx=1), "config2": dict(kind="single", idx=2),
+    "config3": dict(kind="single", idx=3), "config4": dict(kind="single", idx=4),
+}
+DEFAULT_WORKLOAD = "config3-layer"
 
 
 def peaks():
@@ -49,17 +62,58 @@ def peaks():
 
 
 def algorithmic_work(case):
-    """Bytes and flops of one pass, each tensor counted once (adapters at their true rank)."""
+    """Bytes and flops of one pass of one projection, each tensor counted once (adapters at their true rank)."""
     M, N, K = case.M, case.N, case.K
     w_bytes = N * K * 2 if case.w_bf16 is not None else N * K * (0.5 + 1.0 / 16.0)
-    hit = sorted(set(int(s) for s in case.seq_slot if s >= 0))
-    a_bytes = sum(case.adapters[s].rank * K * 2 for s in hit)
-    b_bytes = sum(case.adapters[s].rank * N * 2 for s in hit)
+    slots = np.asarray(case.seq_slot)
+    hit, counts = np.unique(slots[slots >= 0], return_counts=True)
+    a_bytes = sum(case.adapters[int(s)].rank * K * 2 for s in hit)
+    b_bytes = sum(case.adapters[int(s)].rank * N * 2 for s in hit)
     x_bytes, y_bytes, slot_bytes = M * K * 2, M * N * 2, 4 * M
-    flops = 2.0 * M * N * K + 2.0 * sum(case.adapters[int(s)].rank * (K + N) for s in case.seq_slot if s >= 0)
+    flops = 2.0 * M * N * K + 2.0 * sum(int(c) * case.adapters[int(s)].rank * (K + N) for s, c in zip(hit, counts))
     return dict(w=w_bytes, a=a_bytes, b=b_bytes, x=x_bytes, y=y_bytes, slot=slot_bytes,
                 total=w_bytes + a_bytes + b_bytes + x_bytes + y_bytes + slot_bytes, flops=flops,
                 main_kernel=w_bytes + b_bytes + x_bytes + y_bytes + slot_bytes)
+
+
+def total_work(cases):
+    w = [algorithmic_work(c) for c in cases]
+    return {k: sum(d[k] for d in w) for k in w[0]}
+
+
+class HostWork:
+    """The workload on the host: its projections (synth.Case each), their shared inputs and seq_slot."""
+
+    def __init__(self, name):
+        from atlas_b200 import synth
+        spec = WORKLOADS[name]
+        self.name, self.kind, self.fused_out = name, spec["kind"], bool(spec.get("fused_out"))
+        if self.kind == "layer":
+            self.layer = synth.layer_config(spec["idx"])
+            self.projections, self.inputs, self.seq_slot = self.layer.projections, self.layer.inputs, self.layer.seq_slot
+        else:
+            case = synth.baseline_config(spec["idx"])
+            case.meta = {"module": 0, "input": "x"}
+            self.layer = None
+            self.projections, self.inputs, self.seq_slot = [case], {"x": case.x}, case.seq_slot
+        self.M = self.projections[0].M
+        self.n_total = sum(c.N for c in self.projections)
+        self.nvfp4 = all(c.packed is not None for c in self.projections)
+
+    def config(self, args, tp):
+        c0 = self.projections[0]
+        slots = np.asarray(self.seq_slot)
+        return {"workload": self.name, "M": self.M,
+                "projections": [{"name": c.name.split("/")[-1], "K": c.K, "N": c.N} for c in self.projections],
+                "base": "nvfp4" if self.nvfp4 else "bf16",
+                "adapters": sum(a is not None for a in c0.adapters), "adapters_hit": int(len(np.unique(slots[slots >= 0]))),
+                "max_rank": c0.max_rank, "adapter_less_rows": int((slots < 0).sum()),
+                "segments": int((np.diff(slots) != 0).sum() + 1),
+                "adapter_pool": "slot-major pool, slot k at k * pool_slot_bytes (reference layout)" if self.kind == "layer"
+                                else "one-module pool",
+                "activation_mode": "A4 (x quantised to NVFP4)" if getattr(args, "activations", "bf16") == "fp4" else "A16 (exact BF16 x)",
+                "parallelism": (f"column-parallel tp{tp}, " + getattr(args, "collective_used", "all-gather")) if tp > 1 else "single GPU",
+                "l2": "flushed between timed steps", "seed": 1}
 
 
 class ClockSampler(threading.Thread):
@@ -85,65 +139,73 @@ class ClockSampler(threading.Thread):
     def stop(self):
         self._stop_evt.set()
         self.join(timeout=6)
-        sm, mx, reasons = [], 0.0, set()
+        sm, mx, reasons, power = [], 0.0, set(), []
         for r in self.rows:
             if len(r) < 7:
                 continue
             try:
-                sm.append(float(r[0])); mx = max(mx, float(r[1]))
+                sm.append(float(r[0])); mx = max(mx, float(r[1])); power.append(float(r[2]))
             except ValueError:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
 # --------------------------------------------------------------------------------------------------
 # CPU arm: the oracle on host cores
 # --------------------------------------------------------------------------------------------------
-def cpu_sample(case, budget_rows=None):
-    """Time the reference's launch sequence (base linear, then staged routed LoRA) on a row sample."""
+def cpu_sample(work, rows):
+    """The reference's launch sequence (base linear, then staged routed LoRA) for every projection of the workload,
+    on the first `rows` tokens, with every host thread.  Returns (step() -> seconds, rows, threads)."""
     from oracle import oracle_ctypes as oc
-    import copy
-    rows = budget_rows or max(1, min(case.M, int(2.5e10 / (case.N * case.K))))  # ~ 5-20 s of host work per pass
-    sub = copy.copy(case)
-    sub.M, sub.x, sub.seq_slot = rows, case.x[:rows].copy(), case.seq_slot[:rows].copy()
-    pool = oc.HostPool(case.K, case.N, case.max_rank, case.max_loras)
-    for s, ad in enumerate(case.adapters):
-        if ad is not None:
-            pool.pack(s, ad.a, ad.b, ad.scale)
-    kw = dict(packed=case.packed, scales=case.scales, scale2=case.scale2, w_bf16=case.w_bf16,
-              seq_slot=sub.seq_slot, pool=pool)
+    cores = oc.set_num_threads(0)          # launchers export OMP_NUM_THREADS=1; the baseline uses every core
+    rows = max(1, min(rows, work.M))
+    prepared = []
+    for c in work.projections:
+        pool = oc.HostPool(c.K, c.N, c.max_rank, c.max_loras)
+        for s, ad in enumerate(c.adapters):
+            if ad is not None:
+                pool.pack(s, ad.a, ad.b, ad.scale)
+        prepared.append((c, np.ascontiguousarray(c.x[:rows]), np.ascontiguousarray(c.seq_slot[:rows]), pool))
 
     def step():
         t0 = time.perf_counter()
-        oc.reference_sequence(sub.x, rows, case.N, case.K, **kw)
+        for c, x, slot, pool in prepared:
+            oc.reference_sequence(x, rows, c.N, c.K, packed=c.packed, scales=c.scales, scale2=c.scale2, w_bf16=c.w_bf16,
+                                  seq_slot=slot, pool=pool)
         return time.perf_counter() - t0
-    return step, rows, oc.num_threads()
+    return step, rows, cores
 
 
-def run_reference_arm(args, case):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+def default_cpu_rows(work):
+    """Rows whose pass costs the host a few seconds (about 1e9 multiply-adds per second and core)."""
+    macs_per_row = sum(c.N * c.K for c in work.projections)
+    return max(1, min(work.M, int(2.0e10 / macs_per_row)))
+
+
+def run_reference_arm(args, work):
+    """The CPU port of the reference's launch sequence, timed on this box's host cores: each step is one pass over a
+    fixed row sample of the workload; `ms_per_step` is the measured time of that sample, `value` = rows / time."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    # size the per-step sample so that the whole run stays near two minutes on this host
-    probe, probe_rows, _ = cpu_sample(case, budget_rows=min(4, case.M))
-    per_row = probe() / probe_rows
-    budget_rows = int(120.0 / max(args.steps + min(args.warmup, 1), 1) / max(per_row, 1e-9))
-    step, rows, cores = cpu_sample(case, budget_rows=max(1, min(case.M, budget_rows)))
-    for _ in range(min(args.warmup, 1)):
+    rows = args.cpu_rows or default_cpu_rows(work)
+    step, rows, cores = cpu_sample(work, rows)
+    for _ in range(args.warmup):
         step()
     times = [step() for _ in range(args.steps)]
     t = float(np.mean(times))
     tok_s = rows / t
-    sample = f"first {rows} of {case.M} tokens x all {case.N} outputs, every step"
+    sample = (f"first {rows} of {work.M} tokens x all outputs of all {len(work.projections)} projections, every step "
+              f"(ms_per_step is the measured time of that sample, not extrapolated)")
+    args.activations = "bf16"
     line = {
         "impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": t * 1e3 * case.M / rows,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args, case, 1),
+        "config": work.config(args, 1),
         "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -151,37 +213,63 @@ def run_reference_arm(args, case):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(args, case, tp):
-    hit = len(set(int(s) for s in case.seq_slot if s >= 0))
-    return {"workload": args.workload, "M": case.M, "K": case.K, "N": case.N, "base": "nvfp4" if case.packed is not None else "bf16",
-            "adapters": sum(a is not None for a in case.adapters), "adapters_hit": hit, "max_rank": case.max_rank,
-            "adapter_less_rows": int((case.seq_slot < 0).sum()), "activation_mode": "A4 (x quantised to NVFP4)" if getattr(args, "activations", "bf16") == "fp4" else "A16 (exact BF16 x)",
-            "parallelism": (f"column-parallel tp{tp}, " + getattr(args, "collective_used", "all-gather")) if tp > 1 else "single GPU",
-            "l2": "flushed between timed steps"}
-
-
 # --------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------
+class DevWork:
+    """The workload resident on this rank's GPU: per projection the column shard, its scratch and descriptors."""
+
+    def __init__(self, torch, ab, work, tp, rank):
+        from atlas_b200 import tp as tpmod
+        self.torch, self.ab, self.work, self.tp, self.rank = torch, ab, work, tp, rank
+        if work.kind == "layer":
+            self.dl = tpmod.DeviceLayer(torch, ab, work.layer, tp, rank)
+            self.inputs, self.seq_slot = self.dl.inputs, self.dl.seq_slot
+            self.n_local = [p["n_local"] for p in self.dl.proj]
+            self.local_cases = [self.dl.local_case(i) for i in range(len(self.n_local))]
+        else:
+            self.ds = tpmod.DeviceShard(torch, ab, work.projections[0], tp, rank)
+            self.inputs, self.seq_slot = {"x": self.ds.x}, self.ds.seq_slot
+            self.n_local = [self.ds.n_local]
+            self.local_cases = [self.ds.local_case]
+        self.n = len(self.n_local)
+
+    def desc(self, i, y, flags=0, x=None, seq_slot=None, **place):
+        if self.work.kind == "layer":
+            return self.dl.desc(i, y, extra_flags=flags, x=x, seq_slot=seq_slot, **place)
+        d = self.ds.desc(y, extra_flags=flags, **place)
+        if x is not None:
+            d.x = x.data_ptr()
+        if seq_slot is not None:
+            d.seq_slot = seq_slot.data_ptr()
+        return d
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="config1", choices=sorted(WORKLOADS))
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="atlas_b200", choices=["atlas_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU sample (0: sized for a few seconds per pass)")
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
                     help="N > 1: fused = the kernel's epilogue stores into every rank's buffer; nccl = all-gather after it")
     ap.add_argument("--activations", default="bf16", choices=["bf16", "fp4"],
                     help="bf16: the layer as specified (exact activations); fp4: the opt-in W4A4 mode as the timed step")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end loops (profiling runs)")
+    ap.add_argument("--no-other-mode", action="store_true", help="skip the secondary activation-mode timing (profiling runs)")
     args = ap.parse_args()
+    reference = args.impl == "reference"
+    if args.steps is None:
+        args.steps = 3 if reference else 30
+    if args.warmup is None:
+        args.warmup = 1 if reference else 5
 
-    from atlas_b200 import synth
-    case = synth.baseline_config(WORKLOADS[args.workload])
-
-    if args.impl == "reference":
-        run_reference_arm(args, case)
+    work = HostWork(args.workload)
+    if reference:
+        run_reference_arm(args, work)
         return
 
     # peer mappings without an NVLink multicast object bound to them (plain loads and stores only)
@@ -204,15 +292,27 @@ def main():
     assert args.warmup >= 3, "at least 3 warm-up steps"
     tp = world
     dev = torch.device("cuda", local_rank)
+    M = work.M
 
-    # ---- this rank's column shard, resident in HBM ----
-    from atlas_b200 import tp as tpmod
-    shard = tpmod.DeviceShard(torch, ab, case, tp, rank)
-    M, N, K, n_loc = case.M, case.N, case.K, shard.n_local
-    y_loc = torch.empty((M, n_loc), dtype=torch.bfloat16, device=dev)
-    y_all = torch.empty((tp, M, n_loc), dtype=torch.bfloat16, device=dev) if tp > 1 else None
-    # fused collective: every rank's [M, N] result buffer, mapped into every process
-    y_sym, sym_handle, collective_note = None, None, None
+    dw = DevWork(torch, ab, work, tp, rank)
+    n_proj = dw.n
+    # Output buffers.  One [M, n_local] per projection — or, for the fused-QKV workload, column segments of one
+    # [M, sum n_local] buffer (the reference's strided QKV layout).
+    cols0 = np.concatenate([[0], np.cumsum(dw.n_local)]).astype(int)
+    full_cols0 = np.concatenate([[0], np.cumsum([c.N for c in work.projections])]).astype(int)
+
+    def make_outputs():
+        if work.fused_out:
+            buf = torch.empty((M, int(cols0[-1])), dtype=torch.bfloat16, device=dev)
+            return [buf[:, cols0[i]:cols0[i + 1]] for i in range(n_proj)], buf
+        return [torch.empty((M, dw.n_local[i]), dtype=torch.bfloat16, device=dev) for i in range(n_proj)], None
+    y_loc, y_loc_buf = make_outputs()
+    loc_stride = int(cols0[-1]) if work.fused_out else None
+
+    # fused collective: every rank's gathered result buffers, mapped into every process.  Two sets, used in turn:
+    # a rank that has passed step i's barrier may start step i+1's stores while a slower rank still reads step i's
+    # result, so consecutive steps must not write the same buffers.
+    fused, sym_sets, collective_note = False, [], None
     if tp > 1 and args.collective == "fused":
         try:
             import torch.distributed._symmetric_memory as symm_mem
@@ -221,34 +321,55 @@ def main():
                     symm_mem.enable_symm_mem_for_group(dist.group.WORLD.group_name)
                 except Exception:
                     pass
-            y_sym = symm_mem.empty((M, N), dtype=torch.bfloat16, device=dev)
-            sym_handle = symm_mem.rendezvous(y_sym, dist.group.WORLD)
-            peer_ptrs = [int(p) for p in sym_handle.buffer_ptrs]
-            assert len(peer_ptrs) == tp and all(peer_ptrs)
+            for _ in range(2):
+                if work.fused_out:
+                    bufs = [symm_mem.empty((M, work.n_total), dtype=torch.bfloat16, device=dev)]
+                else:
+                    bufs = [symm_mem.empty((M, c.N), dtype=torch.bfloat16, device=dev) for c in work.projections]
+                handles = [symm_mem.rendezvous(b, dist.group.WORLD) for b in bufs]
+                ptrs = [[int(p) for p in h.buffer_ptrs] for h in handles]
+                assert all(len(p) == tp and all(p) for p in ptrs)
+                sym_sets.append(dict(bufs=bufs, handles=handles, ptrs=ptrs))
+            fused = True
         except Exception as e:                     # no peer mapping on this box: the NCCL path still measures the layer
             collective_note = f"peer mapping unavailable ({type(e).__name__}: {e}); NCCL all-gather used"
-            y_sym, sym_handle = None, None
-        ok = torch.tensor([1 if sym_handle is not None else 0], device=dev)
+        ok = torch.tensor([1 if fused else 0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if int(ok.item()) == 0:
-            y_sym, sym_handle = None, None
-    fused = sym_handle is not None
+        fused = bool(int(ok.item()))
+    y_all = ([torch.empty((tp, M, dw.n_local[i]), dtype=torch.bfloat16, device=dev) for i in range(n_proj)]
+             if tp > 1 else None)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > L2 (126 MB)
     mode = ab.FLAG_ACT_FP4 if args.activations == "fp4" else 0
-    place = dict(y_dest=peer_ptrs, y_col_offset=rank * n_loc, out_row_stride=N) if fused else {}
-    desc = shard.desc(y_loc, extra_flags=mode, **place)
-    desc_main_only = shard.desc(y_loc, extra_flags=mode | ab.FLAG_REUSE_SHRINK, **place)
-    # the other activation mode, timed beside the headline as a secondary figure
-    other = 0 if mode else ab.FLAG_ACT_FP4
-    desc_other = shard.desc(y_loc, extra_flags=other) if case.packed is not None and K % 256 == 0 else None
+
+    def build_descs(flags, sym=None, outs=None, x_of=None, seq_slot=None):
+        outs = outs or y_loc
+        ds = []
+        for i in range(n_proj):
+            xin = None if x_of is None else x_of[work.projections[i].meta["input"]]
+            if sym is not None:
+                j = 0 if work.fused_out else i
+                place = dict(y_dest=sym["ptrs"][j], out_row_stride=(work.n_total if work.fused_out else work.projections[i].N),
+                             y_col_offset=(int(full_cols0[i]) if work.fused_out else 0) + rank * dw.n_local[i])
+                ds.append(dw.desc(i, None, flags, x=xin, seq_slot=seq_slot, **place))
+            else:
+                ds.append(dw.desc(i, outs[i], flags, x=xin, seq_slot=seq_slot, out_row_stride=loc_stride))
+        return ds
+
+    descs = [build_descs(mode, s) for s in sym_sets] if fused else [build_descs(mode)]
+    descs_plain = build_descs(mode)                                    # this rank's shard into its own buffers, no placement
     stream = torch.cuda.current_stream()
+    step_no = [0]
 
     def step():
-        v = ab.nvfp4_lora_linear(desc, stream)
+        k = step_no[0] % len(descs)
+        step_no[0] += 1
+        v = None
+        for i in range(n_proj):
+            v = ab.nvfp4_lora_linear(descs[k][i], stream)
+            if tp > 1 and not fused:
+                dist.all_gather_into_tensor(y_all[i].view(tp * M, dw.n_local[i]), y_loc[i] if not work.fused_out else y_loc[i].contiguous())
         if fused:
-            sym_handle.barrier(channel=0)          # every rank's tiles have landed in every buffer
-        elif tp > 1:
-            dist.all_gather_into_tensor(y_all.view(tp * M, n_loc), y_loc)
+            sym_sets[k]["handles"][0].barrier(channel=0)     # every rank's tiles have landed in every buffer
         return v
 
     def barrier():
@@ -257,9 +378,11 @@ def main():
         torch.cuda.synchronize()
 
     if fused:
-        y_sym.view(torch.int16).fill_(0x7FC0)       # NaN pattern: the warm-up must overwrite all of it
+        for s in sym_sets:
+            for b in s["bufs"]:
+                b.view(torch.int16).fill_(0x7FC0)       # NaN pattern: the warm-up must overwrite all of it
     variant = None
-    for _ in range(args.warmup):
+    for _ in range(max(args.warmup, 2 * len(descs))):
         flush.fill_(1)
         variant = step()
     barrier()
@@ -267,10 +390,24 @@ def main():
     status = ab.device_status()
     if status != 0:
         raise RuntimeError(f"device status word {status:#x} after warm-up")
-    if variant != ab.VARIANT_TCGEN05 and case.packed is not None:
+    if variant != ab.VARIANT_TCGEN05 and work.nvfp4:
         raise RuntimeError("the tcgen05 path did not run for this workload")
-    if fused and not bool(torch.isfinite(y_sym.float()).all()):
-        raise RuntimeError("the gathered buffer still holds unwritten elements after the warm-up")
+
+    # ---- the gathered result, checked: every rank's buffers must equal the concatenation of the ranks' own
+    #      (unplaced) shard results, bit for bit; the shards travel by NCCL for this check only ----
+    if tp > 1:
+        for i in range(n_proj):
+            ab.nvfp4_lora_linear(descs_plain[i], stream)
+            mine = y_loc[i].contiguous()
+            dist.all_gather_into_tensor(y_all[i].view(tp * M, dw.n_local[i]), mine)
+        torch.cuda.synchronize()
+        if fused:
+            for s in sym_sets:
+                for i in range(n_proj):
+                    got = s["bufs"][0][:, int(full_cols0[i]):int(full_cols0[i + 1])] if work.fused_out else s["bufs"][i]
+                    want = y_all[i].permute(1, 0, 2).reshape(M, tp * dw.n_local[i])
+                    if not torch.equal(got.view(torch.int16), want.contiguous().view(torch.int16)):
+                        raise RuntimeError(f"rank {rank}: gathered buffer of projection {i} differs from the ranks' own shard results")
 
     # ---- device-timed steps ----
     sampler = ClockSampler(local_rank)
@@ -285,8 +422,22 @@ def main():
     barrier()
     step_ms = float(np.mean([a.elapsed_time(b) for a, b in ev]))
 
-    # ---- the dominant kernel alone (shrink result reused), for the roofline ----
-    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    # ---- per projection (fused call = shrink + main kernel), then the dominant kernel instance alone with the
+    #      shrink result reused: the roofline's kernel ----
+    n_sub = min(args.steps, 20)
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(n_proj + 1)] for _ in range(n_sub)]
+    for row in marks:
+        flush.fill_(1)
+        row[0].record(stream)
+        for i in range(n_proj):
+            ab.nvfp4_lora_linear(descs_plain[i], stream)
+            row[i + 1].record(stream)
+    barrier()
+    proj_ms = [float(np.mean([row[i].elapsed_time(row[i + 1]) for row in marks])) for i in range(n_proj)]
+    works_local = [algorithmic_work(c) for c in dw.local_cases]
+    dom = int(np.argmax([w["flops"] for w in works_local]))
+    desc_main_only = build_descs(mode | ab.FLAG_REUSE_SHRINK)[dom]
+    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_sub)]
     for a, b in ev2:
         flush.fill_(1)
         a.record(stream)
@@ -294,129 +445,158 @@ def main():
         b.record(stream)
     barrier()
     main_ms = float(np.mean([a.elapsed_time(b) for a, b in ev2]))
+    dom_shape = ab.last_launch_shape()
 
     # ---- the same step in the other activation mode (no collective), a secondary figure ----
     other_ms = float("nan")
-    if desc_other is not None:
+    other = 0 if mode else ab.FLAG_ACT_FP4
+    have_other = work.nvfp4 and all(c.K % 256 == 0 for c in work.projections) and not args.no_other_mode
+    if have_other:
+        descs_other = build_descs(other)
         for _ in range(3):
-            ab.nvfp4_lora_linear(desc_other, stream)
-        ev3 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(min(args.steps, 100))]
+            for d in descs_other:
+                ab.nvfp4_lora_linear(d, stream)
+        ev3 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_sub)]
         for a, b in ev3:
             flush.fill_(1)
             a.record(stream)
-            ab.nvfp4_lora_linear(desc_other, stream)
+            for d in descs_other:
+                ab.nvfp4_lora_linear(d, stream)
             b.record(stream)
         barrier()
         other_ms = float(np.mean([a.elapsed_time(b) for a, b in ev3]))
 
-    # ---- end to end through the C ABI with host buffers ----
-    x_host = torch.from_numpy(case.x.view(np.int16).copy()).pin_memory()
-    slot_host = torch.from_numpy(case.seq_slot.copy()).pin_memory()
-    y_host = torch.empty((tp, M, n_loc) if tp > 1 else (M, n_loc), dtype=torch.int16).pin_memory()
-    e2e_steps = max(3, min(args.steps, 20))
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        shard.x.view(torch.int16).copy_(x_host, non_blocking=True)
-        shard.seq_slot.copy_(slot_host, non_blocking=True)
-        step()
-        if rank == 0:
-            y_host.view(-1).copy_((y_sym if fused else (y_all if tp > 1 else y_loc)).view(torch.int16).view(-1), non_blocking=True)
-        barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    e2e_serial_ms = e2e_ms
+    # ---- end to end through the C ABI with host buffers: every step copies its inputs (every activation tensor and
+    #      seq_slot) from pinned host memory and copies its results back.  With N > 1 every rank copies the replicated
+    #      inputs to its own GPU and reads back its own column shard of every result. ----
+    e2e_ms = e2e_serial_ms = float("nan")
+    h2d = sum(int(v.size) * 2 for v in work.inputs.values()) + int(work.seq_slot.size) * 4
+    d2h = sum(M * n * 2 for n in dw.n_local)
+    if not args.no_e2e:
+        x_host = {k: torch.from_numpy(v.view(np.int16)).pin_memory() for k, v in work.inputs.items()}
+        slot_host = torch.from_numpy(work.seq_slot.astype(np.int32)).pin_memory()
+        y_host = [torch.empty((M, n), dtype=torch.int16).pin_memory() for n in dw.n_local]
 
-    # The same, as a serving loop would run it on one GPU: two sets of device buffers, the copy of step i+1's
-    # inputs and of step i-1's result on their own streams while step i computes.  Every step still carries its
-    # own H2D and D2H copy inside the timed region; what changes is that the three overlap.
-    if tp == 1:
-        n_buf = 2
-        e2e_steps = max(8, min(args.steps, 40))
-        xs = [torch.empty_like(shard.x) for _ in range(n_buf)]
-        slots = [torch.empty_like(shard.seq_slot) for _ in range(n_buf)]
-        ys = [torch.empty((M, n_loc), dtype=torch.bfloat16, device=dev) for _ in range(n_buf)]
-        y_hosts = [torch.empty((M, n_loc), dtype=torch.int16).pin_memory() for _ in range(n_buf)]
-        descs = []
-        for b in range(n_buf):
-            db = shard.desc(ys[b], extra_flags=mode)
-            db.x, db.seq_slot = xs[b].data_ptr(), slots[b].data_ptr()
-            descs.append(db)
-        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-        ev_in = [torch.cuda.Event() for _ in range(n_buf)]
-        ev_done = [torch.cuda.Event() for _ in range(n_buf)]
-        ev_out = [torch.cuda.Event() for _ in range(n_buf)]
+        def results(k):
+            if not fused:
+                return y_loc
+            s = sym_sets[k]
+            if work.fused_out:
+                return [s["bufs"][0][:, int(full_cols0[i]) + rank * dw.n_local[i]: int(full_cols0[i]) + (rank + 1) * dw.n_local[i]] for i in range(n_proj)]
+            return [s["bufs"][i][:, rank * dw.n_local[i]:(rank + 1) * dw.n_local[i]] for i in range(n_proj)]
+        e2e_steps = max(3, min(args.steps, 10))
         barrier()
         t0 = time.perf_counter()
-        for i in range(e2e_steps):
-            b = i % n_buf
-            with torch.cuda.stream(s_in):
-                s_in.wait_event(ev_done[b])            # the step that last read these input buffers has finished
-                xs[b].view(torch.int16).copy_(x_host, non_blocking=True)
-                slots[b].copy_(slot_host, non_blocking=True)
-                ev_in[b].record(s_in)
-            stream.wait_event(ev_in[b])
-            stream.wait_event(ev_out[b])               # the copy that last read this output buffer has finished
-            ab.nvfp4_lora_linear(descs[b], stream)
-            ev_done[b].record(stream)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_done[b])
-                y_hosts[b].copy_(ys[b].view(torch.int16), non_blocking=True)
-                ev_out[b].record(s_out)
-        torch.cuda.synchronize()
-        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-        if not np.array_equal(y_hosts[0].numpy(), y_hosts[1].numpy()):
-            raise RuntimeError("the two buffer sets of the end-to-end loop disagree")
+        for _ in range(e2e_steps):
+            for k_, t_ in dw.inputs.items():
+                t_.copy_(x_host[k_], non_blocking=True)
+            dw.seq_slot.copy_(slot_host, non_blocking=True)
+            k = step_no[0] % len(descs)
+            step()
+            for i, r_ in enumerate(results(k)):
+                y_host[i].copy_(r_.view(torch.int16), non_blocking=True)
+            barrier()
+        e2e_ms = e2e_serial_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+
+        # The same as a serving loop would run it on one GPU: two sets of device buffers, the copy of step i+1's
+        # inputs and of step i-1's results on their own streams while step i computes.  Every step still carries
+        # its own H2D and D2H copies inside the timed region; what changes is that the three overlap.
+        if tp == 1:
+            n_buf = 2
+            e2e_steps = max(6, min(args.steps, 16))
+            xs = [{k_: torch.empty_like(t_) for k_, t_ in dw.inputs.items()} for _ in range(n_buf)]
+            slots = [torch.empty_like(dw.seq_slot) for _ in range(n_buf)]
+            outs = [make_outputs()[0] for _ in range(n_buf)]
+            y_hosts = [[torch.empty((M, n), dtype=torch.int16).pin_memory() for n in dw.n_local] for _ in range(n_buf)]
+            dsets = [build_descs(mode, outs=outs[b], x_of=xs[b], seq_slot=slots[b]) for b in range(n_buf)]
+            s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+            ev_in = [torch.cuda.Event() for _ in range(n_buf)]
+            ev_done = [torch.cuda.Event() for _ in range(n_buf)]
+            ev_out = [torch.cuda.Event() for _ in range(n_buf)]
+            barrier()
+            t0 = time.perf_counter()
+            for it in range(e2e_steps):
+                b = it % n_buf
+                with torch.cuda.stream(s_in):
+                    s_in.wait_event(ev_done[b])            # the step that last read these input buffers has finished
+                    for k_ in xs[b]:
+                        xs[b][k_].copy_(x_host[k_], non_blocking=True)
+                    slots[b].copy_(slot_host, non_blocking=True)
+                    ev_in[b].record(s_in)
+                stream.wait_event(ev_in[b])
+                stream.wait_event(ev_out[b])               # the copies that last read these output buffers have finished
+                for d in dsets[b]:
+                    ab.nvfp4_lora_linear(d, stream)
+                ev_done[b].record(stream)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_done[b])
+                    for i in range(n_proj):
+                        y_hosts[b][i].copy_(outs[b][i].view(torch.int16), non_blocking=True)
+                    ev_out[b].record(s_out)
+            torch.cuda.synchronize()
+            e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+            for i in range(n_proj):
+                if not torch.equal(y_hosts[0][i], y_hosts[1][i]):
+                    raise RuntimeError("the two buffer sets of the end-to-end loop disagree")
     clocks = sampler.stop()
 
-    t = torch.tensor([step_ms, main_ms, e2e_ms, other_ms], dtype=torch.float64, device=dev)
+    t = torch.tensor([step_ms, main_ms, e2e_ms, other_ms, e2e_serial_ms] + proj_ms, dtype=torch.float64, device=dev)
     if tp > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    step_ms, main_ms, e2e_ms, other_ms = [float(v) for v in t.tolist()]
+    vals = [float(v) for v in t.tolist()]
+    step_ms, main_ms, e2e_ms, other_ms, e2e_serial_ms = vals[:5]
+    proj_ms = vals[5:]
 
-    args.collective_used = "tiles stored into every rank's buffer by the kernel + device barrier" if fused else "NCCL all-gather"
+    args.collective_used = ("tiles stored into every rank's buffer by the kernel + one device barrier per step"
+                            if fused else "NCCL all-gather per projection")
     if rank == 0:
         hbm_gbs, peak_kind = peaks()
-        work = algorithmic_work(case)
-        shard_work = algorithmic_work(shard.local_case)
-        achieved = shard_work["main_kernel"] / (main_ms * 1e-3) / 1e9
-        t_roof = max(work["flops"] / (FP4_PEAK_TFLOPS * 1e12), work["total"] / (hbm_gbs * 1e9))
+        work_all = total_work(work.projections)
+        dom_work = works_local[dom]
+        achieved = dom_work["main_kernel"] / (main_ms * 1e-3) / 1e9
+        t_roof = max(work_all["flops"] / (FP4_PEAK_TFLOPS * 1e12), work_all["total"] / (hbm_gbs * 1e9))
+        per_step_launches = sum((1 if c.seq_slot is not None else 0) + 1 + (1 if mode else 0) for c in work.projections) + (1 if fused else 0)
         line = {
             "metric": METRIC, "value": M / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": tp,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(args, case, tp),
-            "tflops": work["flops"] / (step_ms * 1e-3) / 1e12,
+            "config": work.config(args, tp),
+            "tflops": work_all["flops"] / (step_ms * 1e-3) / 1e12,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
-                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if tp == 1 else None, "peak_kind": peak_kind,
-                         "kernel": "nvfp4_lora_linear_tc_kernel (per rank)", "kernel_ms": main_ms,
-                         "algorithmic_bytes": shard_work["main_kernel"]},
+                         "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.activations)) if tp == 1 else None,
+                         "peak_kind": peak_kind,
+                         "kernel": f"nvfp4_lora_linear_tc_kernel, projection '{work.projections[dom].name.split('/')[-1]}' (per rank)",
+                         "kernel_ms": main_ms, "algorithmic_bytes": dom_work["main_kernel"],
+                         "kernel_tflops": dom_work["flops"] / (main_ms * 1e-3) / 1e12, "launch_shape": dom_shape},
             "layer_roofline": {"time_us": t_roof * 1e6, "frac": t_roof / (step_ms * 1e-3),
                                "rule": "max(flops / 9 PFLOP/s nominal NVFP4, algorithmic bytes / measured HBM GB/s), single GPU",
-                               "algorithmic_bytes": work["total"], "flops": work["flops"]},
-            "e2e": {"value": M / (e2e_ms * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": int(x_host.numel() * 2 + slot_host.numel() * 4),
-                    "d2h_bytes_per_step": int(y_host.numel() * 2), "ms_per_step": e2e_ms,
+                               "algorithmic_bytes": work_all["total"], "flops": work_all["flops"]},
+            "projections": [{"name": c.name.split("/")[-1], "ms": proj_ms[i],
+                             "tflops": works_local[i]["flops"] / (proj_ms[i] * 1e-3) / 1e12} for i, c in enumerate(work.projections)],
+            "e2e": {"value": M / (e2e_ms * 1e-3) if e2e_ms == e2e_ms else None, "unit": "tokens/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                     "serial_ms_per_step": e2e_serial_ms,
-                    "note": "value: copies of neighbouring steps overlap the compute (two buffer sets, three streams); "
-                            "serial_ms_per_step: copy in, compute, copy out, one step at a time" if tp == 1 else
-                            "copy in, compute + collective, copy out, one step at a time"},
+                    "note": ("value: copies of neighbouring steps overlap the compute (two buffer sets, three streams); "
+                             "serial_ms_per_step: copy in, compute, copy out, one step at a time") if tp == 1 else
+                            "per rank: copy the replicated inputs in, compute + exchange, copy this rank's column shard of every "
+                            "result out, one step at a time; byte counts are per rank"},
             "launch_shape": launch_shape,
-            "gpu_launches": args.steps * (3 if mode else 2) + args.steps * (2 if mode else 1),
+            "gpu_launches": args.steps * per_step_launches + n_sub * (per_step_launches - (1 if fused else 0)) + n_sub * (2 if mode else 1),
             "clocks": clocks,
         }
         if collective_note:
             line["collective_note"] = collective_note
-        if desc_other is not None:
+        if have_other:
             line["other_activation_mode"] = {
                 "activations": "bf16" if mode else "fp4", "ms_per_step": other_ms, "value": M / (other_ms * 1e-3),
                 "unit": "tokens/s", "layer_roofline_frac": t_roof / (other_ms * 1e-3),
                 "note": "layer kernels only, no collective; fp4 = activations quantised to NVFP4 before the base product "
                         "(the reference's opt-in W4A4 arm), outside the BF16-activation tolerance by construction"}
         if not args.no_cpu_baseline and tp == 1:
-            cstep, rows, cores = cpu_sample(case)
+            cstep, rows, cores = cpu_sample(work, args.cpu_rows or default_cpu_rows(work))
             ct = cstep()
             line["cpu_baseline"] = {"value": rows / ct, "unit": "tokens/s", "cores": cores, "kind": "port",
-                                    "sample": f"first {rows} of {M} tokens x all {N} outputs, one pass ({ct:.1f} s)"}
+                                    "sample": f"first {rows} of {M} tokens x all outputs of all {n_proj} projections, one pass ({ct:.1f} s)"}
         print(json.dumps(line), flush=True)
     if tp > 1:
         dist.barrier()

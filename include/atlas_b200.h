@@ -68,9 +68,12 @@ extern "C" {
  * strided pool declared (b_pool_base / b_slot_stride), the shrink writes the LoRA K-steps' activation tiles there
  * once per call and `lora_t` is left untouched; with less, every CTA builds them from `lora_t`.  Same results. */
 #define ATLAS_B200_LORA_WS_BYTES(m, max_loras, max_rank) \
-    ((((size_t)(m) + 255) / 256) * 256 * ((max_loras) < 256 ? (max_loras) : 256) * (((size_t)(max_rank) + 15) / 16) * 32)
+    (((((size_t)(m) + 255) / 256) * 256 + 256) * ((max_loras) < 256 ? (max_loras) : 256) * (((size_t)(max_rank) + 15) / 16) * 32)
 #define ATLAS_B200_FLAG_NO_CTA_PAIR   32u   /* tcgen05 path: keep every CTA on its own (no two-CTA MMAs); for comparison runs */
 #define ATLAS_B200_FLAG_NO_K_SPLIT    64u   /* tcgen05 path: one CTA per output tile even when that leaves SMs idle; for comparison runs */
+#define ATLAS_B200_FLAG_NO_PERSISTENT 128u   /* tcgen05 path: one output tile per CTA even for many-tile shapes; for comparison runs */
+#define ATLAS_B200_FLAG_TWO_TILE_PASS 256u   /* tcgen05 path, persistent form, BF16 activations: passes of two 192-token tiles that share
+                                                each expanded weight stage (m >= 768) */
 #define ATLAS_B200_ACT_FP4_WS_BYTES(m, k) \
     ((((size_t)(m) * ((k) / 2) + 255) / 256) * 256 + (size_t)(m) * ((k) / 16))
 
@@ -232,6 +235,18 @@ ATLAS_B200_API int atlas_b200_module_slot_offsets(const atlas_b200_model_dims* c
  * to stride max_rank; pads zeroed. `slot_image` is the slot's byte image (pool_slot_bytes long). */
 ATLAS_B200_API int atlas_b200_pack_module(const atlas_b200_model_dims* cfg, size_t max_rank, size_t layer_ordinal, int module,
                            const void* a_bf16, const void* b_bf16, size_t r, void* slot_image);
+/* The per-(layer, module) pointer tables of `load_lora_adapters_multi`'s post-pass
+ * (crates/spark-model/src/lora/loading.rs:310-369; one cell of them is what `refresh_slot_tables`,
+ * lora/types.rs:338-373, rewrites after a swap).  For module `module` of adapted layer `layer_ordinal`:
+ * a_table[s] / b_table[s], s < max_loras, receive the device addresses of slot s's padded A [max_rank, in]
+ * and B [out, max_rank] inside a pool whose slot 0 starts at device address `pool_base` — or 0 where
+ * present[s] == 0 (slot not packed, or its adapter omits the module).  `present` may be NULL (= every slot).
+ * Host arrays in, host arrays out (little-endian u64, the image the reference uploads); no GPU involved.
+ * b_table[s] == b_table[0] + s * atlas_b200_pool_slot_bytes(...) for every present slot, so
+ * atlas_b200_linear_desc::b_pool_base / b_slot_stride can describe the B side. */
+ATLAS_B200_API int atlas_b200_build_route_tables(const atlas_b200_model_dims* cfg, size_t max_rank, size_t layer_ordinal, int module,
+                                  uint64_t pool_base, size_t max_loras, const uint8_t* present,
+                                  uint64_t* a_table, uint64_t* b_table);
 /* `select_victim_slot` (slot_math.rs:25-38): free-first, else least-recently-used idle slot,
  * else -1 (pool full).  Arrays describe the cache region only. */
 ATLAS_B200_API int atlas_b200_select_victim_slot(const size_t* slot_index, const uint8_t* filled, const size_t* ref_count,
@@ -250,6 +265,9 @@ ATLAS_B200_API int atlas_b200_last_variant(void);
  * out[0] = token tile, out[1] = 1 if CTAs were paired for two-CTA MMAs, out[2] = CTAs per output tile (K split),
  * out[3] = 1 if the LoRA activation tiles came from the shrink through `ws`. */
 ATLAS_B200_API int atlas_b200_last_launch_shape(uint32_t out[4]);
+/* The persistent form of the most recent tcgen05 call on this thread: out[0] = token tiles per pass (0: the call ran one
+ * output tile per CTA), out[1] = CTA pairs in the grid. */
+ATLAS_B200_API int atlas_b200_last_persistent_shape(uint32_t out[2]);
 /* Per-CTA cycle counters of the tcgen05 kernel, the counterpart of the reference's per-phase timers
  * (crates/spark-model/src/layers/qwen3_attention/trait_impl/multi_seq/mod.rs:125-141).  While a device
  * buffer of `n_words` u64 is set (16 words per CTA, CTA index = blockIdx.y * gridDim.x + blockIdx.x) each

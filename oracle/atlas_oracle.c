@@ -534,3 +534,16 @@ int orc_num_threads(void) {
     return 1;
 #endif
 }
+
+/* Threads the OpenMP loops use from now on (launchers such as torch.distributed.run export OMP_NUM_THREADS=1,
+ * which would otherwise silently serialise the timed baseline).  n <= 0: one per online core. */
+int orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n <= 0) n = omp_get_num_procs();
+    omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}

@@ -115,6 +115,7 @@ void orc_fused_linear_f32(const orc_fused_args *g, const uint32_t *rows, uint32_
 void orc_reference_sequence(const orc_fused_args *g, uint16_t *y, uint16_t *xa, uint32_t out_row_stride);
 
 int orc_num_threads(void);
+int orc_set_num_threads(int n);   /* n <= 0: one per online core; returns the count in effect */
 
 #ifdef __cplusplus
 }

@@ -90,6 +90,8 @@ def lib() -> C.CDLL:
         L.orc_fused_linear_f32.argtypes = [C.POINTER(FusedArgs), C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
         L.orc_reference_sequence.argtypes = [C.POINTER(FusedArgs), C.c_void_p, C.c_void_p, C.c_uint32]
         L.orc_num_threads.restype = C.c_int
+        L.orc_set_num_threads.restype = C.c_int
+        L.orc_set_num_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
 
@@ -252,3 +254,8 @@ def reference_sequence(x, M, N, K, out_row_stride=None, **kw):
 
 def num_threads() -> int:
     return lib().orc_num_threads()
+
+
+def set_num_threads(n: int = 0) -> int:
+    """Threads for the OpenMP loops (0 = one per online core, whatever OMP_NUM_THREADS says); returns the count in effect."""
+    return lib().orc_set_num_threads(n)

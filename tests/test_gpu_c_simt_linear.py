@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from gpu_util import DeviceCase, assert_close, ideal
+from gpu_util import ATOL, RTOL, DeviceCase, assert_close, ideal
 
 pytestmark = pytest.mark.gpu
 
@@ -19,10 +19,16 @@ def test_simt_nvfp4_fused(cuda, atlas, oracle, M, K, N, ranks, max_rank):
     dc = DeviceCase(cuda, atlas, case, out_row_stride=N + 6)
     y, variant = dc.run(flags=atlas.FLAG_FORCE_SIMT)
     assert variant == atlas.VARIANT_SIMT
-    assert_close(oracle, y[:, :N], ideal(oracle, case), "fused")
+    # This path keeps the reference's rounding boundaries (base -> BF16, xa -> BF16, delta -> BF16, fold -> BF16,
+    # kernels/gb10/common/lora_bgmv.cu:121-125, :214-223), so where base and delta cancel the result carries the
+    # BF16 rounding of the larger term: allow one BF16 ulp (2^-8) of |base| and of |delta| beyond the path's rtol / atol.
+    want, want_base = ideal(oracle, case), ideal(oracle, case, lora=False)
+    got = oracle.bf16_to_f32(np.ascontiguousarray(y[:, :N]))
+    lim = ATOL + RTOL * np.abs(want) + 2.0 ** -8 * (np.abs(want_base) + np.abs(want - want_base))
+    assert np.isfinite(got).all() and (np.abs(got - want) <= lim).all(), "fused"
     assert (y[:, N:] == 0x7FC0).all()                       # padding columns of the output are untouched
     yb, _ = dc.run(lora=False, flags=atlas.FLAG_FORCE_SIMT)
-    assert_close(oracle, yb[:, :N], ideal(oracle, case, lora=False), "base")
+    assert_close(oracle, yb[:, :N], want_base, "base")
     none = case.seq_slot < 0
     assert np.array_equal(y[none], yb[none])                # un-adapted rows are the base result, bit for bit
     assert atlas.device_status() == 0
