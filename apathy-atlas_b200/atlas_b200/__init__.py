@@ -69,6 +69,7 @@ class LinearDesc(C.Structure):
         ("lora_t", C.c_void_p), ("ws", C.c_void_p), ("ws_bytes", C.c_size_t),
         ("b_pool_base", C.c_void_p), ("b_slot_stride", C.c_size_t),
         ("n_dest", C.c_uint32), ("y_col_offset", C.c_uint32), ("y_dest", C.c_void_p * 8),
+        ("a_pool_base", C.c_void_p), ("a_slot_stride", C.c_size_t),
     ]
 
 
@@ -220,6 +221,8 @@ class LoraRoute:
     rank_table: object = None   # optional [max_loras] u32 true ranks (not in the reference)
     b_pool_base: object = None  # optional: B side of the pool as a strided array (see atlas_b200.h)
     b_slot_stride: int = 0
+    a_pool_base: object = None  # optional: A side of the pool as a strided array
+    a_slot_stride: int = 0
 
 
 def apply_lora_bgmv(route: LoraRoute, x, base_out, seq_slot, n: int, x_row_stride: int, out_row_stride: int,
@@ -269,6 +272,7 @@ def make_linear_desc(*, x, m, k, n, y, w_packed=None, w_scale=None, scale2=1.0, 
         d.max_loras, d.max_rank = route.max_loras, route.max_rank
         d.lora_t = _ptr(lora_t)
         d.b_pool_base, d.b_slot_stride = _ptr(route.b_pool_base), route.b_slot_stride
+        d.a_pool_base, d.a_slot_stride = _ptr(route.a_pool_base), route.a_slot_stride
     d.y = _ptr(y)
     d.out_row_stride = out_row_stride if out_row_stride is not None else n
     d.ws, d.ws_bytes = _ptr(ws), ws_bytes
@@ -368,4 +372,5 @@ class LoraPool:
                       self.max_rank, self.max_loras, self.rank_table if with_ranks else None)
         if strided:     # slot s of b_pool starts s * n_out * max_rank * 2 bytes after slot 0
             r.b_pool_base, r.b_slot_stride = self.b_pool.data_ptr(), self.n_out * self.max_rank * 2
+            r.a_pool_base, r.a_slot_stride = self.a_pool.data_ptr(), self.max_rank * self.k_in * 2
         return r

@@ -105,6 +105,7 @@ class LoraWeights:
             _check("atlas_b200_build_route_tables", lib().atlas_b200_build_route_tables(
                 C.byref(self.cfg), self.max_rank, layer, module, self.pool.data_ptr(), 1, None, a0.ctypes.data, b0.ctypes.data))
             r.b_pool_base, r.b_slot_stride = int(b0[0]) + row_begin * self.max_rank * 2, self.slot_bytes
+            r.a_pool_base, r.a_slot_stride = int(a0[0]), self.slot_bytes
         return r
 
     def module_name(self, module: int) -> str:

@@ -22,6 +22,7 @@
 #include "kernel_tc_persist.cuh"
 #include "kernels_simt.cuh"
 #include "kernel_shrink_mma.cuh"
+#include "kernel_shrink_tc.cuh"
 
 namespace atlas {
 
@@ -56,6 +57,7 @@ struct DeviceState {
     bool persist_attr_set[kPersistKernels] = {};
     int persist_clusters[kPersistKernels] = {};
     bool carveout_set = false;
+    bool shrink_tc_attr_set = false;
 };
 static DeviceState g_dev[kMaxDevices];
 static std::mutex g_dev_mutex;
@@ -123,6 +125,36 @@ static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool
     }
     const bool mma_ok = shrink_takes_mma_path(p);
     if (p.tile_out && !mma_ok) return ATLAS_B200_ERR_DIMS;      // tile output exists in the tensor-core shrink only
+    const void* a_base = p.seq_slot ? p.a_pool_base : static_cast<const void*>(p.a_uniform);
+    const size_t a_stride = p.seq_slot ? p.a_slot_stride : size_t(p.max_rank) * p.k_in * 2;
+    if (mma_ok && p.M >= 1024 && !release_dependents && p.k_in % SHT_KSTAGE == 0 && p.max_rank % 16 == 0 && p.max_rank <= 256 &&
+        n_slots <= 4096 && dst && dst->sm100 && g_encode && a_base && aligned(a_base, 16) && a_stride % 16 == 0 &&
+        (!p.tile_out || (p.part_rows && p.chunk % p.part_rows == 0))) {
+        // a prefill batch: one CTA per 128 tokens and all ranks of all their adapters on the tcgen05 tensor cores,
+        // x read once (kernel_shrink_tc.cuh)
+        if (!dst->shrink_tc_attr_set) {
+            cudaError_t e = cudaFuncSetAttribute(lora_shrink_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SHT_SMEM_BYTES);
+            if (e != cudaSuccess) return cuda_status(e);
+            dst->shrink_tc_attr_set = true;
+        }
+        CUtensorMap map_x, map_a;
+        if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.x, p.k_in, p.M, uint64_t(p.x_row_stride) * 2, SHT_KSTAGE, SHT_ROWS,
+                       CU_TENSOR_MAP_SWIZZLE_128B))
+            return ATLAS_B200_ERR_DIMS;
+        {
+            const cuuint64_t dims[3] = {p.k_in, p.max_rank, p.seq_slot ? n_slots : 1u};
+            const cuuint64_t strides[2] = {uint64_t(p.k_in) * 2, uint64_t(a_stride)};
+            const cuuint32_t box[3] = {SHT_KSTAGE, p.max_rank, 1};
+            const cuuint32_t estr[3] = {1, 1, 1};
+            if (g_encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(a_base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return ATLAS_B200_ERR_DIMS;
+        }
+        p.a_pool_base = nullptr;      // host-side fields: not part of what the kernel reads
+        lora_shrink_tc_kernel<<<(p.M + SHT_ROWS - 1) / SHT_ROWS, SHT_THREADS, SHT_SMEM_BYTES, st>>>(map_x, map_a, p);
+        return launch_status();
+    }
     if (mma_ok) {
         const uint32_t chunk = p.chunk ? p.chunk : uint32_t(SHM_CHUNK);
         // CTAs per (slot, granule, chunk) sharing K: 8 for the sake of loads in flight; fewer when the dependent kernel
@@ -651,6 +683,7 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
         sp.rank_table = d.rank_table;
         sp.out = static_cast<uint16_t*>(d.lora_t);
         sp.M = d.m; sp.k_in = d.k; sp.max_rank = d.max_rank; sp.x_row_stride = d.x_row_stride; sp.max_loras = d.max_loras;
+        sp.a_pool_base = d.a_pool_base; sp.a_slot_stride = d.a_slot_stride;
         // t = scale_s / (scale2 * 2^8) * (A_s x), the unit of the MMA accumulator (no 2^8 with FP4 activations)
         sp.post = act_fp4 ? 1.0f / d.scale2 : 1.0f / (d.scale2 * kWeightPreScale);
 

@@ -159,6 +159,9 @@ struct ShrinkParams {
     uint32_t chunk;                 // tokens scanned per CTA (<= 256); 0 = 256
     uint32_t part_rows;             // chunk or chunk / 2
     uint32_t ksplit;                // tensor-core shrink: CTAs per cluster sharing K (set by the launcher)
+    // host side only: the A side of the adapter pool as a strided array (0: not known), for the launcher's tensor map
+    const void* a_pool_base;
+    size_t a_slot_stride;
 };
 
 __global__ void __launch_bounds__(SHRINK_THREADS)

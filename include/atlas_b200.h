@@ -177,6 +177,12 @@ typedef struct atlas_b200_linear_desc {
     uint32_t        n_dest;
     uint32_t        y_col_offset;
     void*           y_dest[8];
+    /* Optional: the A side of the adapter pool as a strided array, the counterpart of b_pool_base / b_slot_stride:
+     * a_table[s] == a_pool_base + s * a_slot_stride for every resident slot s (in the reference's pool both strides are
+     * pool_slot_bytes).  With it, and max_rank a multiple of 16, the shrink of a prefill batch (m >= 1024) runs on the
+     * tcgen05 tensor cores with A_s tiles fetched by TMA.  NULL / 0: A_s is read through a_table (any placement). */
+    const void*     a_pool_base;
+    size_t          a_slot_stride;
 } atlas_b200_linear_desc;
 
 ATLAS_B200_API int atlas_b200_nvfp4_lora_linear(const atlas_b200_linear_desc* desc, void* stream);

@@ -28,7 +28,7 @@ def test_linear_desc_layout_matches_header(atlas):
     assert d.scale2.offset == 48 and d.flags.offset == 52 and d.seq_slot.offset == 56
     assert d.max_loras.offset == 96 and d.y.offset == 104 and d.lora_t.offset == 120
     assert d.b_pool_base.offset == 144 and d.b_slot_stride.offset == 152
-    assert C.sizeof(d) == 232
+    assert C.sizeof(d) == 248
 
 
 def test_seq_slot_and_scaling_match_oracle(atlas, oracle):
