@@ -24,7 +24,7 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libatlas_b200.so")
 
 VARIANT_NONE, VARIANT_SIMT, VARIANT_TCGEN05 = 0, 1, 2
 FLAG_FORCE_SIMT, FLAG_FORCE_TCGEN05, FLAG_STAGED_LORA, FLAG_REUSE_SHRINK, FLAG_ACT_FP4, FLAG_NO_CTA_PAIR, FLAG_NO_K_SPLIT = 1, 2, 4, 8, 16, 32, 64
-FLAG_NO_PERSISTENT, FLAG_TWO_TILE_PASS = 128, 256
+FLAG_NO_PERSISTENT, FLAG_ONE_TILE_PASS = 128, 256
 
 
 def lora_ws_bytes(m: int, max_loras: int, max_rank: int) -> int:
@@ -40,7 +40,8 @@ MODULES = ("q", "k", "v", "o", "gate", "up", "down")
 EXPORTS = (
     "atlas_b200_lora_bgmv", "atlas_b200_lora_delta", "atlas_b200_w4a16_gemm",
     "atlas_b200_dequant_nvfp4_to_bf16", "atlas_b200_quantize_bf16_to_nvfp4",
-    "atlas_b200_nvfp4_lora_linear", "atlas_b200_nvfp4_lora_linear_noalloc", "atlas_b200_column_shard",
+    "atlas_b200_nvfp4_lora_linear", "atlas_b200_nvfp4_lora_linear_noalloc", "atlas_b200_lora_shrink_tiles",
+    "atlas_b200_column_shard",
     "atlas_b200_build_seq_slot", "atlas_b200_routed_prefill_slot_of", "atlas_b200_peft_scaling",
     "atlas_b200_module_dims", "atlas_b200_pool_slot_bytes", "atlas_b200_slot_base_offset",
     "atlas_b200_module_slot_offsets", "atlas_b200_pack_module", "atlas_b200_build_route_tables", "atlas_b200_select_victim_slot",
@@ -100,6 +101,7 @@ def lib() -> C.CDLL:
     L.atlas_b200_quantize_bf16_to_nvfp4.argtypes = [vp, vp, vp, f32, u32, u32, vp]
     L.atlas_b200_nvfp4_lora_linear.argtypes = [C.POINTER(LinearDesc), vp]
     L.atlas_b200_nvfp4_lora_linear_noalloc.argtypes = [C.POINTER(LinearDesc), vp]
+    L.atlas_b200_lora_shrink_tiles.argtypes = [C.POINTER(LinearDesc), u32, u32, C.POINTER(vp), u32, vp]
     L.atlas_b200_column_shard.argtypes = [u32, u32, u32, C.POINTER(u32), C.POINTER(u32)]
     L.atlas_b200_build_seq_slot.argtypes = [C.POINTER(i32), sz, sz, i32, C.POINTER(i32)]
     L.atlas_b200_routed_prefill_slot_of.argtypes = [i32, sz, sz]
@@ -287,6 +289,14 @@ def nvfp4_lora_linear(desc: LinearDesc, stream=None) -> int:
     """Launch the fused layer; returns the kernel family that ran (VARIANT_*)."""
     _check("atlas_b200_nvfp4_lora_linear", lib().atlas_b200_nvfp4_lora_linear(C.byref(desc), _stream_ptr(stream)))
     return lib().atlas_b200_last_variant()
+
+
+def lora_shrink_tiles(desc: LinearDesc, row_begin: int, row_count: int, ws_dest, stream=None) -> None:
+    """The shrink of `desc` for rows [row_begin, row_begin + row_count) only, its tiles stored into every scratch buffer
+    of `ws_dest` (device addresses or tensors laid out like desc.ws); the fused call then runs with FLAG_REUSE_SHRINK."""
+    arr = (C.c_void_p * len(ws_dest))(*[_ptr(w) for w in ws_dest])
+    _check("atlas_b200_lora_shrink_tiles", lib().atlas_b200_lora_shrink_tiles(
+        C.byref(desc), row_begin, row_count, arr, len(ws_dest), _stream_ptr(stream)))
 
 
 STATIC_SCRATCH_ELEMS = 512 * 1024

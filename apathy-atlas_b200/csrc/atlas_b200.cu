@@ -152,9 +152,12 @@ static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool
                 return ATLAS_B200_ERR_DIMS;
         }
         p.a_pool_base = nullptr;      // host-side fields: not part of what the kernel reads
-        lora_shrink_tc_kernel<<<(p.M + SHT_ROWS - 1) / SHT_ROWS, SHT_THREADS, SHT_SMEM_BYTES, st>>>(map_x, map_a, p);
+        if (p.m_begin % SHT_ROWS != 0 || p.m_begin >= p.M) return ATLAS_B200_ERR_DIMS;
+        const uint32_t rows = p.m_count ? std::min(p.m_count, p.M - p.m_begin) : p.M - p.m_begin;
+        lora_shrink_tc_kernel<<<(rows + SHT_ROWS - 1) / SHT_ROWS, SHT_THREADS, SHT_SMEM_BYTES, st>>>(map_x, map_a, p);
         return launch_status();
     }
+    if (p.m_begin || p.m_count || p.n_tile_dest > 1) return ATLAS_B200_ERR_DIMS;      // a row range / several destinations: that kernel only
     if (mma_ok) {
         const uint32_t chunk = p.chunk ? p.chunk : uint32_t(SHM_CHUNK);
         // CTAs per (slot, granule, chunk) sharing K: 8 for the sake of loads in flight; fewer when the dependent kernel
@@ -616,7 +619,14 @@ static int validate_linear(const atlas_b200_linear_desc& d) {
     return ATLAS_B200_OK;
 }
 
-int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
+// A call that stops after the shrink: rows [row_begin, row_begin + row_count) of the batch, masked-t tiles written into
+// n_dest scratch buffers laid out like d.ws (see atlas_b200_lora_shrink_tiles).
+struct ShrinkOnly {
+    uint32_t row_begin, row_count, n_dest;
+    void* const* ws_dest;
+};
+
+int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st, const ShrinkOnly* shrink_only = nullptr) {
     int rc = validate_linear(d);
     if (rc) return rc;
     t_last_variant = ATLAS_B200_VARIANT_NONE;
@@ -624,7 +634,7 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
 
     const bool staged = (d.flags & ATLAS_B200_FLAG_STAGED_LORA) != 0;
     bool use_tc = !(d.flags & ATLAS_B200_FLAG_FORCE_SIMT) && !staged && tc_eligible(d);
-    if (!use_tc && (d.flags & ATLAS_B200_FLAG_FORCE_TCGEN05)) return ATLAS_B200_ERR_DIMS;
+    if (!use_tc && ((d.flags & ATLAS_B200_FLAG_FORCE_TCGEN05) || shrink_only)) return ATLAS_B200_ERR_DIMS;
     if (!use_tc && d.n_dest) return ATLAS_B200_ERR_DIMS;          // placement into several buffers is the tcgen05 epilogue's
 
     const bool act_fp4 = (d.flags & ATLAS_B200_FLAG_ACT_FP4) != 0;
@@ -713,12 +723,12 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
                           (d.n_dest ? d.y_col_offset % 8 == 0 : aligned(d.y, 16));
         for (uint32_t r = 0; persistent && r < d.n_dest; ++r) persistent = aligned(d.y_dest[r], 16);
         // two token tiles of 192 per pass (the expanded weight operand is used twice) where the batch has several passes
-        const bool two_tiles = persistent && !act_fp4 && (d.flags & ATLAS_B200_FLAG_TWO_TILE_PASS) && d.m >= 768;
+        const bool two_tiles = persistent && !act_fp4 && !(d.flags & ATLAS_B200_FLAG_ONE_TILE_PASS) && d.m >= 768;
         if (persistent) {
             const int clusters = act_fp4 ? persist_resident_clusters<256, 1, true>(1)
                                          : (two_tiles ? persist_resident_clusters<192, 2, false>(2) : persist_resident_clusters<256, 1, false>(0));
             const uint32_t tiles = two_tiles ? persist_tiles<192, 2>(d) : persist_tiles<256, 1>(d);
-            persistent = clusters > 0 && tiles >= 2u * uint32_t(clusters);
+            persistent = clusters > 0 && tiles > uint32_t(clusters);
         }
         const uint32_t mt_tiles = (persistent && two_tiles) ? 192u : mt;     // token tile of the shrink's masked-t blocks
         if (persistent && d.seq_slot) {
@@ -740,6 +750,23 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st) {
                 }
             }
             if (t2.tiles) { tt = t2; sp = sp2; } else persistent = false;
+        }
+        if (shrink_only) {
+            // the shrink alone, for a row range, into several copies of the scratch: the launch shape decided above fixes
+            // the tile layout, exactly as the call that later consumes the tiles (ATLAS_B200_FLAG_REUSE_SHRINK) decides it
+            if (!d.seq_slot || !tt.tiles || shrink_only->n_dest == 0 || shrink_only->n_dest > 8) return ATLAS_B200_ERR_DIMS;
+            const size_t off = size_t(reinterpret_cast<uint8_t*>(tt.tiles) - static_cast<uint8_t*>(d.ws));
+            for (uint32_t i = 0; i < shrink_only->n_dest; ++i)
+                if (!shrink_only->ws_dest[i] || !aligned(shrink_only->ws_dest[i], 256)) return ATLAS_B200_ERR_ALIGN;
+            sp.tile_out = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(shrink_only->ws_dest[0]) + off);
+            for (uint32_t i = 1; i < shrink_only->n_dest; ++i)
+                sp.tile_out_more[i - 1] = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(shrink_only->ws_dest[i]) + off);
+            sp.n_tile_dest = shrink_only->n_dest;
+            sp.m_begin = shrink_only->row_begin;
+            sp.m_count = shrink_only->row_count;
+            rc = launch_shrink(sp, d.max_loras, st);
+            if (rc == ATLAS_B200_OK) t_last_variant = ATLAS_B200_VARIANT_TCGEN05;
+            return rc;
         }
         const ShrinkParams* shrink = (d.seq_slot && !(d.flags & ATLAS_B200_FLAG_REUSE_SHRINK)) ? &sp : nullptr;
         if (persistent) {
@@ -857,6 +884,13 @@ int atlas_b200_quantize_bf16_to_nvfp4(const void* in_bf16, void* packed, void* s
 int atlas_b200_nvfp4_lora_linear(const atlas_b200_linear_desc* desc, void* stream) {
     if (!desc) return ATLAS_B200_ERR_NULL;
     return ops::nvfp4_lora_linear(*desc, static_cast<cudaStream_t>(stream));
+}
+
+int atlas_b200_lora_shrink_tiles(const atlas_b200_linear_desc* desc, uint32_t row_begin, uint32_t row_count,
+                                 void* const* ws_dest, uint32_t n_dest, void* stream) {
+    if (!desc || !ws_dest) return ATLAS_B200_ERR_NULL;
+    ops::ShrinkOnly so{row_begin, row_count, n_dest, ws_dest};
+    return ops::nvfp4_lora_linear(*desc, static_cast<cudaStream_t>(stream), &so);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -3,11 +3,11 @@
 //
 // lora_shrink_mma_kernel (kernel_shrink_mma.cuh) spreads one (slot, 16 ranks, token tile) over a cluster so that a
 // decode batch still has loads in flight on every SM; with thousands of tokens that shape reads every x row once
-// per 16 ranks and spends its time in cluster barriers.  Here one CTA owns SHT_ROWS = 128 consecutive tokens and ALL
+// per 16 ranks and spends its time in cluster barriers.  Here one CTA owns SHT_ROWS = 64 consecutive tokens and ALL
 // ranks of EVERY adapter those tokens use, so x is read from HBM exactly once:
 //
 //   acc_i[row, j] = sum_k x[row, k] * A_{s_i}[j, k]        one accumulator per adapter s_i that occurs in the CTA's rows,
-//                                                          side by side in tensor memory (128 lanes = rows,
+//                                                          side by side in tensor memory (lanes = rows,
 //                                                          rank_pad columns each, at most 512 columns per pass)
 //   t[row, :]     = f(s_i) * acc_i[row, :]  where seq_slot[row] == s_i
 //
@@ -15,12 +15,12 @@
 // touches one to three) and the epilogue keeps, per row, the accumulator of its own adapter.  The surplus products
 // cost nothing next to the memory traffic, and the contraction order of a row does not depend on its neighbours.
 //
-// Pipeline: a ring of shared-memory stages of 64 K elements — the x tile [128 x 128 B] and one A_s tile
+// Pipeline: a ring of shared-memory stages of 64 K elements — the x tile [64 x 128 B] and one A_s tile
 // [rank_pad x 128 B] per present adapter, both in the 128-byte swizzled K-major layout the MMA reads — filled by ONE
 // thread with TMA copies (cp.async.bulk.tensor, never multicast): one 2-D box of x and one 3-D box per adapter out
 // of the A side of the strided adapter pool [max_loras][max_rank][k_in] (rows past max_rank are filled with zeros),
 // so the copies of as many stages as fit are in flight at the cost of a handful of instructions per stage; one
-// thread issues tcgen05.mma (M = 128 rows, N = rank_pad, K = 16) per adapter and K step and releases the stage with
+// thread issues tcgen05.mma (M = 128 rows of which 64 are tokens, N = rank_pad, K = 16) per adapter and K step and releases the stage with
 // tcgen05.commit.  Afterwards four warps read the accumulators back (lane = row) and write
 //   * rows of t [M, max_rank] (routed rows only), or
 //   * the masked [part_rows x 16] blocks of ShrinkParams::tile_out, numbered per token tile exactly as the fused
@@ -36,14 +36,17 @@
 namespace atlas {
 
 constexpr int SHT_THREADS = 256;
-constexpr int SHT_ROWS = 128;            // tokens per CTA = UMMA M
+constexpr int SHT_ROWS = 64;             // tokens per CTA: half of the UMMA's 128 rows, so that a batch of a few thousand
+                                         // tokens still gives every SM a CTA (the stream is bound by how many SMs pull);
+                                         // MMA rows 64..127 read whatever follows the x tile in the stage and land in
+                                         // accumulator lanes nobody reads
 constexpr int SHT_KSTAGE = 64;           // K elements per stage (one 128-byte swizzle row of BF16)
 constexpr int SHT_X_BYTES = SHT_ROWS * 128;
-constexpr int SHT_MAX_STAGES = 8;
+constexpr int SHT_MAX_STAGES = 12;
 constexpr int SHT_RING_BYTES = 192 * 1024;
 constexpr int SHT_MAX_ACC_COLS = 512;
 constexpr int SHT_MAX_SLOTS = 32;        // adapters per pass (512 columns / 16 ranks)
-constexpr int SHT_SMEM_BYTES = SHT_RING_BYTES + 1024;
+constexpr int SHT_SMEM_BYTES = SHT_RING_BYTES + 128 * 128 + 1024;     // + what the MMA's rows 64..127 may touch past the last stage
 
 __global__ void __launch_bounds__(SHT_THREADS, 1)
 lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_a, const ShrinkParams p) {
@@ -59,7 +62,7 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     __shared__ uint32_t tmem_base_s, abort_s;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t m0 = blockIdx.x * SHT_ROWS;
+    const uint32_t m0 = p.m_begin + blockIdx.x * SHT_ROWS;      // (m_begin: a multiple of SHT_ROWS)
     if (m0 >= p.M) return;
     const uint32_t chunk = p.chunk ? p.chunk : 256u;     // token tile of the fused kernel (tile output only)
     const uint32_t tile_lo = m0 / chunk;                 // first token tile this CTA's rows lie in
@@ -91,7 +94,7 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     if (p.tile_out) {
         for (uint32_t tl = 0; tl < 2; ++tl) {
             const uint32_t t_m0 = (tile_lo + tl) * chunk;
-            if (t_m0 >= min(m0 + SHT_ROWS, p.M)) break;
+            if (t_m0 >= min(m0 + uint32_t(SHT_ROWS), p.M)) break;
             for (uint32_t i = tid; i < chunk; i += SHT_THREADS) {
                 const int32_t s = valid_slot(t_m0 + i);
                 if (s >= 0) atomicOr(&present_t[tl][uint32_t(s) >> 5], 1u << (uint32_t(s) & 31u));
@@ -138,12 +141,23 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             q += (rank_of((s & ~31u) + (__ffs(bits) - 1)) + 15u) / 16u;
         return q;
     };
-    // where row `idx_in_cta` keeps granule block q: its 32 bytes inside ShrinkParams::tile_out
-    auto block_row = [&](uint32_t row, uint32_t q, uint32_t& swap) -> uint16_t* {
+    // where row `row` of this CTA keeps granule block q: element offset of its 32 bytes inside ShrinkParams::tile_out
+    auto block_row = [&](uint32_t row, uint32_t q, uint32_t& swap) -> size_t {
         const uint32_t m = m0 + row, tile = m / chunk, idx = m % chunk;
         const uint32_t part = idx / p.part_rows, r = idx % p.part_rows;
         swap = (r >> 2) & 1u;
-        return p.tile_out + (((size_t(tile) * (chunk / p.part_rows) + part) * p.tile_cap + q) * p.part_rows + r) * 16;
+        return (((size_t(tile) * (chunk / p.part_rows) + part) * p.tile_cap + q) * p.part_rows + r) * 16;
+    };
+    // the two 16-byte halves of a block row, to every destination buffer
+    auto store_block_row = [&](size_t at, uint32_t swap, const uint4& lo, const uint4& hi) {
+        uint4* dst = reinterpret_cast<uint4*>(p.tile_out + at);
+        dst[swap] = lo;
+        dst[swap ^ 1u] = hi;
+        for (uint32_t d = 1; d < p.n_tile_dest; ++d) {
+            uint4* peer = reinterpret_cast<uint4*>(p.tile_out_more[d - 1] + at);
+            peer[swap] = lo;
+            peer[swap ^ 1u] = hi;
+        }
     };
 
     // Parity each role waits for next, one bit per stage: the ring's depth changes from pass to pass (it depends on how
@@ -185,9 +199,11 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 empty_par ^= 1u << s;
                 const uint32_t st = ring + s * stage_bytes;
                 tc::mbar_arrive_expect_tx(BAR_FULL + 8 * s, stage_bytes);
-                tc::tma_load_2d(st, &map_x, int32_t(ks * SHT_KSTAGE), int32_t(m0), BAR_FULL + 8 * s);
+                // (every CTA walks K in the same order, so a row's result does not depend on how the batch is cut into launches)
+                const uint32_t kk = ks;
+                tc::tma_load_2d(st, &map_x, int32_t(kk * SHT_KSTAGE), int32_t(m0), BAR_FULL + 8 * s);
                 for (uint32_t ci = 0; ci < n_cs; ++ci)
-                    tc::tma_load_3d(st + SHT_X_BYTES + ci * rank_pad * 128u, &map_a, int32_t(ks * SHT_KSTAGE), 0, int32_t(cslot[ci]), BAR_FULL + 8 * s);
+                    tc::tma_load_3d(st + SHT_X_BYTES + ci * rank_pad * 128u, &map_a, int32_t(kk * SHT_KSTAGE), 0, int32_t(cslot[ci]), BAR_FULL + 8 * s);
             }
         } else if (n_cs > 0 && warp == 4 && lane == 0) {
             // ================================ MMA issue ================================
@@ -214,14 +230,15 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 
         if (warp >= 4) {
             // ================================ epilogue: lane = row ================================
-            const uint32_t row = (warp & 3u) * 32 + lane;
-            const int32_t my_slot = slot_row[row];
-            const bool row_live = m0 + row < p.M;
+            const uint32_t row = (warp & 3u) * 32 + lane;              // accumulator lane; lanes 64..127 hold nothing
+            const bool has_rows = (warp & 3u) * 32 < uint32_t(SHT_ROWS);
+            const int32_t my_slot = has_rows ? slot_row[row] : -1;
+            const bool row_live = has_rows && m0 + row < p.M;
             if (n_cs > 0) {
                 ok = tc::mbar_wait(BAR_ACC, acc_phase, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 200) && ok;
                 tc::tcgen05_fence_after();
             }
-            if (ok) {
+            if (ok && has_rows) {
                 for (uint32_t ci = 0; ci < n_cs; ++ci) {
                     const uint32_t sl = cslot[ci];
                     const uint32_t rank = rank_of(sl);
@@ -246,9 +263,8 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                             const uint32_t q = q0 + j0 / 16;
                             if (q >= p.tile_cap) { record_status(STATUS_TILE_CAPACITY); continue; }
                             uint32_t swap;
-                            uint4* dst = reinterpret_cast<uint4*>(block_row(row, q, swap));
-                            dst[swap] = make_uint4(w[0], w[1], w[2], w[3]);
-                            dst[swap ^ 1u] = make_uint4(w[4], w[5], w[6], w[7]);
+                            const size_t at = block_row(row, q, swap);
+                            store_block_row(at, swap, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]));
                         } else if (mine) {
                             uint16_t* dst = p.out + size_t(m0 + row) * p.max_rank + j0;
                             if (j0 + 16 <= p.max_rank && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
@@ -271,9 +287,8 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                             const uint32_t q0 = granules_ahead(tl, sl), n_gr = (rank_of(sl) + 15u) / 16u;
                             for (uint32_t k = 0; k < n_gr && q0 + k < p.tile_cap; ++k) {
                                 uint32_t swap;
-                                uint4* dst = reinterpret_cast<uint4*>(block_row(row, q0 + k, swap));
-                                dst[0] = make_uint4(0u, 0u, 0u, 0u);
-                                dst[1] = make_uint4(0u, 0u, 0u, 0u);
+                                const size_t at = block_row(row, q0 + k, swap);
+                                store_block_row(at, swap, make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u));
                             }
                         }
                     }

@@ -29,12 +29,13 @@
 // (strided adapter pool + masked-t tiles written by the shrink).  The launcher falls back to the one-tile-per-CTA
 // kernel otherwise.
 //
-// Warp roles (15 warps, 480 threads):
+// Warp roles (19 warps, 608 threads):
 //   warp 0        TMA producer of the base K loop
 //   warp 1        TMEM allocation, tcgen05.mma issue (first CTA of the pair issues for both)
-//   warps 2-5     granule list of the next tile; accumulator drain; row stores
+//   warps 2-5     accumulator drain; row stores; granule list of the next tile
 //   warps 6-13    A16: NVFP4 -> BF16 weight operand into tensor memory; A4: block scales into tensor memory
 //   warp 14       TMA producer of the LoRA operand ring
+//   warps 15-18   accumulator drain and row stores, with warps 2-5 (two warps per tensor-memory lane quadrant)
 // Every wait is bounded as in kernel_tc.cuh; on expiry all roles fall through to the common teardown.
 #pragma once
 
@@ -43,12 +44,14 @@
 namespace atlas {
 namespace tc {
 
-constexpr int P_NUM_THREADS = 32 * 15;
+constexpr int P_NUM_THREADS = 32 * 19;
 constexpr int P_LORA_WARP = 14;
-constexpr int P_EPI_WARPS = 4;
+constexpr int P_EPI_WARP1 = 15;         // second group of four drain / store warps (the first is warps 2-5)
+constexpr int P_EPI_WARPS = 8;
+constexpr int P_EPI_THREADS = 32 * P_EPI_WARPS;
 
 template <int MT, int G, bool A4> struct PCfg {
-    static_assert(MT % 32 == 0 && MT >= 128 && MT <= 256, "token tile of a pass");
+    static_assert(MT % 64 == 0 && MT >= 128 && MT <= 256, "token tile of a pass");
     static_assert(!A4 || G == 1, "FP4 activations: one token tile per pass");
     static constexpr int XROWS = MT / 2;                                   // token rows of a tile this CTA stages
     static constexpr int X_TILE_BYTES = XROWS * KB * 2;
@@ -83,7 +86,8 @@ template <int MT, int G, bool A4> struct PCfg {
     static constexpr int OFF_GRAN = OFF_SLOT + MT * 4;                            // uint16[G][MAX_GRANULES]
     static constexpr int OFF_BITMAP = OFF_GRAN + G * MAX_GRANULES * 2;            // uint32[128]
     static constexpr int OFF_SCAN = OFF_BITMAP + (MAX_LORAS_TC / 32) * 4;         // uint32[8]
-    static constexpr int OFF_BAR = OFF_SCAN + 64;
+    static constexpr int OFF_GCOUNT = OFF_SCAN + 64;                              // uint8[MAX_LORAS_TC]: granules per slot, 0 = slot not usable
+    static constexpr int OFF_BAR = OFF_GCOUNT + MAX_LORAS_TC;
     static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_STAGES + 2 * L_STAGES + 2 * G + 2;
     static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;                       // tmem ptr, abort, n_gran[G]
     static constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;
@@ -122,6 +126,7 @@ nvfp4_lora_linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x
     uint16_t* gran = reinterpret_cast<uint16_t*>(smem_gen + C::OFF_GRAN);
     uint32_t* bitmap = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_BITMAP);
     uint32_t* scan = reinterpret_cast<uint32_t*>(smem_gen + C::OFF_SCAN);
+    uint8_t* gcount = smem_gen + C::OFF_GCOUNT;
     const uint32_t bar0 = smem_base + C::OFF_BAR;
     const uint32_t BAR_FULL = bar0;                                     // [STAGES]   operands of a K block -> MMA (first CTA)
     const uint32_t BAR_EMPTY = BAR_FULL + 8 * C::STAGES;                // [STAGES]   MMA -> producers
@@ -182,6 +187,14 @@ nvfp4_lora_linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x
     if (warp == P_LORA_WARP && lane == 0 && p.seq_slot) {
         tma_prefetch_desc(&map_b);
         tma_prefetch_desc(&map_t);
+    }
+    if (p.seq_slot) {
+        // granules (16 ranks each) every slot contributes to a tile it occurs in; 0 for a slot without both tables' entries
+        for (uint32_t sl = tid; sl < p.max_loras; sl += P_NUM_THREADS) {
+            const bool usable = p.a_table[sl] != 0ull && p.b_table[sl] != 0ull;
+            const uint32_t r = p.rank_table ? min(p.rank_table[sl], p.max_rank) : p.max_rank;
+            gcount[sl] = usable ? uint8_t((r + 15u) / 16u) : uint8_t(0);
+        }
     }
     tcgen05_fence_before();
     __syncwarp();
@@ -378,14 +391,15 @@ nvfp4_lora_linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x
             }
         }
         __syncwarp();
-    } else if (warp < DEQ_WARP0) {
-        // ============================ granule lists, accumulator drain, row stores ===========================
-        const uint32_t te = tid - EPI_WARP0 * 32;          // 0..127
+    } else if (warp < DEQ_WARP0 || warp >= P_EPI_WARP1) {
+        // ============================ accumulator drain, row stores, granule lists ===========================
+        const uint32_t grp = warp < DEQ_WARP0 ? 0u : 1u;                            // which of the two groups of four warps
+        const uint32_t te = ((warp < DEQ_WARP0 ? warp - EPI_WARP0 : warp - P_EPI_WARP1 + 4u) << 5) + lane;   // 0..255
         const uint32_t q = warp & 3u;                      // TMEM lane quadrant this warp may read
         uint32_t epi_phase = 0;
         bool ok = true;
         unsigned long long w_accfull = 0, c_drain = 0, c_store = 0, c_list = 0;
-        // bounded rendezvous of the four warps of this role
+        // bounded rendezvous of the eight warps of this role
         auto epi_sync = [&]() -> bool {
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR_EPI);
@@ -393,54 +407,58 @@ nvfp4_lora_linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x
             epi_phase ^= 1u;
             return r;
         };
-        // lists of pass `pass`: for each of its G token tiles the (slot, granule) pairs that occur, slots ascending
-        auto build_lists = [&](uint32_t pass) -> bool {
+        // this thread's row of each token tile of pass `pass`: its slot if the row takes a LoRA term, else -1
+        auto load_slots = [&](uint32_t pass, int32_t (&out)[G]) {
+#pragma unroll
+            for (uint32_t g = 0; g < uint32_t(G); ++g) {
+                const uint32_t m = (pass * G + g) * MT + te;
+                out[g] = (p.seq_slot && te < uint32_t(MT) && m < p.M) ? p.seq_slot[m] : -1;
+            }
+        };
+        // lists of a pass from those slots: for each of its G token tiles the (slot, granule) pairs that occur, slots ascending
+        auto build_lists = [&](const int32_t (&slots)[G]) -> bool {
             if (!p.seq_slot) return true;
             for (uint32_t g = 0; g < uint32_t(G); ++g) {
-                const uint32_t m0 = (pass * G + g) * MT;
-                bitmap[te] = 0;
+                if (te < 128u) bitmap[te] = 0;
                 if (!epi_sync()) return false;
-                for (uint32_t r = te; r < uint32_t(MT); r += EPI_THREADS) {
-                    const uint32_t m = m0 + r;
-                    int32_t s = (m < p.M) ? p.seq_slot[m] : -1;
-                    if (s >= 0) {
-                        if (uint32_t(s) >= p.max_loras) { record_status(STATUS_SLOT_OUT_OF_RANGE); s = -1; }
-                        else if (p.a_table[s] == 0ull || p.b_table[s] == 0ull) s = -1;
-                    }
-                    if (s >= 0) atomicOr(&bitmap[uint32_t(s) >> 5], 1u << (uint32_t(s) & 31u));
+                int32_t sl = slots[g];
+                if (sl >= 0) {
+                    if (uint32_t(sl) >= p.max_loras) { record_status(STATUS_SLOT_OUT_OF_RANGE); sl = -1; }
+                    else if (gcount[sl] == 0) sl = -1;
                 }
+                if (sl >= 0) atomicOr(&bitmap[uint32_t(sl) >> 5], 1u << (uint32_t(sl) & 31u));
                 if (!epi_sync()) return false;
-                uint32_t word = bitmap[te], cnt = 0;
-                for (uint32_t w = word; w; w &= w - 1) {
-                    const uint32_t s = te * 32 + (__ffs(w) - 1);
-                    const uint32_t r = p.rank_table ? min(p.rank_table[s], p.max_rank) : p.max_rank;
-                    cnt += (r + 15u) / 16u;
-                }
-                uint32_t incl = cnt;
+                uint32_t word = 0, cnt = 0, incl = 0;
+                if (te < 128u) {                                  // (warps 2-5: one bitmap word = 32 slots per thread)
+                    word = bitmap[te];
+                    for (uint32_t w = word; w; w &= w - 1) cnt += gcount[te * 32 + (__ffs(w) - 1)];
+                    incl = cnt;
 #pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                    if (lane >= uint32_t(o)) incl += v;
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                        if (lane >= uint32_t(o)) incl += v;
+                    }
+                    if (lane == 31) scan[te >> 5] = incl;
                 }
-                if (lane == 31) scan[warp - EPI_WARP0] = incl;
                 if (!epi_sync()) return false;
-                uint32_t base = 0;
-                for (uint32_t w = 0; w < warp - EPI_WARP0; ++w) base += scan[w];
-                const uint32_t n_gran = scan[0] + scan[1] + scan[2] + scan[3];
-                uint32_t pos = base + incl - cnt;
-                for (uint32_t w = word; w; w &= w - 1) {
-                    const uint32_t s = te * 32 + (__ffs(w) - 1);
-                    const uint32_t r = p.rank_table ? min(p.rank_table[s], p.max_rank) : p.max_rank;
-                    for (uint32_t k = 0; k < (r + 15u) / 16u; ++k) gran[g * C::MAX_GRANULES + pos++] = uint16_t((s << 2) | k);
+                if (te < 128u) {
+                    uint32_t base = 0;
+                    for (uint32_t w = 0; w < (te >> 5); ++w) base += scan[w];
+                    uint32_t pos = base + incl - cnt;
+                    for (uint32_t w = word; w; w &= w - 1) {
+                        const uint32_t s2 = te * 32 + (__ffs(w) - 1);
+                        for (uint32_t k = 0; k < gcount[s2]; ++k) gran[g * C::MAX_GRANULES + pos++] = uint16_t((s2 << 2) | k);
+                    }
+                    if (te == 0) misc[4 + g] = scan[0] + scan[1] + scan[2] + scan[3];
                 }
-                if (te == 0) misc[4 + g] = n_gran;
-                if (!epi_sync()) return false;
             }
-            return true;
+            return epi_sync();
         };
         (void)slot_arr;
+        int32_t next_slots[G];
         if (my_tiles) {
-            ok = build_lists(tile_pass(0));
+            load_slots(tile_pass(0), next_slots);
+            ok = build_lists(next_slots);
             if (ok && te == 0) mbar_arrive(BAR_LIST);
         }
         const float osc = p.out_scale;
@@ -448,6 +466,8 @@ nvfp4_lora_linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x
         const uint32_t fe = (q * 32u + lane) & ~1u;
         for (uint32_t i = 0; ok && i < my_tiles; ++i) {
             const uint32_t f0 = (tile_fpair(i) * 2u + cta_rank) * FT;
+            // the next pass's routing entries travel while this pass's accumulators complete
+            if (i + 1 < my_tiles) load_slots(tile_pass(i + 1), next_slots);
             // ---- drain: every accumulator of the pass -> BF16 [token][128 features] in shared memory ----
             for (uint32_t g = 0; ok && g < uint32_t(G); ++g) {
                 const long long t_w = prof ? clock64() : 0;
@@ -462,23 +482,37 @@ nvfp4_lora_linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x
                 const long long t_d = prof ? clock64() : 0;
                 if (prof) w_accfull += (unsigned long long)(t_d - t_w);
                 const uint32_t tile = epi0 + g * (MT * 256);
-#pragma unroll 2
-                for (uint32_t c0 = 0; c0 < uint32_t(MT); c0 += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_acc + ((q * 32u) << 16) + g * MT + c0, v);
-                    tmem_ld_wait();
+                // The two warps of a quadrant take alternate blocks of 32 token columns.  The next block's tensor-memory
+                // loads are issued before the current block is converted and stored, so their latency is not exposed.
+                constexpr uint32_t N_BLK = uint32_t(MT) / 64u;
+                const uint32_t t_col0 = tmem_acc + ((q * 32u) << 16) + g * MT + grp * 32u;
+                uint32_t v[2][2][16];
+                tmem_ld16(t_col0, v[0][0]);
+                tmem_ld16(t_col0 + 16, v[0][1]);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const float a = __uint_as_float(v[2 * u]) * osc, b = __uint_as_float(v[2 * u + 1]) * osc;
-                        const float got = __shfl_xor_sync(0xFFFFFFFFu, odd ? a : b, 1);
-                        const uint32_t row = c0 + 2 * u + (odd ? 1u : 0u);
-                        const uint32_t w = odd ? pack_bf16x2(got, b) : pack_bf16x2(a, got);
-                        const uint32_t chunk = (fe >> 3) ^ ((row & 1u) << 2);
-                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile + row * 256u + chunk * 16u + (fe & 7u) * 2u), "r"(w) : "memory");
+                for (uint32_t blk = 0; blk < N_BLK; ++blk) {
+                    const uint32_t cur = blk & 1u;
+                    if (blk + 1 < N_BLK) {
+                        tmem_ld16(t_col0 + 64 * (blk + 1), v[cur ^ 1u][0]);
+                        tmem_ld16(t_col0 + 64 * (blk + 1) + 16, v[cur ^ 1u][1]);
                     }
+                    const uint32_t c0 = grp * 32 + 64 * blk;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const float a = __uint_as_float(v[cur][h][2 * u]) * osc, b = __uint_as_float(v[cur][h][2 * u + 1]) * osc;
+                            const float got = __shfl_xor_sync(0xFFFFFFFFu, odd ? a : b, 1);
+                            const uint32_t row = c0 + 16 * h + 2 * u + (odd ? 1u : 0u);
+                            const uint32_t w = odd ? pack_bf16x2(got, b) : pack_bf16x2(a, got);
+                            const uint32_t chunk = (fe >> 3) ^ ((row & 1u) << 2);
+                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile + row * 256u + chunk * 16u + (fe & 7u) * 2u), "r"(w) : "memory");
+                        }
+                    if (blk + 1 < N_BLK) tmem_ld_wait();
                 }
                 tcgen05_fence_before();
-                ok = epi_sync();                              // all four quadrants are out of tensor memory and in the tile
+                ok = epi_sync();                              // all of the accumulator is out of tensor memory and in the tile
                 if (!ok) break;
                 if (te == 0) mbar_arrive_cluster(acc_empty_at_leader + 8 * g);
                 if (prof) c_drain += (unsigned long long)(clock64() - t_d);
@@ -492,7 +526,7 @@ nvfp4_lora_linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x
                 if (f < p.N) {
                     const bool whole = f + 8u <= p.N;
                     const uint32_t m_base = tile_pass(i) * (MT * G);
-                    for (uint32_t row = te >> 4; row < uint32_t(MT * G); row += EPI_THREADS >> 4) {
+                    for (uint32_t row = te >> 4; row < uint32_t(MT * G); row += P_EPI_THREADS >> 4) {
                         const uint32_t m = m_base + row;
                         if (m >= p.M) break;
                         const uint4 val = lds128(epi0 + row * 256u + ((j ^ ((row & 1u) << 2)) << 4));
@@ -517,7 +551,7 @@ nvfp4_lora_linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x
             if (!ok) break;
             if (i + 1 < my_tiles) {
                 const long long t_l = prof ? clock64() : 0;
-                ok = build_lists(tile_pass(i + 1));
+                ok = build_lists(next_slots);
                 if (ok && te == 0) mbar_arrive(BAR_LIST);
                 if (prof) c_list += (unsigned long long)(clock64() - t_l);
             }

@@ -159,6 +159,12 @@ struct ShrinkParams {
     uint32_t chunk;                 // tokens scanned per CTA (<= 256); 0 = 256
     uint32_t part_rows;             // chunk or chunk / 2
     uint32_t ksplit;                // tensor-core shrink: CTAs per cluster sharing K (set by the launcher)
+    // Token-sharded tile output (tcgen05 shrink only): the launch covers rows [m_begin, m_begin + m_count) of the batch
+    // (m_count == 0: all of it) and writes every block row into n_tile_dest buffers of identical layout —
+    // tile_out itself and tile_out_more[0 .. n_tile_dest - 2] (the same scratch on other GPUs, mapped into this process).
+    uint32_t m_begin, m_count;
+    uint32_t n_tile_dest;           // 0 or 1: tile_out only
+    uint16_t* tile_out_more[7];
     // host side only: the A side of the adapter pool as a strided array (0: not known), for the launcher's tensor map
     const void* a_pool_base;
     size_t a_slot_stride;

@@ -355,7 +355,36 @@ def main():
                 ds.append(dw.desc(i, outs[i], flags, x=xin, seq_slot=seq_slot, out_row_stride=loc_stride))
         return ds
 
+    # Token-sharded shrink (fused collective, prefill layers): the LoRA scratch of every projection lives in symmetric
+    # memory; each rank shrinks its own 1/tp of the tokens and stores the tiles into every rank's scratch, one device
+    # barrier, then the fused calls run with the shrink result reused — instead of tp identical shrinks over all of x.
+    sharded_shrink, ws_sym = False, None
+    if fused and work.kind == "layer":
+        try:
+            ws_bufs = [symm_mem.empty(pr["ws"].numel(), dtype=torch.uint8, device=dev) for pr in dw.dl.proj]
+            ws_handles = [symm_mem.rendezvous(b, dist.group.WORLD) for b in ws_bufs]
+            ws_ptrs = [[int(p) for p in h.buffer_ptrs] for h in ws_handles]
+            for pr, b in zip(dw.dl.proj, ws_bufs):
+                pr["ws"] = b
+            ws_sym = dict(bufs=ws_bufs, handles=ws_handles, ptrs=ws_ptrs)
+        except Exception as e:
+            collective_note = f"scratch could not be mapped to the peers ({type(e).__name__}: {e}); every rank runs the whole shrink"
     descs = [build_descs(mode, s) for s in sym_sets] if fused else [build_descs(mode)]
+    descs_reuse = [build_descs(mode | ab.FLAG_REUSE_SHRINK, s) for s in sym_sets] if fused else None
+    rows_per_rank = (-(-M // tp) + 63) // 64 * 64
+    row_begin = rank * rows_per_rank
+    row_count = max(0, min(rows_per_rank, M - row_begin))
+    if ws_sym is not None:
+        try:
+            for i in range(n_proj):
+                if row_count:
+                    ab.lora_shrink_tiles(descs[0][i], row_begin, row_count, ws_sym["ptrs"][i])
+            sharded_shrink = True
+        except ab.AtlasError:
+            sharded_shrink = False
+        ok = torch.tensor([1 if sharded_shrink else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        sharded_shrink = bool(int(ok.item()))
     descs_plain = build_descs(mode)                                    # this rank's shard into its own buffers, no placement
     stream = torch.cuda.current_stream()
     step_no = [0]
@@ -364,6 +393,15 @@ def main():
         k = step_no[0] % len(descs)
         step_no[0] += 1
         v = None
+        if sharded_shrink:
+            for i in range(n_proj):
+                if row_count:
+                    ab.lora_shrink_tiles(descs[k][i], row_begin, row_count, ws_sym["ptrs"][i], stream)
+            ws_sym["handles"][0].barrier(channel=1)          # every rank's tiles are in every rank's scratch
+            for i in range(n_proj):
+                v = ab.nvfp4_lora_linear(descs_reuse[k][i], stream)
+            sym_sets[k]["handles"][0].barrier(channel=0)     # every rank's output tiles have landed in every buffer
+            return v
         for i in range(n_proj):
             v = ab.nvfp4_lora_linear(descs[k][i], stream)
             if tp > 1 and not fused:
@@ -548,6 +586,7 @@ def main():
     proj_ms = vals[5:]
 
     args.collective_used = ("tiles stored into every rank's buffer by the kernel + one device barrier per step"
+                            + ("; shrink sharded by tokens, its tiles stored into every rank's scratch + one device barrier" if sharded_shrink else "")
                             if fused else "NCCL all-gather per projection")
     if rank == 0:
         hbm_gbs, peak_kind = peaks()

@@ -72,8 +72,9 @@ extern "C" {
 #define ATLAS_B200_FLAG_NO_CTA_PAIR   32u   /* tcgen05 path: keep every CTA on its own (no two-CTA MMAs); for comparison runs */
 #define ATLAS_B200_FLAG_NO_K_SPLIT    64u   /* tcgen05 path: one CTA per output tile even when that leaves SMs idle; for comparison runs */
 #define ATLAS_B200_FLAG_NO_PERSISTENT 128u   /* tcgen05 path: one output tile per CTA even for many-tile shapes; for comparison runs */
-#define ATLAS_B200_FLAG_TWO_TILE_PASS 256u   /* tcgen05 path, persistent form, BF16 activations: passes of two 192-token tiles that share
-                                                each expanded weight stage (m >= 768) */
+#define ATLAS_B200_FLAG_ONE_TILE_PASS 256u   /* tcgen05 path, persistent form, BF16 activations: one 256-token tile per pass instead of two
+                                                192-token tiles that share each expanded weight stage (the default from 768 tokens);
+                                                for comparison runs */
 #define ATLAS_B200_ACT_FP4_WS_BYTES(m, k) \
     ((((size_t)(m) * ((k) / 2) + 255) / 256) * 256 + (size_t)(m) * ((k) / 16))
 
@@ -186,6 +187,21 @@ typedef struct atlas_b200_linear_desc {
 } atlas_b200_linear_desc;
 
 ATLAS_B200_API int atlas_b200_nvfp4_lora_linear(const atlas_b200_linear_desc* desc, void* stream);
+
+/* The shrink of a fused call alone, sharded by tokens over a tensor-parallel group (no counterpart in the reference,
+ * which recomputes nothing across ranks because it runs LoRA on one GPU only: crates/spark-server/src/main_modules/
+ * serve.rs:364-369).  Column-parallel ranks all need t = A_s x for every token, but x and A_s are replicated, so each
+ * rank would otherwise stream the whole of x through the same shrink.  Instead rank r calls this for its rows
+ * [row_begin, row_begin + row_count) (row_begin a multiple of 64; row_count 0 = to the end) and the kernel stores the
+ * LoRA activation tiles of those rows into ws_dest[0 .. n_dest): the `ws` scratch of every rank's descriptor (its own
+ * included), as mapped into this process — plain stores, over NVLink for the peers.  After the ranks have synchronised,
+ * every rank runs atlas_b200_nvfp4_lora_linear with ATLAS_B200_FLAG_REUSE_SHRINK on the same descriptor.
+ * `desc` must be the descriptor of that later call (same shapes, flags and `ws` layout on every rank; desc->ws is used
+ * only to derive where the tiles live inside a scratch buffer).  Needs what the tcgen05 shrink needs: m >= 1024, the
+ * strided A and B pools, max_rank a multiple of 16, `ws` of ATLAS_B200_LORA_WS_BYTES; -1 otherwise (the caller then
+ * lets every rank run the whole shrink inside the fused call). */
+ATLAS_B200_API int atlas_b200_lora_shrink_tiles(const atlas_b200_linear_desc* desc, uint32_t row_begin, uint32_t row_count,
+                                 void* const* ws_dest, uint32_t n_dest, void* stream);
 
 /* The fused layer for a caller that must not allocate device memory (no counterpart in the
  * reference, whose callers size their scratch from a buffer arena).  Identical to

@@ -28,7 +28,7 @@ def test_same_bits_as_one_tile_per_cta(cuda, atlas, oracle, M, K, N, ids, fp4):
     case = _case(synth, M, K, N, seed=M + N, ids=ids, segments=24)
     dc = DeviceCase(cuda, atlas, case)
     mode = atlas.FLAG_ACT_FP4 if fp4 else 0
-    y, variant = dc.run(flags=mode, lora_ws=True)
+    y, variant = dc.run(flags=mode | atlas.FLAG_ONE_TILE_PASS, lora_ws=True)
     assert variant == atlas.VARIANT_TCGEN05
     shape = atlas.last_launch_shape()
     assert shape["persistent_tiles_per_pass"] == 1 and shape["persistent_cta_pairs"] >= 32, shape
@@ -46,7 +46,7 @@ def test_base_only_and_second_call(cuda, atlas, oracle):
     case = _case(synth, 2304, 512, 4864, seed=5)
     dc = DeviceCase(cuda, atlas, case)
     y, _ = dc.run(lora=False)
-    assert atlas.last_launch_shape()["persistent_tiles_per_pass"] == 1
+    assert atlas.last_launch_shape()["persistent_tiles_per_pass"] == 2
     y2, _ = dc.run(lora=False)
     y_one, _ = dc.run(lora=False, flags=atlas.FLAG_NO_PERSISTENT)
     assert np.array_equal(y, y2) and np.array_equal(y, y_one)
@@ -61,10 +61,10 @@ def test_two_token_tiles_per_pass(cuda, atlas, oracle, M, K, N):
     from atlas_b200 import synth
     case = _case(synth, M, K, N, seed=M, ids="segments", segments=20)
     dc = DeviceCase(cuda, atlas, case)
-    y2, _ = dc.run(flags=atlas.FLAG_TWO_TILE_PASS, lora_ws=True)
+    y2, _ = dc.run(lora_ws=True)
     shape = atlas.last_launch_shape()
     assert shape["persistent_tiles_per_pass"] == 2 and shape["token_tile"] == 192, shape
-    y1, _ = dc.run(lora_ws=True)
+    y1, _ = dc.run(flags=atlas.FLAG_ONE_TILE_PASS, lora_ws=True)
     assert atlas.last_launch_shape()["persistent_tiles_per_pass"] == 1
     assert np.array_equal(y2, y1)
     y_one, _ = dc.run(flags=atlas.FLAG_NO_PERSISTENT, lora_ws=True)
@@ -80,7 +80,7 @@ def test_without_tile_scratch_the_one_tile_form_runs(cuda, atlas, oracle):
     y, _ = dc.run(lora_ws=False)
     assert atlas.last_launch_shape()["persistent_tiles_per_pass"] == 0
     y_p, _ = dc.run(lora_ws=True)
-    assert atlas.last_launch_shape()["persistent_tiles_per_pass"] == 1
+    assert atlas.last_launch_shape()["persistent_tiles_per_pass"] == 2
     assert np.array_equal(y, y_p)
     assert atlas.device_status() == 0
 
@@ -100,7 +100,7 @@ def test_placement_into_several_buffers(cuda, atlas, oracle, fp4):
     for r in range(tp):
         sh = tpmod.DeviceShard(cuda, atlas, case, tp, r)
         atlas.nvfp4_lora_linear(sh.desc(None, extra_flags=mode, out_row_stride=stride, y_dest=bufs, y_col_offset=r * sh.n_local))
-        assert atlas.last_launch_shape()["persistent_tiles_per_pass"] == 1
+        assert atlas.last_launch_shape()["persistent_tiles_per_pass"] == (1 if fp4 else 2)
     cuda.cuda.synchronize()
     want = bits_from_dev(y_ref.view(cuda.int16))
     for b in bufs:
