@@ -46,7 +46,14 @@ EXPORTS = (
     "atlas_b200_module_dims", "atlas_b200_pool_slot_bytes", "atlas_b200_slot_base_offset",
     "atlas_b200_module_slot_offsets", "atlas_b200_pack_module", "atlas_b200_build_route_tables", "atlas_b200_select_victim_slot",
     "atlas_b200_device_status", "atlas_b200_last_variant", "atlas_b200_last_launch_shape", "atlas_b200_last_persistent_shape",
-    "atlas_b200_set_profile_buffer",
+    "atlas_b200_set_profile_buffer", "atlas_b200_peft_parse", "atlas_b200_peft_config_scaling", "atlas_b200_classify_key",
+    "atlas_b200_adapter_id_hash", "atlas_b200_convert_to_bf16", "atlas_b200_registry_create", "atlas_b200_registry_destroy",
+    "atlas_b200_registry_slot_bytes", "atlas_b200_registry_pool_bytes", "atlas_b200_registry_load_adapter",
+    "atlas_b200_registry_set_pinned", "atlas_b200_registry_set_active", "atlas_b200_registry_route_tables",
+    "atlas_b200_registry_scale_table", "atlas_b200_registry_rank_table", "atlas_b200_registry_acquire_slot",
+    "atlas_b200_registry_release_slot", "atlas_b200_registry_touch_slot", "atlas_b200_registry_slot_ref_count",
+    "atlas_b200_registry_slot_last_used", "atlas_b200_registry_slot_generation", "atlas_b200_registry_slot_of",
+    "atlas_b200_registry_adapter_id_for_slot", "atlas_b200_registry_select_victim",
     "atlas_b200_version",
 )
 
@@ -72,6 +79,12 @@ class LinearDesc(C.Structure):
         ("n_dest", C.c_uint32), ("y_col_offset", C.c_uint32), ("y_dest", C.c_void_p * 8),
         ("a_pool_base", C.c_void_p), ("a_slot_stride", C.c_size_t),
     ]
+
+
+class PeftConfig(C.Structure):
+    _fields_ = [("r", C.c_size_t), ("lora_alpha", C.c_double), ("use_rslora", C.c_int32), ("n_target_modules", C.c_uint32),
+                ("target_modules", (C.c_char * 96) * 16), ("has_layers_to_transform", C.c_int32),
+                ("n_layers_to_transform", C.c_uint32), ("layers_to_transform", C.c_uint32 * 256)]
 
 
 class ModelDims(C.Structure):
@@ -121,6 +134,34 @@ def lib() -> C.CDLL:
     L.atlas_b200_device_status.argtypes = [C.POINTER(u32), C.c_int]
     L.atlas_b200_set_profile_buffer.argtypes = [vp, sz]
     L.atlas_b200_version.restype = C.c_char_p
+    u64, cp = C.c_uint64, C.c_char_p
+    L.atlas_b200_peft_parse.argtypes = [cp, sz, C.POINTER(PeftConfig), cp, sz]
+    L.atlas_b200_peft_config_scaling.argtypes = [C.POINTER(PeftConfig)]
+    L.atlas_b200_peft_config_scaling.restype = f32
+    L.atlas_b200_classify_key.argtypes = [cp, u32, vp, C.POINTER(u32), C.POINTER(C.c_int), C.POINTER(C.c_int), cp, sz]
+    L.atlas_b200_adapter_id_hash.argtypes = [cp, u64]
+    L.atlas_b200_adapter_id_hash.restype = u64
+    L.atlas_b200_convert_to_bf16.argtypes = [cp, vp, sz, vp]
+    L.atlas_b200_registry_create.argtypes = [C.POINTER(ModelDims), u32, vp, sz, sz, u64, C.POINTER(vp)]
+    L.atlas_b200_registry_destroy.argtypes = [vp]
+    L.atlas_b200_registry_destroy.restype = None
+    for fn in (L.atlas_b200_registry_slot_bytes, L.atlas_b200_registry_pool_bytes):
+        fn.argtypes, fn.restype = [vp], sz
+    L.atlas_b200_registry_load_adapter.argtypes = [vp, sz, cp, cp, sz, vp, sz, vp, cp, sz]
+    L.atlas_b200_registry_set_pinned.argtypes = [vp, sz]
+    L.atlas_b200_registry_set_active.argtypes = [vp, sz]
+    L.atlas_b200_registry_route_tables.argtypes = [vp, u32, C.c_int, vp, vp]
+    L.atlas_b200_registry_scale_table.argtypes = [vp, vp]
+    L.atlas_b200_registry_rank_table.argtypes = [vp, vp]
+    L.atlas_b200_registry_acquire_slot.argtypes, L.atlas_b200_registry_acquire_slot.restype = [vp, i32], i32
+    L.atlas_b200_registry_release_slot.argtypes, L.atlas_b200_registry_release_slot.restype = [vp, i32], None
+    L.atlas_b200_registry_touch_slot.argtypes, L.atlas_b200_registry_touch_slot.restype = [vp, sz], None
+    L.atlas_b200_registry_slot_ref_count.argtypes, L.atlas_b200_registry_slot_ref_count.restype = [vp, sz], sz
+    L.atlas_b200_registry_slot_last_used.argtypes, L.atlas_b200_registry_slot_last_used.restype = [vp, sz], u64
+    L.atlas_b200_registry_slot_generation.argtypes, L.atlas_b200_registry_slot_generation.restype = [vp, sz], u64
+    L.atlas_b200_registry_slot_of.argtypes, L.atlas_b200_registry_slot_of.restype = [vp, cp], i32
+    L.atlas_b200_registry_adapter_id_for_slot.argtypes, L.atlas_b200_registry_adapter_id_for_slot.restype = [vp, i32], u64
+    L.atlas_b200_registry_select_victim.argtypes, L.atlas_b200_registry_select_victim.restype = [vp], i32
     _lib = L
     return L
 

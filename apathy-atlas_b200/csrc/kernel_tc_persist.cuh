@@ -319,7 +319,7 @@ nvfp4_lora_linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x
         // ===================================== MMA issuer ====================================================
         if (lane == 0 && leader) {
             constexpr uint32_t idesc = make_idesc_bf16(MT, 256u);
-            unsigned long long w_full = 0, w_acc = 0, w_lora = 0;
+            unsigned long long w_full = 0, w_acc = 0, w_lora = 0, w_head = 0;
             const long long t_begin = prof ? clock64() : 0;
             bool ok = true;
             uint32_t s = 0, ph = 0, ls = 0, lph = 0;
@@ -329,6 +329,7 @@ nvfp4_lora_linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x
                     ok = mbar_wait_timed(BAR_ACC_EMPTY + 8 * g, (i & 1u) ^ 1u, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_acc, MMA_BACKOFF_NS);
                 if (!ok) break;
                 tcgen05_fence_after();
+                const unsigned long long w_full_at_pass = w_full;
                 uint32_t acc = 0;
                 if constexpr (A4) {
                     constexpr uint32_t idesc4 = make_idesc_nvfp4(MT, 256u);
@@ -348,6 +349,7 @@ nvfp4_lora_linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x
                     }
                 } else {
                     for (uint32_t it = 0; it < num_kb; ++it) {
+                        if (prof && it == 4) w_head += w_full - w_full_at_pass;
                         ok = mbar_wait_timed(BAR_FULL + 8 * s, ph, abort_flag, STATUS_WAIT_EXPIRED_MMA, prof, w_full, MMA_BACKOFF_NS);
                         if (!ok) break;
                         tcgen05_fence_after();
@@ -387,7 +389,7 @@ nvfp4_lora_linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x
             }
             if (prof) {
                 prof_row[0] = w_full; prof_row[2] = (unsigned long long)(clock64() - t_begin);
-                prof_row[10] = w_acc; prof_row[11] = w_lora;
+                prof_row[10] = w_acc; prof_row[11] = w_lora; prof_row[9] = w_head;
             }
         }
         __syncwarp();

@@ -16,6 +16,8 @@
  *     -3            misaligned pointer or stride
  *     -4            null pointer where one is required
  *     -5            limit exceeded (max_loras, max_rank, scratch capacity)
+ *     -6            adapter rejected at ingest (named reason in the caller's message buffer)
+ *     -7            registry slot busy (sequences in flight)
  *     -10 - e       CUDA runtime error e at launch
  *     -120          library was not built for this GPU architecture
  */
@@ -41,6 +43,8 @@ extern "C" {
 #define ATLAS_B200_ERR_ALIGN     (-3)
 #define ATLAS_B200_ERR_NULL      (-4)
 #define ATLAS_B200_ERR_LIMIT     (-5)
+#define ATLAS_B200_ERR_REJECT    (-6)   /* adapter ingest: the adapter cannot be applied faithfully; the reason is in the message buffer */
+#define ATLAS_B200_ERR_BUSY      (-7)   /* registry: the slot has sequences in flight */
 #define ATLAS_B200_ERR_CUDA_BASE (-10)
 #define ATLAS_B200_ERR_ARCH      (-120)
 
@@ -273,6 +277,90 @@ ATLAS_B200_API int atlas_b200_build_route_tables(const atlas_b200_model_dims* cf
  * else -1 (pool full).  Arrays describe the cache region only. */
 ATLAS_B200_API int atlas_b200_select_victim_slot(const size_t* slot_index, const uint8_t* filled, const size_t* ref_count,
                                   const uint64_t* last_used, size_t count);
+
+
+/* ---------------------------------------------------------------------------------------
+ * Adapter ingest and the adapter registry (host only, no GPU): PEFT config rules, safetensors -> BF16,
+ * key classification, audit, slot packing, routing tables and slot lifecycle.
+ */
+#define ATLAS_B200_PEFT_MAX_TARGETS 16
+#define ATLAS_B200_PEFT_MAX_LAYERS  256
+/* Parsed subset of a PEFT adapter_config.json (crates/atlas-core/src/config/parsers/lora.rs:44-78). */
+typedef struct atlas_b200_peft_config {
+    size_t   r;
+    double   lora_alpha;
+    int32_t  use_rslora;
+    uint32_t n_target_modules;
+    char     target_modules[ATLAS_B200_PEFT_MAX_TARGETS][96];   /* verbatim entries (bare names or full paths) */
+    int32_t  has_layers_to_transform;
+    uint32_t n_layers_to_transform;
+    uint32_t layers_to_transform[ATLAS_B200_PEFT_MAX_LAYERS];
+} atlas_b200_peft_config;
+
+/* `parse_peft_adapter_config` (crates/atlas-core/src/config/parsers/lora.rs:121-262): hard-fails with the reference's
+ * named REJECT(<feature>) reasons — peft_type, use_dora, bias, rank_pattern, alpha_pattern, modules_to_save, use_rslora
+ * absent, layers_to_transform malformed, r == 0, lora_alpha, target_modules string / empty / non-string entries, gdn,
+ * embedding, unknown_module.  0 on success; ATLAS_B200_ERR_REJECT with the message (NUL terminated, truncated to
+ * err_cap) in `err`; ATLAS_B200_ERR_DIMS for a document that is not JSON or lacks r / lora_alpha / target_modules. */
+ATLAS_B200_API int atlas_b200_peft_parse(const char* json, size_t len, atlas_b200_peft_config* out, char* err, size_t err_cap);
+/* `PeftAdapterConfig::scaling` of a parsed config (lora.rs:70-77). */
+ATLAS_B200_API float atlas_b200_peft_config_scaling(const atlas_b200_peft_config* cfg);
+/* `classify_key` (crates/spark-model/src/lora/key.rs:53-113): PEFT tensor name -> (global layer index, module, 0 = lora_A /
+ * 1 = lora_B).  `full_attention` [num_hidden_layers] flags the layers that carry LoRA (NULL: all of them).
+ * ATLAS_B200_ERR_REJECT with the reference's REJECT[...] reason in `err` otherwise. */
+ATLAS_B200_API int atlas_b200_classify_key(const char* key, uint32_t num_hidden_layers, const uint8_t* full_attention,
+                            uint32_t* layer, int* module, int* ab, char* err, size_t err_cap);
+/* `adapter_id_hash` (key.rs:33-47): FNV-1a of the name, the generation folded in when non-zero, never 0. */
+ATLAS_B200_API uint64_t atlas_b200_adapter_id_hash(const char* name, uint64_t generation);
+/* BF16 (round to nearest even, NaN quieted) of F16 / F32 / BF16 little-endian tensor bytes, the host conversion of
+ * `load_adapter_safetensors` (crates/spark-runtime/src/weights/adapter.rs:62-105).  dtype: "F16", "F32" or "BF16". */
+ATLAS_B200_API int atlas_b200_convert_to_bf16(const char* dtype, const void* src, size_t n_elems, void* dst_bf16);
+
+/* The registry: `LoraWeights` (crates/spark-model/src/lora/types.rs:120-200) without the device side.  It knows the
+ * pool's device base address but never touches the device: packing produces a host image of one slot that the caller
+ * uploads to pool_base + slot * slot_bytes, and the table functions produce the host images of the device tables. */
+typedef struct atlas_b200_registry atlas_b200_registry;
+/* `full_attention` [num_hidden_layers]: layers that carry LoRA modules, ascending = the pool's layer ordinals (NULL:
+ * every layer); their count must equal cfg->num_full_attention_layers. */
+ATLAS_B200_API int atlas_b200_registry_create(const atlas_b200_model_dims* cfg, uint32_t num_hidden_layers, const uint8_t* full_attention,
+                               size_t max_loras, size_t max_rank, uint64_t pool_device_base, atlas_b200_registry** out);
+ATLAS_B200_API void atlas_b200_registry_destroy(atlas_b200_registry* reg);
+ATLAS_B200_API size_t atlas_b200_registry_slot_bytes(const atlas_b200_registry* reg);
+ATLAS_B200_API size_t atlas_b200_registry_pool_bytes(const atlas_b200_registry* reg);
+/* Audit and pack one adapter into `slot`: `audit_adapter` + `pack_slot` (crates/spark-model/src/lora/loading.rs:48-230) at
+ * load time, `pack_store_into_slot` (loading.rs:401-459) for a slot that is already filled — then the slot must be idle
+ * (ATLAS_B200_ERR_BUSY, nothing changed), its generation is bumped and its table cells are refreshed.
+ *   config_json / config_len     adapter_config.json
+ *   safetensors / st_len         adapter_model.safetensors (F16 / F32 / BF16 tensors; anything else is rejected)
+ *   slot_image                   receives the slot's byte image (atlas_b200_registry_slot_bytes long, zero padded)
+ * Every rejection of the reference is reproduced by name: the config rules above, REJECT[rank-exceeds-max], the
+ * classify_key reasons, duplicate-tensor, empty-adapter, unpaired-tensor, shape-mismatch, unmatched-target. */
+ATLAS_B200_API int atlas_b200_registry_load_adapter(atlas_b200_registry* reg, size_t slot, const char* name,
+                                     const char* config_json, size_t config_len, const void* safetensors, size_t st_len,
+                                     void* slot_image, char* err, size_t err_cap);
+/* Slots [0, pinned) are never eviction victims (the start-up adapter set, loading.rs:300-312). */
+ATLAS_B200_API int atlas_b200_registry_set_pinned(atlas_b200_registry* reg, size_t pinned);
+ATLAS_B200_API int atlas_b200_registry_set_active(atlas_b200_registry* reg, size_t slot);
+/* Host images of the device tables: for (global layer, module) the [max_loras] A / B address tables (0 = base only), the
+ * scale table and the true-rank table (`load_lora_adapters_multi` post-pass, loading.rs:310-369; `refresh_slot_tables`,
+ * types.rs:338-373).  ATLAS_B200_ERR_DIMS for a layer that carries no LoRA. */
+ATLAS_B200_API int atlas_b200_registry_route_tables(const atlas_b200_registry* reg, uint32_t layer, int module, uint64_t* a_table, uint64_t* b_table);
+ATLAS_B200_API int atlas_b200_registry_scale_table(const atlas_b200_registry* reg, float* out);
+ATLAS_B200_API int atlas_b200_registry_rank_table(const atlas_b200_registry* reg, uint32_t* out);
+/* Slot lifecycle (types.rs:268-413): acquire resolves `slot` (>= 0: that slot, -1: the active one), takes a reference,
+ * stamps the slot as most recently used and returns the resolved index (-1: out of range, nothing taken); release is
+ * saturating and ignores -1; touch stamps without taking a reference. */
+ATLAS_B200_API int32_t atlas_b200_registry_acquire_slot(atlas_b200_registry* reg, int32_t slot);
+ATLAS_B200_API void atlas_b200_registry_release_slot(atlas_b200_registry* reg, int32_t resolved);
+ATLAS_B200_API void atlas_b200_registry_touch_slot(atlas_b200_registry* reg, size_t slot);
+ATLAS_B200_API size_t atlas_b200_registry_slot_ref_count(const atlas_b200_registry* reg, size_t slot);
+ATLAS_B200_API uint64_t atlas_b200_registry_slot_last_used(const atlas_b200_registry* reg, size_t slot);
+ATLAS_B200_API uint64_t atlas_b200_registry_slot_generation(const atlas_b200_registry* reg, size_t slot);
+ATLAS_B200_API int32_t atlas_b200_registry_slot_of(const atlas_b200_registry* reg, const char* name);
+ATLAS_B200_API uint64_t atlas_b200_registry_adapter_id_for_slot(const atlas_b200_registry* reg, int32_t slot);
+/* `cache_slot_views` + `select_victim_slot` over the cache region [pinned, max_loras): a never-filled slot first, else
+ * the least recently used idle slot, else -1 (every cache slot is busy). */
+ATLAS_B200_API int32_t atlas_b200_registry_select_victim(const atlas_b200_registry* reg);
 
 /* ---------------------------------------------------------------------------------------
  * Diagnostics.

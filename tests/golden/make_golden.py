@@ -1,6 +1,6 @@
 """Regenerates the golden fixtures in this directory from a checkout of the reference.
 
-Usage:  python tests/golden/make_golden.py [/path/to/reference]
+Usage:  python tests/golden/make_golden.py /path/to/reference
 
 Needs the reference checkout (it is read as data: numeric tables are parsed out of its source
 text, and the PEFT fixture is pushed through the same torch expression its offline parity script
@@ -11,6 +11,9 @@ uses).  The outputs are committed; the tests never read the reference itself.
   peft_delta_k_proj.npz  lora_A / lora_B of layer 11 k_proj from test_data/lora-holo-tiny and
                        delta = scaling * B.float() @ A.float() (scripts/reference_deltas.py:77-93),
                        first 32 input columns
+  peft_holo_tiny_pairs.npz  for every (layer, module) pair of that adapter: its PEFT key, the shapes, and of
+                       delta = scaling * B @ A (float64 accumulation of the BF16 factors) the sum, the sum of magnitudes
+                       and the top-left 4 x 4 block
 """
 import json
 import os
@@ -19,7 +22,9 @@ import sys
 
 import numpy as np
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit(__doc__)
+REF = sys.argv[1]
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 
@@ -56,6 +61,17 @@ def main():
         a_bits=a.view(torch.int16).numpy().view(np.uint16), b_bits=b.view(torch.int16).numpy().view(np.uint16),
         scaling=np.float32(scaling), r=np.int32(r), alpha=np.float32(alpha), use_rslora=np.int32(rs),
         delta_cols32=delta[:, :32].contiguous().numpy())
+    keys = sorted(k[: -len(".lora_A.weight")] for k in t if k.endswith(".lora_A.weight"))
+    sums, abs_sums, corners, shapes = [], [], [], []
+    for k in keys:
+        a64 = t[k + ".lora_A.weight"].double().numpy()
+        b64 = t[k + ".lora_B.weight"].double().numpy()
+        dl = scaling * (b64 @ a64)
+        sums.append(dl.sum()); abs_sums.append(np.abs(dl).sum()); corners.append(dl[:4, :4].copy())
+        shapes.append([b64.shape[0], a64.shape[1], a64.shape[0]])
+    np.savez_compressed(os.path.join(OUT, "peft_holo_tiny_pairs.npz"), keys=np.array(keys), sums=np.array(sums),
+                        abs_sums=np.array(abs_sums), corners=np.array(corners), shapes=np.array(shapes, dtype=np.int64),
+                        n_tensors=np.int64(len(t)), scaling=np.float64(scaling))
     print("wrote", os.listdir(OUT))
 
 
