@@ -24,7 +24,7 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libatlas_b200.so")
 
 VARIANT_NONE, VARIANT_SIMT, VARIANT_TCGEN05 = 0, 1, 2
 FLAG_FORCE_SIMT, FLAG_FORCE_TCGEN05, FLAG_STAGED_LORA, FLAG_REUSE_SHRINK, FLAG_ACT_FP4, FLAG_NO_CTA_PAIR, FLAG_NO_K_SPLIT = 1, 2, 4, 8, 16, 32, 64
-FLAG_NO_PERSISTENT, FLAG_ONE_TILE_PASS = 128, 256
+FLAG_NO_PERSISTENT, FLAG_ONE_TILE_PASS, FLAG_ACT_FP4_READY = 128, 256, 512
 
 
 def lora_ws_bytes(m: int, max_loras: int, max_rank: int) -> int:
@@ -39,7 +39,9 @@ MODULES = ("q", "k", "v", "o", "gate", "up", "down")
 
 EXPORTS = (
     "atlas_b200_lora_bgmv", "atlas_b200_lora_delta", "atlas_b200_w4a16_gemm",
-    "atlas_b200_dequant_nvfp4_to_bf16", "atlas_b200_quantize_bf16_to_nvfp4",
+    "atlas_b200_dequant_nvfp4_to_bf16", "atlas_b200_quantize_bf16_to_nvfp4", "atlas_b200_nvfp4_global_absmax",
+    "atlas_b200_nvfp4_scale2_from_absmax", "atlas_b200_nvfp4_combined_global_scale", "atlas_b200_silu_mul",
+    "atlas_b200_silu_mul_quant_nvfp4",
     "atlas_b200_nvfp4_lora_linear", "atlas_b200_nvfp4_lora_linear_noalloc", "atlas_b200_lora_shrink_tiles",
     "atlas_b200_column_shard",
     "atlas_b200_build_seq_slot", "atlas_b200_routed_prefill_slot_of", "atlas_b200_peft_scaling",
@@ -113,6 +115,11 @@ def lib() -> C.CDLL:
     L.atlas_b200_dequant_nvfp4_to_bf16.argtypes = [vp, vp, vp, f32, u32, u32, vp]
     L.atlas_b200_quantize_bf16_to_nvfp4.argtypes = [vp, vp, vp, f32, u32, u32, vp]
     L.atlas_b200_nvfp4_lora_linear.argtypes = [C.POINTER(LinearDesc), vp]
+    L.atlas_b200_nvfp4_global_absmax.argtypes = [vp, vp, sz, vp]
+    L.atlas_b200_nvfp4_scale2_from_absmax.argtypes, L.atlas_b200_nvfp4_scale2_from_absmax.restype = [f32], f32
+    L.atlas_b200_nvfp4_combined_global_scale.argtypes, L.atlas_b200_nvfp4_combined_global_scale.restype = [f32, C.c_int], f32
+    L.atlas_b200_silu_mul.argtypes = [vp, vp, vp, f32, f32, f32, u32, u32, u32, u32, vp]
+    L.atlas_b200_silu_mul_quant_nvfp4.argtypes = [vp, vp, vp, sz, f32, f32, f32, u32, u32, u32, vp]
     L.atlas_b200_nvfp4_lora_linear_noalloc.argtypes = [C.POINTER(LinearDesc), vp]
     L.atlas_b200_lora_shrink_tiles.argtypes = [C.POINTER(LinearDesc), u32, u32, C.POINTER(vp), u32, vp]
     L.atlas_b200_column_shard.argtypes = [u32, u32, u32, C.POINTER(u32), C.POINTER(u32)]
@@ -296,6 +303,31 @@ def dequant_nvfp4_to_bf16(packed, scales, out, combined_global: float, n: int, k
 def quantize_bf16_to_nvfp4(inp, packed, scales, scale2: float, n: int, k: int, stream=None) -> None:
     _check("atlas_b200_quantize_bf16_to_nvfp4", lib().atlas_b200_quantize_bf16_to_nvfp4(
         _ptr(inp), _ptr(packed), _ptr(scales), scale2, n, k, _stream_ptr(stream)))
+
+
+def nvfp4_global_absmax(inp, out_max, total: int, stream=None) -> None:
+    """max |inp| into the device float `out_max` (zeroed by the caller)."""
+    _check("atlas_b200_nvfp4_global_absmax", lib().atlas_b200_nvfp4_global_absmax(_ptr(inp), _ptr(out_max), total, _stream_ptr(stream)))
+
+
+def scale2_from_absmax(global_max: float) -> float:
+    return float(lib().atlas_b200_nvfp4_scale2_from_absmax(global_max))
+
+
+def combined_global_scale(stored: float, is_reciprocal: bool) -> float:
+    return float(lib().atlas_b200_nvfp4_combined_global_scale(stored, int(is_reciprocal)))
+
+
+def silu_mul(gate, up, out, m: int, k: int, gate_scale=1.0, up_scale=1.0, swiglu_limit=0.0, in_row_stride=None,
+             out_row_stride=None, stream=None) -> None:
+    _check("atlas_b200_silu_mul", lib().atlas_b200_silu_mul(_ptr(gate), _ptr(up), _ptr(out), gate_scale, up_scale, swiglu_limit,
+                                                            m, k, in_row_stride or k, out_row_stride or k, _stream_ptr(stream)))
+
+
+def silu_mul_quant_nvfp4(gate, up, ws, ws_bytes: int, m: int, k: int, gate_scale=1.0, up_scale=1.0, swiglu_limit=0.0,
+                         in_row_stride=None, stream=None) -> None:
+    _check("atlas_b200_silu_mul_quant_nvfp4", lib().atlas_b200_silu_mul_quant_nvfp4(
+        _ptr(gate), _ptr(up), _ptr(ws), ws_bytes, gate_scale, up_scale, swiglu_limit, m, k, in_row_stride or k, _stream_ptr(stream)))
 
 
 def make_linear_desc(*, x, m, k, n, y, w_packed=None, w_scale=None, scale2=1.0, w_bf16=None,

@@ -23,6 +23,7 @@
 #include "kernels_simt.cuh"
 #include "kernel_shrink_mma.cuh"
 #include "kernel_shrink_tc.cuh"
+#include "kernels_mlp_glue.cuh"
 
 namespace atlas {
 
@@ -644,14 +645,16 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st, const Sh
         if (!d.ws || !aligned(d.ws, 256)) return d.ws ? ATLAS_B200_ERR_ALIGN : ATLAS_B200_ERR_NULL;
         if (d.ws_bytes < act_fp4_ws_bytes(d)) return ATLAS_B200_ERR_WORKSPACE;
         // x -> NVFP4 with a tensor scale of one (scale byte = E4M3 of group max / 6), the activation side
-        // of crates/spark-model/src/layers/ops/gemm_fp4.rs:20-40
+        // of crates/spark-model/src/layers/ops/gemm_fp4.rs:20-40 — unless the caller says they are in place already
         uint8_t* codes = static_cast<uint8_t*>(d.ws);
+        if (!(d.flags & ATLAS_B200_FLAG_ACT_FP4_READY) && !shrink_only) {
         const size_t groups = size_t(d.m) * (d.k / 16);
         const unsigned blocks = unsigned(std::min<size_t>((groups + 255) / 256, size_t(rt_sm_count()) * 16));
         quantize_nvfp4_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(d.x), codes, codes + act_fp4_codes_bytes(d),
                                                       1.0f, d.m, d.k, d.x_row_stride, 1u);
         rc = launch_status();
         if (rc) return rc;
+        }
     }
     if (use_tc) {
         // Token tile: the smallest power of two that covers m, at most 256 — then halved (down to 64)
@@ -878,6 +881,54 @@ int atlas_b200_quantize_bf16_to_nvfp4(const void* in_bf16, void* packed, void* s
     const uint32_t vec = aligned(in_bf16, 16) && aligned(packed, 8) && k % 16 == 0;
     quantize_nvfp4_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(in_bf16), static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales), scale2, n, k, k, vec);
+    return launch_status();
+}
+
+int atlas_b200_nvfp4_global_absmax(const void* in_bf16, float* global_max_dev, size_t total, void* stream) {
+    if (total == 0) return ATLAS_B200_OK;
+    if (!in_bf16 || !global_max_dev) return ATLAS_B200_ERR_NULL;
+    if (!aligned(in_bf16, 2) || !aligned(global_max_dev, 4)) return ATLAS_B200_ERR_ALIGN;
+    const unsigned blocks = unsigned(std::min<size_t>((total / 8 + 255) / 256 + 1, size_t(rt_sm_count()) * 8));
+    nvfp4_global_absmax_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint16_t*>(in_bf16), global_max_dev, total);
+    return launch_status();
+}
+
+float atlas_b200_nvfp4_scale2_from_absmax(float global_max) { return global_max / (6.0f * 448.0f); }
+
+float atlas_b200_nvfp4_combined_global_scale(float stored_scale, int is_reciprocal) {
+    if (!is_reciprocal) return stored_scale;
+    return stored_scale != 0.0f ? 1.0f / stored_scale : 0.0f;
+}
+
+int atlas_b200_silu_mul(const void* gate_bf16, const void* up_bf16, void* out_bf16, float gate_scale, float up_scale, float swiglu_limit,
+                        uint32_t m, uint32_t k, uint32_t in_row_stride, uint32_t out_row_stride, void* stream) {
+    if (m == 0 || k == 0) return ATLAS_B200_OK;
+    if (!gate_bf16 || !up_bf16 || !out_bf16) return ATLAS_B200_ERR_NULL;
+    if (k % 8 != 0 || in_row_stride < k || out_row_stride < k) return ATLAS_B200_ERR_DIMS;
+    if (in_row_stride % 8 != 0 || out_row_stride % 8 != 0 || !aligned(gate_bf16, 16) || !aligned(up_bf16, 16) || !aligned(out_bf16, 16))
+        return ATLAS_B200_ERR_ALIGN;
+    const size_t vecs = size_t(m) * (k / 8);
+    const unsigned blocks = unsigned(std::min<size_t>((vecs + 255) / 256, size_t(rt_sm_count()) * 16));
+    silu_mul_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(gate_bf16), static_cast<const uint16_t*>(up_bf16), static_cast<uint16_t*>(out_bf16), gate_scale,
+        up_scale, swiglu_limit, m, k, in_row_stride, out_row_stride);
+    return launch_status();
+}
+
+int atlas_b200_silu_mul_quant_nvfp4(const void* gate_bf16, const void* up_bf16, void* ws, size_t ws_bytes, float gate_scale, float up_scale,
+                                    float swiglu_limit, uint32_t m, uint32_t k, uint32_t in_row_stride, void* stream) {
+    if (m == 0 || k == 0) return ATLAS_B200_OK;
+    if (!gate_bf16 || !up_bf16 || !ws) return ATLAS_B200_ERR_NULL;
+    if (k % 16 != 0 || in_row_stride < k) return ATLAS_B200_ERR_DIMS;
+    if (in_row_stride % 8 != 0 || !aligned(gate_bf16, 16) || !aligned(up_bf16, 16) || !aligned(ws, 256)) return ATLAS_B200_ERR_ALIGN;
+    const size_t codes_bytes = (size_t(m) * (k / 2) + 255) / 256 * 256;
+    if (ws_bytes < codes_bytes + size_t(m) * (k / 16)) return ATLAS_B200_ERR_WORKSPACE;
+    const size_t groups = size_t(m) * (k / 16);
+    const unsigned blocks = unsigned(std::min<size_t>((groups + 255) / 256, size_t(rt_sm_count()) * 16));
+    uint8_t* codes = static_cast<uint8_t*>(ws);
+    silu_mul_quant_nvfp4_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(gate_bf16), static_cast<const uint16_t*>(up_bf16), codes, codes + codes_bytes, gate_scale, up_scale,
+        swiglu_limit, m, k, in_row_stride);
     return launch_status();
 }
 

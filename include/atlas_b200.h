@@ -79,6 +79,8 @@ extern "C" {
 #define ATLAS_B200_FLAG_ONE_TILE_PASS 256u   /* tcgen05 path, persistent form, BF16 activations: one 256-token tile per pass instead of two
                                                 192-token tiles that share each expanded weight stage (the default from 768 tokens);
                                                 for comparison runs */
+#define ATLAS_B200_FLAG_ACT_FP4_READY 512u    /* with ATLAS_B200_FLAG_ACT_FP4: `ws` already holds the quantised activations of this call (written by
+                                                atlas_b200_silu_mul_quant_nvfp4, or by an earlier call over the same x); the quantiser is skipped */
 #define ATLAS_B200_ACT_FP4_WS_BYTES(m, k) \
     ((((size_t)(m) * ((k) / 2) + 255) / 256) * 256 + (size_t)(m) * ((k) / 16))
 
@@ -130,6 +132,32 @@ ATLAS_B200_API int atlas_b200_dequant_nvfp4_to_bf16(const void* packed, const vo
  * Replaces `quantize_bf16_to_nvfp4` (kernels/gb10/common/quantize_bf16_to_nvfp4.cu:176-243). */
 ATLAS_B200_API int atlas_b200_quantize_bf16_to_nvfp4(const void* in_bf16, void* packed, void* scales,
                                       float scale2, uint32_t n, uint32_t k, void* stream);
+
+/* First phase of the weight quantiser: *global_max (a device float the caller has zeroed) becomes max |in| over `total`
+ * BF16 elements.  Replaces `nvfp4_global_absmax` (kernels/gb10/common/quantize_bf16_to_nvfp4.cu:131-167). */
+ATLAS_B200_API int atlas_b200_nvfp4_global_absmax(const void* in_bf16, float* global_max_dev, size_t total, void* stream);
+/* scale2 the quantiser uses for a tensor with that maximum: max / (6 * 448) (quantize_bf16_to_nvfp4.cu:174-175). */
+ATLAS_B200_API float atlas_b200_nvfp4_scale2_from_absmax(float global_max);
+/* The two checkpoint conventions for the per-tensor scale folded into the one multiplier the kernels take (`scale2` /
+ * `combined_global`): ModelOpt stores a direct multiplier (weight_scale_2), compressed-tensors a reciprocal
+ * (weight_global_scale), 0 mapping to 0 (crates/spark-model/src/weight_map/fp8_lut.rs:46-57). */
+ATLAS_B200_API float atlas_b200_nvfp4_combined_global_scale(float stored_scale, int is_reciprocal);
+
+/* SwiGLU between the gate / up and the down projection: out = SiLU(min(g, L)) * clamp(u, -L, L) with g = gate * gate_scale,
+ * u = up * up_scale, L = swiglu_limit (0: no clamp); BF16 in, FP32 math with the fast exponential, BF16 out.  Replaces
+ * `moe_silu_mul` / `silu_mul_noclamp` (kernels/gb10/common/moe_silu_mul.cu:14-54).  gate, up [m, in_row_stride], out
+ * [m, out_row_stride]; k a multiple of 8, strides multiples of 8 elements, pointers 16-byte aligned. */
+ATLAS_B200_API int atlas_b200_silu_mul(const void* gate_bf16, const void* up_bf16, void* out_bf16, float gate_scale, float up_scale,
+                        float swiglu_limit, uint32_t m, uint32_t k, uint32_t in_row_stride, uint32_t out_row_stride, void* stream);
+/* The same product quantised straight to NVFP4 for the down projection's FP4-activation mode, so that the BF16
+ * intermediate never reaches memory: the fusion of `nvfp4_silu_mul_quant` (crates/spark-model/src/layers/ops/
+ * nvfp4_mmq.rs:126-157), with this library's activation quantiser (group of 16, E4M3(group max / 6), tensor scale 1).
+ * `ws` receives what an ATLAS_B200_FLAG_ACT_FP4 call writes there: packed codes [m, k/2], then — 256-byte aligned —
+ * scale bytes [m, k/16]; ws_bytes >= ATLAS_B200_ACT_FP4_WS_BYTES(m, k).  The down projection then runs with
+ * ATLAS_B200_FLAG_ACT_FP4 | ATLAS_B200_FLAG_ACT_FP4_READY on that `ws` (its x is only read by the LoRA shrink).
+ * k a multiple of 16. */
+ATLAS_B200_API int atlas_b200_silu_mul_quant_nvfp4(const void* gate_bf16, const void* up_bf16, void* ws, size_t ws_bytes, float gate_scale,
+                                    float up_scale, float swiglu_limit, uint32_t m, uint32_t k, uint32_t in_row_stride, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * The fused layer:  y = dequant_NVFP4(W) x + scale_s B_s (A_s x),  y written once.

@@ -547,3 +547,45 @@ int orc_set_num_threads(int n) {
     return 1;
 #endif
 }
+
+/* SwiGLU between the gate / up and the down projection, the arithmetic of kernels/gb10/common/moe_silu_mul.cu:14-54
+ * (clamped at `limit` when limit > 0: gate from above only, up on both sides) with the per-projection scale folds of
+ * kernels/gb10/qwen3.6-27b/nvfp4/nvfp4_mmq.cu:126-139.  FP32; the GPU's fast exponential differs from expf in the last
+ * bits, which is why comparisons with this function allow one BF16 ulp. */
+static float orc_swiglu(float g, float u, float limit) {
+    if (limit > 0.0f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    return g * (1.0f / (1.0f + expf(-g))) * u;
+}
+
+void orc_silu_mul(const uint16_t *gate, const uint16_t *up, float *out_f32, float gate_scale, float up_scale, float limit, size_t total) {
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < (long)total; i++)
+        out_f32[i] = orc_swiglu(orc_bf16_to_f32(gate[i]) * gate_scale, orc_bf16_to_f32(up[i]) * up_scale, limit);
+}
+
+/* The activation quantiser of the FP4-activation mode applied to FP32 values (what the fused SwiGLU + quantise kernel
+ * does): group of 16, scale byte = software E4M3 encode of max / 6 with tensor scale 1
+ * (kernels/gb10/common/quantize_bf16_to_nvfp4.cu:176-243 with scale2 = 1), codes by the E2M1 bins of :109-124. */
+void orc_quantize_f32_to_nvfp4_scale1(const float *in, uint8_t *packed, uint8_t *scales, uint32_t M, uint32_t K) {
+    uint32_t groups = K / 16;
+#pragma omp parallel for schedule(static)
+    for (long row = 0; row < (long)M; row++) {
+        for (uint32_t g = 0; g < groups; g++) {
+            const float *p = in + (size_t)row * K + g * 16;
+            float mx = 0.0f;
+            for (int i = 0; i < 16; i++) mx = fmaxf(mx, fabsf(p[i]));
+            uint8_t sf = orc_e4m3_encode(mx > 0.0f ? mx / 6.0f : 0.0f);
+            scales[(size_t)row * groups + g] = sf;
+            float dec = orc_e4m3_decode(sf);
+            float inv = dec > 0.0f ? 1.0f / dec : 0.0f;
+            for (int i = 0; i < 16; i += 2) {
+                uint32_t n0 = orc_e2m1_quantize(p[i] * inv);
+                uint32_t n1 = orc_e2m1_quantize(p[i + 1] * inv);
+                packed[(size_t)row * (K / 2) + g * 8 + i / 2] = (uint8_t)(n0 | (n1 << 4));
+            }
+        }
+    }
+}

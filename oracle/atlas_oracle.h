@@ -114,6 +114,8 @@ void orc_fused_linear_f32(const orc_fused_args *g, const uint32_t *rows, uint32_
 /* Reference launch sequence on the CPU: base (bf16-rounded weights, bf16 out) then staged bgmv. */
 void orc_reference_sequence(const orc_fused_args *g, uint16_t *y, uint16_t *xa, uint32_t out_row_stride);
 
+void orc_silu_mul(const uint16_t *gate, const uint16_t *up, float *out_f32, float gate_scale, float up_scale, float limit, size_t total);
+void orc_quantize_f32_to_nvfp4_scale1(const float *in, uint8_t *packed, uint8_t *scales, uint32_t M, uint32_t K);
 int orc_num_threads(void);
 int orc_set_num_threads(int n);   /* n <= 0: one per online core; returns the count in effect */
 

@@ -90,6 +90,8 @@ def lib() -> C.CDLL:
         L.orc_fused_linear_f32.argtypes = [C.POINTER(FusedArgs), C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
         L.orc_reference_sequence.argtypes = [C.POINTER(FusedArgs), C.c_void_p, C.c_void_p, C.c_uint32]
         L.orc_num_threads.restype = C.c_int
+        L.orc_silu_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_float, C.c_size_t]
+        L.orc_quantize_f32_to_nvfp4_scale1.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32]
         L.orc_set_num_threads.restype = C.c_int
         L.orc_set_num_threads.argtypes = [C.c_int]
         _lib = L
@@ -250,6 +252,22 @@ def reference_sequence(x, M, N, K, out_row_stride=None, **kw):
     xa = np.zeros((M, max(g.max_rank, 1)), dtype=np.uint16)
     lib().orc_reference_sequence(C.byref(g), _p(y), _p(xa), os_)
     return y, xa
+
+
+def silu_mul(gate, up, gate_scale=1.0, up_scale=1.0, limit=0.0) -> np.ndarray:
+    """FP32 SwiGLU of two BF16 bit arrays of one shape."""
+    out = np.empty(gate.shape, dtype=np.float32)
+    lib().orc_silu_mul(_p(np.ascontiguousarray(gate)), _p(np.ascontiguousarray(up)), _p(out), gate_scale, up_scale, limit, gate.size)
+    return out
+
+
+def quantize_f32_to_nvfp4_scale1(v: np.ndarray):
+    """[M, K] FP32 -> (packed [M, K/2], scales [M, K/16]) with the activation quantiser (tensor scale 1)."""
+    M, K = v.shape
+    packed = np.empty((M, K // 2), dtype=np.uint8)
+    scales = np.empty((M, K // 16), dtype=np.uint8)
+    lib().orc_quantize_f32_to_nvfp4_scale1(_p(np.ascontiguousarray(v, dtype=np.float32)), _p(packed), _p(scales), M, K)
+    return packed, scales
 
 
 def num_threads() -> int:
