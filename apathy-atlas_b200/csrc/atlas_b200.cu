@@ -20,6 +20,7 @@
 #include "common.cuh"
 #include "kernel_tc.cuh"
 #include "kernel_tc_persist.cuh"
+#include "kernel_dense_tc.cuh"
 #include "kernels_simt.cuh"
 #include "kernel_shrink_mma.cuh"
 #include "kernel_shrink_tc.cuh"
@@ -59,6 +60,7 @@ struct DeviceState {
     int persist_clusters[kPersistKernels] = {};
     bool carveout_set = false;
     bool shrink_tc_attr_set = false;
+    bool dense_attr_set[5] = {};      // token tiles 16, 32, 64, 128, 256 of the dense-BF16 kernel
 };
 static DeviceState g_dev[kMaxDevices];
 static std::mutex g_dev_mutex;
@@ -601,6 +603,59 @@ static int launch_tc_persist(const atlas_b200_linear_desc& d, int idx, const Shr
                                           maps.xs, maps.t, p, pp));
 }
 
+// ---- dense-BF16 base on the tensor cores (kernel_dense_tc.cuh) ----
+static bool dense_tc_eligible(const atlas_b200_linear_desc& d) {
+    DeviceState* dst = device_state();
+    return dst && dst->sm100 && g_encode && d.w_bf16 && d.k % tc::KB == 0 && d.x_row_stride % 8 == 0 && aligned(d.x, 16) &&
+           aligned(d.w_bf16, 16) && !d.n_dest;
+}
+
+template <int MT>
+static int launch_dense_tc_mt(const atlas_b200_linear_desc& d, int idx, uint32_t k_split, cudaStream_t st) {
+    using C = tc::DCfg<MT>;
+    DeviceState* dst = device_state();
+    if (!dst->dense_attr_set[idx]) {
+        cudaError_t e = cudaFuncSetAttribute(tc::dense_bf16_linear_tc_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return cuda_status(e);
+        dst->dense_attr_set[idx] = true;
+    }
+    CUtensorMap map_x, map_w;
+    if (!encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.x, d.k, d.m, uint64_t(d.x_row_stride) * 2, tc::KB, MT, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !encode_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d.w_bf16, d.k, d.n, uint64_t(d.k) * 2, tc::KB, tc::FT, CU_TENSOR_MAP_SWIZZLE_128B))
+        return ATLAS_B200_ERR_DIMS;
+    tc::DParams p{};
+    p.y = static_cast<uint16_t*>(d.y);
+    p.M = d.m; p.N = d.n; p.K = d.k; p.out_row_stride = d.out_row_stride; p.k_split = k_split;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((d.n + tc::FT - 1) / tc::FT, (d.m + MT - 1) / MT, k_split);
+    if (cfg.gridDim.y > 65535) return ATLAS_B200_ERR_LIMIT;
+    cfg.blockDim = dim3(tc::D_THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = k_split;
+    cfg.attrs = attr;
+    cfg.numAttrs = k_split > 1 ? 1 : 0;
+    return cuda_status(cudaLaunchKernelEx(&cfg, tc::dense_bf16_linear_tc_kernel<MT>, map_x, map_w, p));
+}
+
+static int launch_dense_tc(const atlas_b200_linear_desc& d, cudaStream_t st) {
+    uint32_t mt = 16;
+    while (mt < 128 && mt < d.m) mt <<= 1;
+    // few output tiles (a decode batch): CTAs along z share a tile's K so that every SM streams weights
+    const uint32_t tiles = ((d.n + tc::FT - 1) / tc::FT) * ((d.m + mt - 1) / mt);
+    uint32_t k_split = std::max(1u, std::min(std::min(uint32_t(rt_sm_count()) / std::max(tiles, 1u), 8u), d.k / uint32_t(tc::KB)));
+    while (k_split & (k_split - 1)) --k_split;           // a power of two: clusters of 1, 2, 4 or 8
+    t_last_shape[0] = mt; t_last_shape[1] = 0u; t_last_shape[2] = k_split; t_last_shape[3] = 0u; t_last_shape[4] = 0u; t_last_shape[5] = 0u;
+    if (mt == 16) return launch_dense_tc_mt<16>(d, 0, k_split, st);
+    if (mt == 32) return launch_dense_tc_mt<32>(d, 1, k_split, st);
+    if (mt == 64) return launch_dense_tc_mt<64>(d, 2, k_split, st);
+    return launch_dense_tc_mt<128>(d, 3, k_split, st);
+}
+
 static int validate_linear(const atlas_b200_linear_desc& d) {
     if (!d.x || (!d.y && !d.n_dest)) return ATLAS_B200_ERR_NULL;
     if (d.n_dest > uint32_t(tc::MAX_DEST)) return ATLAS_B200_ERR_LIMIT;
@@ -635,7 +690,8 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st, const Sh
 
     const bool staged = (d.flags & ATLAS_B200_FLAG_STAGED_LORA) != 0;
     bool use_tc = !(d.flags & ATLAS_B200_FLAG_FORCE_SIMT) && !staged && tc_eligible(d);
-    if (!use_tc && ((d.flags & ATLAS_B200_FLAG_FORCE_TCGEN05) || shrink_only)) return ATLAS_B200_ERR_DIMS;
+    if (!use_tc && shrink_only) return ATLAS_B200_ERR_DIMS;
+    if (!use_tc && (d.flags & ATLAS_B200_FLAG_FORCE_TCGEN05) && !(d.w_bf16 && !staged && dense_tc_eligible(d))) return ATLAS_B200_ERR_DIMS;
     if (!use_tc && d.n_dest) return ATLAS_B200_ERR_DIMS;          // placement into several buffers is the tcgen05 epilogue's
 
     const bool act_fp4 = (d.flags & ATLAS_B200_FLAG_ACT_FP4) != 0;
@@ -794,8 +850,10 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st, const Sh
         return rc;
     }
 
-    // CUDA-core path: base linear, then the reference's two-stage LoRA in place
-    rc = launch_simt_linear(d, st);
+    // Base linear — a dense BF16 weight on the tensor cores where the shape allows, everything else on CUDA cores —
+    // then the reference's two-stage LoRA in place
+    const bool dense_tc = !(d.flags & ATLAS_B200_FLAG_FORCE_SIMT) && !staged && dense_tc_eligible(d);
+    rc = dense_tc ? launch_dense_tc(d, st) : launch_simt_linear(d, st);
     if (rc) return rc;
     if (d.seq_slot) {
         ShrinkParams sp{};
@@ -820,7 +878,7 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st, const Sh
         rc = launch_expand(ep, st);
         if (rc) return rc;
     }
-    t_last_variant = ATLAS_B200_VARIANT_SIMT;
+    t_last_variant = dense_tc ? ATLAS_B200_VARIANT_TCGEN05 : ATLAS_B200_VARIANT_SIMT;
     return ATLAS_B200_OK;
 }
 
