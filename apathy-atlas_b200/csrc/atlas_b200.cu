@@ -14,6 +14,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -92,16 +93,52 @@ static DeviceState* device_state() {
 
 static int rt_sm_count() { DeviceState* st = device_state(); return st ? st->sm_count : 148; }
 
+// Encoded tensor maps are a pure function of (address, shape, strides, box, type, swizzle): a serving loop calls with the
+// same tensors step after step, so the most recent encodings are kept per host thread (direct-mapped, 64 entries) and a
+// repeated call costs a compare instead of a driver call per map.
+struct MapKey {
+    const void* base;
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    int32_t rank, dtype, swizzle;
+};
+struct MapEntry {
+    MapKey key;
+    CUtensorMap map;
+    bool valid;
+};
+static thread_local MapEntry t_map_cache[64];
+
+static bool encode_tiled(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, const void* base, const uint64_t* dims,
+                         const uint64_t* strides, const uint32_t* box, CUtensorMapSwizzle swz,
+                         CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B) {
+    MapKey key;
+    std::memset(&key, 0, sizeof(key));
+    key.base = base; key.rank = int32_t(rank); key.dtype = int32_t(dt); key.swizzle = int32_t(swz) | (int32_t(promo) << 8);
+    for (uint32_t i = 0; i < rank; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+    for (uint32_t i = 0; i + 1 < rank; ++i) key.strides[i] = strides[i];
+    uint64_t h = reinterpret_cast<uintptr_t>(base) * 0x9E3779B97F4A7C15ull;
+    h ^= (key.dims[0] * 31 + key.dims[1]) * 0xBF58476D1CE4E5B9ull + key.box[0] * 131 + key.box[1] * 17 + uint64_t(key.swizzle);
+    MapEntry& e = t_map_cache[(h >> 32) & 63u];
+    if (e.valid && std::memcmp(&e.key, &key, sizeof(key)) == 0) { *map = e.map; return true; }
+    cuuint64_t gd[3], gs[2];
+    cuuint32_t bx[3], es[3] = {1, 1, 1};
+    for (uint32_t i = 0; i < rank; ++i) { gd[i] = dims[i]; bx[i] = box[i]; }
+    for (uint32_t i = 0; i + 1 < rank; ++i) gs[i] = strides[i];
+    if (g_encode(map, dt, rank, const_cast<void*>(base), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                 promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    e.key = key; e.map = *map; e.valid = true;
+    return true;
+}
+
 static bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t elem, const void* base, uint64_t inner,
                       uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
-                      CUtensorMapSwizzle swz) {
-    const cuuint64_t dims[2] = {inner, outer};
-    const cuuint64_t strides[1] = {row_stride_bytes};
-    const cuuint32_t box[2] = {box_inner, box_outer};
-    const cuuint32_t estr[2] = {1, 1};
+                      CUtensorMapSwizzle swz, CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B) {
     (void)elem;
-    return g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                            swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const uint64_t dims[2] = {inner, outer}, strides[1] = {row_stride_bytes};
+    const uint32_t box[2] = {box_inner, box_outer};
+    return encode_tiled(map, dt, 2, base, dims, strides, box, swz, promo);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -145,13 +182,10 @@ static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool
                        CU_TENSOR_MAP_SWIZZLE_128B))
             return ATLAS_B200_ERR_DIMS;
         {
-            const cuuint64_t dims[3] = {p.k_in, p.max_rank, p.seq_slot ? n_slots : 1u};
-            const cuuint64_t strides[2] = {uint64_t(p.k_in) * 2, uint64_t(a_stride)};
-            const cuuint32_t box[3] = {SHT_KSTAGE, p.max_rank, 1};
-            const cuuint32_t estr[3] = {1, 1, 1};
-            if (g_encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(a_base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            const uint64_t dims[3] = {p.k_in, p.max_rank, p.seq_slot ? n_slots : 1u};
+            const uint64_t strides[2] = {uint64_t(p.k_in) * 2, uint64_t(a_stride)};
+            const uint32_t box[3] = {SHT_KSTAGE, p.max_rank, 1};
+            if (!encode_tiled(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a_base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
                 return ATLAS_B200_ERR_DIMS;
         }
         p.a_pool_base = nullptr;      // host-side fields: not part of what the kernel reads
@@ -194,9 +228,16 @@ static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool
 static int launch_expand(const ExpandParams& p, cudaStream_t st) {
     if (p.M == 0 || p.n_out == 0) return ATLAS_B200_OK;
     if (p.max_rank > EXPAND_MAX_RANK) return ATLAS_B200_ERR_LIMIT;
-    dim3 grid((p.n_out + EXPAND_OUTS - 1) / EXPAND_OUTS, (p.M + EXPAND_ROWS - 1) / EXPAND_ROWS);
+    // rows per CTA: 32 for large batches (a CTA re-uses its B rows out of L1 while neighbouring rows share an adapter),
+    // fewer while the grid would otherwise leave SMs without a CTA (a decode batch)
+    ExpandParams q = p;
+    const uint32_t col_blocks = (p.n_out + EXPAND_OUTS - 1) / EXPAND_OUTS;
+    uint32_t rpc = EXPAND_ROWS;
+    while (rpc > 1 && col_blocks * ((p.M + rpc - 1) / rpc) < 2u * uint32_t(rt_sm_count())) rpc >>= 1;
+    q.rows_per_cta = rpc;
+    dim3 grid(col_blocks, (p.M + rpc - 1) / rpc);
     if (grid.y > 65535) return ATLAS_B200_ERR_LIMIT;
-    lora_expand_fold_kernel<<<grid, EXPAND_OUTS, 0, st>>>(p);
+    lora_expand_fold_kernel<<<grid, EXPAND_OUTS, 0, st>>>(q);
     return launch_status();
 }
 
@@ -335,13 +376,10 @@ static int encode_tc_maps(const atlas_b200_linear_desc& d, bool a4, uint32_t xro
 
     // B side of the adapter pool as one 3-D tensor [max_loras][n][max_rank]: box = one granule of one slot
     if (b_pool_is_strided(d)) {
-        const cuuint64_t dims[3] = {d.max_rank, d.n, d.max_loras};
-        const cuuint64_t strides[2] = {uint64_t(d.max_rank) * 2, uint64_t(d.b_slot_stride)};
-        const cuuint32_t box[3] = {16, tc::FT, 1};
-        const cuuint32_t estr[3] = {1, 1, 1};
-        if (g_encode(&m.b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(d.b_pool_base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        const uint64_t dims[3] = {d.max_rank, d.n, d.max_loras};
+        const uint64_t strides[2] = {uint64_t(d.max_rank) * 2, uint64_t(d.b_slot_stride)};
+        const uint32_t box[3] = {16, tc::FT, 1};
+        if (!encode_tiled(&m.b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d.b_pool_base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_32B))
             return ATLAS_B200_ERR_DIMS;
     } else {
         m.b = m.s;   // never dereferenced

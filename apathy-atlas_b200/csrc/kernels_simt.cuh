@@ -60,12 +60,22 @@ __device__ __forceinline__ uint32_t e4m3_encode_sw(float v) {
     return (sign << 7) | (uint32_t(e) << 3) | man;
 }
 
+// E2M1 code of v with the reference's bins (|v| <= .25 -> 0, <= .75 -> .5, <= 1.25 -> 1, <= 1.75 -> 1.5, <= 2.5 -> 2,
+// <= 3.5 -> 3, <= 5 -> 4, else 6: ties go to the smaller magnitude, kernels/gb10/common/quantize_bf16_to_nvfp4.cu:109-124).
+// From 1 upward E2M1 is "one mantissa bit": adding just under half an ulp of that bit to the FP32 pattern and truncating
+// rounds half DOWN, which is exactly the `<=` of the bins (and carries into the exponent at 1.75 and 3.5); the code is
+// then twice the unbiased exponent plus the mantissa bit plus 2, clamped to 6.0's code.  Below 1 the two bins are compared
+// directly.  Same results as the chain of compares, in half the instructions (the quantiser is bound by instruction issue).
 __device__ __forceinline__ uint32_t e2m1_quantize(float v) {
-    const float a = fabsf(v);
-    const uint32_t sign = v < 0.0f ? 8u : 0u;
-    uint32_t idx = a <= 0.25f ? 0 : a <= 0.75f ? 1 : a <= 1.25f ? 2 : a <= 1.75f ? 3
-                 : a <= 2.5f ? 4 : a <= 3.5f ? 5 : a <= 5.0f ? 6 : 7;
-    return sign | idx;
+    const uint32_t bits = __float_as_uint(v);
+    const uint32_t mag = bits & 0x7FFFFFFFu;
+    const float a = __uint_as_float(mag);
+    // (mag + 0x1FFFFF) >> 22 = (biased exponent << 1) | mantissa bit, after rounding half down
+    int32_t code = int32_t((mag + 0x1FFFFFu) >> 22) - (127 * 2 - 2);
+    code = min(max(code, 2), 7);
+    uint32_t idx = a <= 0.75f ? (a <= 0.25f ? 0u : 1u) : uint32_t(code);
+    if (mag > 0x7F800000u) idx = 7u;                 // NaN compares false everywhere in the chain of bins: the last one
+    return (v < 0.0f ? 8u : 0u) | idx;
 }
 
 // `in_row_stride` (elements) lets the rows of `in` be spaced wider than K (activations); the outputs
@@ -330,6 +340,7 @@ struct ExpandParams {
     uint16_t* out;                  // [M, out_row_stride]
     uint16_t* delta_out;            // nullable, [M, n_out]
     uint32_t M, n_out, max_rank, out_row_stride, max_loras;
+    uint32_t rows_per_cta;          // 1..EXPAND_ROWS: fewer rows per CTA for small batches, so that the grid still fills the GPU
 };
 
 __global__ void __launch_bounds__(EXPAND_OUTS)
@@ -338,8 +349,9 @@ lora_expand_fold_kernel(const ExpandParams p) {
     __shared__ int32_t slot_s[EXPAND_ROWS];
     const uint32_t tid = threadIdx.x;
     const uint32_t o = blockIdx.x * EXPAND_OUTS + tid;
-    const uint32_t m0 = blockIdx.y * EXPAND_ROWS;
-    const uint32_t nrows = min(uint32_t(EXPAND_ROWS), p.M - m0);
+    const uint32_t rpc = p.rows_per_cta ? min(p.rows_per_cta, uint32_t(EXPAND_ROWS)) : uint32_t(EXPAND_ROWS);
+    const uint32_t m0 = blockIdx.y * rpc;
+    const uint32_t nrows = min(rpc, p.M - m0);
 
     if (tid < EXPAND_ROWS) {
         int32_t s = -1;

@@ -54,11 +54,12 @@ DEFAULT_WORKLOAD = "config3-layer"
 
 
 def peaks():
+    """(HBM GB/s, dense BF16 TFLOP/s of a kernel timed alone, the same inside a long step, "measured" | "fallback")."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
 
 
 def algorithmic_work(case):
@@ -84,12 +85,12 @@ def total_work(cases):
 class HostWork:
     """The workload on the host: its projections (synth.Case each), their shared inputs and seq_slot."""
 
-    def __init__(self, name):
+    def __init__(self, name, only=None):
         from atlas_b200 import synth
         spec = WORKLOADS[name]
         self.name, self.kind, self.fused_out = name, spec["kind"], bool(spec.get("fused_out"))
         if self.kind == "layer":
-            self.layer = synth.layer_config(spec["idx"])
+            self.layer = synth.layer_config(spec["idx"], **({"modules": tuple(only)} if only else {}))
             self.projections, self.inputs, self.seq_slot = self.layer.projections, self.layer.inputs, self.layer.seq_slot
         else:
             case = synth.baseline_config(spec["idx"])
@@ -245,6 +246,54 @@ class DevWork:
         return d
 
 
+def run_lora_bgmv(args, torch, ab, work, dw, outs, out_stride, flush):
+    """The routed LoRA op alone: out[i] += scale_s B_s (A_s x[i]) in place, reference rounding (two launches per projection)."""
+    M = work.M
+    for o in outs:
+        o.zero_()
+    routes, xs = [], []
+    for i, c in enumerate(work.projections):
+        if work.kind == "layer":
+            routes.append(dw.dl.proj[i]["route"]); xs.append(dw.dl.proj[i]["x"])
+        else:
+            routes.append(dw.ds.pool.route()); xs.append(dw.ds.x)
+    xa = [torch.zeros((M, c.max_rank), dtype=torch.int16, device=outs[0].device) for c in work.projections]
+    stream = torch.cuda.current_stream()
+
+    def step():
+        for i, c in enumerate(work.projections):
+            ab.apply_lora_bgmv(routes[i], xs[i], outs[i], dw.seq_slot, M, c.K, out_stride or c.N, xa[i], stream)
+    for _ in range(args.warmup):
+        flush.fill_(1)
+        step()
+    torch.cuda.synchronize()
+    if ab.device_status() != 0:
+        raise RuntimeError("device status word set after warm-up")
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in ev:
+        flush.fill_(1)
+        a.record(stream)
+        step()
+        b.record(stream)
+    torch.cuda.synchronize()
+    ms = float(np.mean([a.elapsed_time(b) for a, b in ev]))
+    hbm_gbs, _, _, peak_kind = peaks()
+    # bytes of the op: x, A and B of the adapters hit at their true rank, the routed rows of out read and written, seq_slot, xa
+    byts = 0.0
+    for c in work.projections:
+        w = algorithmic_work(c)
+        routed = int((np.asarray(c.seq_slot) >= 0).sum())
+        byts += w["x"] + w["a"] + w["b"] + 2 * routed * c.N * 2 + w["slot"] + 2 * routed * c.max_rank * 2
+    line = {"metric": "routed LoRA op (apply_lora_bgmv) tokens/s", "op": "lora_bgmv", "value": M / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic", "config": work.config(args, 1),
+            "roofline": {"bound": "hbm", "achieved": byts / (ms * 1e-3) / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                         "frac": byts / (ms * 1e-3) / 1e9 / hbm_gbs, "peak_kind": f"{peak_kind} HBM copy", "algorithmic_bytes": byts,
+                         "kernel": "lora_shrink_* + lora_expand_fold_kernel (whole op)"},
+            "gpu_launches": args.steps * 2 * len(work.projections)}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -258,6 +307,10 @@ def main():
                     help="N > 1: fused = the kernel's epilogue stores into every rank's buffer; nccl = all-gather after it")
     ap.add_argument("--activations", default="bf16", choices=["bf16", "fp4"],
                     help="bf16: the layer as specified (exact activations); fp4: the opt-in W4A4 mode as the timed step")
+    ap.add_argument("--op", default="fused", choices=["fused", "lora_bgmv"],
+                    help="fused: the fused layer (the benchmark); lora_bgmv: the routed LoRA op alone (shrink + expand/fold in place, "
+                         "the reference's apply_lora_bgmv) on the workload's projections, 1 GPU")
+    ap.add_argument("--only", default="", help="layer workloads: run these projections only, e.g. --only gate or --only q,k,v (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end loops (profiling runs)")
     ap.add_argument("--no-other-mode", action="store_true", help="skip the secondary activation-mode timing (profiling runs)")
     args = ap.parse_args()
@@ -267,7 +320,7 @@ def main():
     if args.warmup is None:
         args.warmup = 1 if reference else 5
 
-    work = HostWork(args.workload)
+    work = HostWork(args.workload, only=[m for m in args.only.split(",") if m] or None)
     if reference:
         run_reference_arm(args, work)
         return
@@ -340,6 +393,10 @@ def main():
              if tp > 1 else None)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > L2 (126 MB)
     mode = ab.FLAG_ACT_FP4 if args.activations == "fp4" else 0
+
+    if args.op == "lora_bgmv":
+        run_lora_bgmv(args, torch, ab, work, dw, y_loc, loc_stride, flush)
+        return
 
     def build_descs(flags, sym=None, outs=None, x_of=None, seq_slot=None):
         outs = outs or y_loc
@@ -484,6 +541,8 @@ def main():
     barrier()
     main_ms = float(np.mean([a.elapsed_time(b) for a, b in ev2]))
     dom_shape = ab.last_launch_shape()
+    dom_kernel = ("nvfp4_lora_linear_tc_persistent_kernel" if dom_shape.get("persistent_tiles_per_pass") else
+                  ("nvfp4_lora_linear_tc_kernel" if work.nvfp4 else "dense_bf16_linear_tc_kernel"))
 
     # ---- the same step in the other activation mode (no collective), a secondary figure ----
     other_ms = float("nan")
@@ -589,11 +648,29 @@ def main():
                             + ("; shrink sharded by tokens, its tiles stored into every rank's scratch + one device barrier" if sharded_shrink else "")
                             if fused else "NCCL all-gather per projection")
     if rank == 0:
-        hbm_gbs, peak_kind = peaks()
+        hbm_gbs, bf16_burst, bf16_sustained, peak_kind = peaks()
         work_all = total_work(work.projections)
         dom_work = works_local[dom]
-        achieved = dom_work["main_kernel"] / (main_ms * 1e-3) / 1e9
+        # What bounds the dominant kernel: exact-BF16 activations run at the BF16 tensor rate, so a prefill tile is tensor-bound
+        # against the measured BF16 GEMM peak of a kernel timed alone; a decode batch streams weights and is HBM-bound.  With FP4
+        # activations the tensor peak is the nominal NVFP4 figure (no measured one on this pool).
+        tensor_peak = FP4_PEAK_TFLOPS if mode else bf16_burst
+        t_hbm = dom_work["main_kernel"] / (hbm_gbs * 1e9)
+        t_tensor = dom_work["flops"] / (tensor_peak * 1e12)
+        traffic = NCU_TRAFFIC_BYTES.get((args.workload if not args.only else f"{args.workload}:{args.only}", args.activations)) if tp == 1 else None
+        if t_tensor > t_hbm:
+            achieved = dom_work["flops"] / (main_ms * 1e-3) / 1e12
+            roof = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
+                    "peak_kind": ("nominal dense NVFP4" if mode else f"{peak_kind} dense BF16 GEMM, kernel timed alone"),
+                    "algorithmic_flops": dom_work["flops"], "hbm_gbs": dom_work["main_kernel"] / (main_ms * 1e-3) / 1e9}
+        else:
+            achieved = dom_work["main_kernel"] / (main_ms * 1e-3) / 1e9
+            roof = {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
+                    "peak_kind": f"{peak_kind} HBM copy", "tflops": dom_work["flops"] / (main_ms * 1e-3) / 1e12}
+        roof.update({"traffic": traffic, "kernel": f"{dom_kernel}, projection '{work.projections[dom].name.split('/')[-1]}' (per rank)",
+                     "kernel_ms": main_ms, "algorithmic_bytes": dom_work["main_kernel"], "launch_shape": dom_shape})
         t_roof = max(work_all["flops"] / (FP4_PEAK_TFLOPS * 1e12), work_all["total"] / (hbm_gbs * 1e9))
+        t_roof_bf16 = max(work_all["flops"] / (bf16_sustained * 1e12), work_all["total"] / (hbm_gbs * 1e9))
         per_step_launches = sum((1 if c.seq_slot is not None else 0) + 1 + (1 if mode else 0) for c in work.projections) + (1 if fused else 0)
         line = {
             "metric": METRIC, "value": M / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": tp,
@@ -601,15 +678,13 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": work.config(args, tp),
             "tflops": work_all["flops"] / (step_ms * 1e-3) / 1e12,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
-                         "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.activations)) if tp == 1 else None,
-                         "peak_kind": peak_kind,
-                         "kernel": f"nvfp4_lora_linear_tc_kernel, projection '{work.projections[dom].name.split('/')[-1]}' (per rank)",
-                         "kernel_ms": main_ms, "algorithmic_bytes": dom_work["main_kernel"],
-                         "kernel_tflops": dom_work["flops"] / (main_ms * 1e-3) / 1e12, "launch_shape": dom_shape},
+            "roofline": roof,
             "layer_roofline": {"time_us": t_roof * 1e6, "frac": t_roof / (step_ms * 1e-3),
                                "rule": "max(flops / 9 PFLOP/s nominal NVFP4, algorithmic bytes / measured HBM GB/s), single GPU",
-                               "algorithmic_bytes": work_all["total"], "flops": work_all["flops"]},
+                               "algorithmic_bytes": work_all["total"], "flops": work_all["flops"],
+                               "exact_activation_ceiling": {"time_us": t_roof_bf16 * 1e6, "frac": t_roof_bf16 / (step_ms * 1e-3),
+                                                            "rule": "the same with flops / measured sustained dense BF16 TFLOP/s: what exact BF16 "
+                                                                    "activations can reach at most, since they run at the BF16 tensor rate"}},
             "projections": [{"name": c.name.split("/")[-1], "ms": proj_ms[i],
                              "tflops": works_local[i]["flops"] / (proj_ms[i] * 1e-3) / 1e12} for i, c in enumerate(work.projections)],
             "e2e": {"value": M / (e2e_ms * 1e-3) if e2e_ms == e2e_ms else None, "unit": "tokens/s",

@@ -248,7 +248,10 @@ ATLAS_B200_API int atlas_b200_lora_shrink_tiles(const atlas_b200_linear_desc* de
  *   - All calls on a device share the one array and it keeps the previous call's contents.  The
  *     kernels overwrite every element they later read, so nothing is cleared between calls; but two
  *     calls whose kernels overlap on the GPU (different streams, or concurrent graph branches) race
- *     on it.  Serialise such calls, or use atlas_b200_nvfp4_lora_linear with a scratch per stream. */
+ *     on it.  Serialise such calls, or use atlas_b200_nvfp4_lora_linear with a scratch per stream.
+ *   - ATLAS_B200_FLAG_REUSE_SHRINK through this entry point reuses whatever the array holds: it is only meaningful when
+ *     no other call (of any descriptor, on any stream of the device) has gone through this entry point since the call
+ *     whose shrink result is to be reused. */
 #define ATLAS_B200_STATIC_SCRATCH_ELEMS (512u * 1024u)
 ATLAS_B200_API int atlas_b200_nvfp4_lora_linear_noalloc(const atlas_b200_linear_desc* desc, void* stream);
 

@@ -51,6 +51,28 @@ def test_noalloc_entry_matches_regular_entry_twice(cuda, atlas, oracle):
     assert atlas.device_status() == 0
 
 
+def test_noalloc_entry_at_the_limit_and_on_the_cuda_core_path(cuda, atlas, oracle):
+    """Both consumers of the built-in array: the tensor-core path with m * max_rank exactly at its capacity, and the
+    CUDA-core path (K not a multiple of 256), each against the regular entry point."""
+    torch = cuda
+    from atlas_b200 import synth
+    m_full = atlas.STATIC_SCRATCH_ELEMS // 64                          # 8192 rows x rank 64 = every element of the array
+    cases = [
+        synth.make_case("na_full", M=m_full, K=256, N=128, ranks=[64, 32], max_rank=64, max_loras=2, ids="segments", segments=9,
+                        none_frac=0.1, scale2=0.02, b_std=0.1, seed=13),
+        synth.make_case("na_simt", M=40, K=272, N=136, ranks=[8, 16], max_rank=16, max_loras=3, none_frac=0.2, scale2=0.02,
+                        b_std=0.1, seed=14),
+    ]
+    for case, want_variant in zip(cases, (atlas.VARIANT_TCGEN05, atlas.VARIANT_SIMT)):
+        dc = DeviceCase(torch, atlas, case)
+        want_bits, variant = dc.run()
+        assert variant == want_variant
+        got_bits, variant = _run_noalloc(torch, atlas, dc, fill=0x7FC0)
+        assert variant == want_variant
+        assert np.array_equal(got_bits, want_bits)
+    assert atlas.device_status() == 0
+
+
 def test_noalloc_entry_rejects_oversized_scratch(cuda, atlas):
     torch = cuda
     d = atlas.LinearDesc()
