@@ -42,7 +42,15 @@ METRIC = "NVFP4+multi-LoRA linear tokens/s"
 FP4_PEAK_TFLOPS = 9000.0          # B200 dense NVFP4, nominal (no measured figure on this pool)
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel instance, from the ncu captures
 # summarised under profiles/ (per workload and activation mode; absent = no capture)
-NCU_TRAFFIC_BYTES = {("config1", "bf16"): 72.9e6}
+NCU_TRAFFIC_BYTES = {
+    # (workload, dominant projection, activations)
+    ("config3-layer", "gate", "bf16"): 432.6e6,      # persistent kernel <192, 2, A16>
+    ("config3-layer", "gate", "fp4"): 336.8e6,       # persistent kernel <256, 1, A4>
+    ("config4-mlp", "gate", "bf16"): 409.1e6,        # persistent kernel <256, 1, A16>
+    ("config1", "config1", "bf16"): 73.1e6,          # one-tile kernel <256>
+    ("config2", "config2", "bf16"): 66.1e6,          # one-tile kernel <64>
+    ("config0", "config0", "bf16"): 33.7e6,          # dense BF16 kernel <16>
+}
 WORKLOADS = {
     "config3-layer": dict(kind="layer", idx=3),
     "config4-mlp": dict(kind="layer", idx=4),
@@ -657,7 +665,7 @@ def main():
         tensor_peak = FP4_PEAK_TFLOPS if mode else bf16_burst
         t_hbm = dom_work["main_kernel"] / (hbm_gbs * 1e9)
         t_tensor = dom_work["flops"] / (tensor_peak * 1e12)
-        traffic = NCU_TRAFFIC_BYTES.get((args.workload if not args.only else f"{args.workload}:{args.only}", args.activations)) if tp == 1 else None
+        traffic = NCU_TRAFFIC_BYTES.get((args.workload, work.projections[dom].name.split("/")[-1], args.activations)) if tp == 1 else None
         if t_tensor > t_hbm:
             achieved = dom_work["flops"] / (main_ms * 1e-3) / 1e12
             roof = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
