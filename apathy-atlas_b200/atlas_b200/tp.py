@@ -33,6 +33,16 @@ def shard_case(case: synth.Case, tp: int, rank: int) -> synth.Case:
     return c
 
 
+def token_shard(M: int, tp: int, rank: int, align: int = 64):
+    """(row_begin, row_count) of rank `rank`'s share of the M tokens for the token-sharded shrink: equal shares rounded
+    up to `align` rows (the shrink kernel's rows per CTA), the last ranks taking what is left (possibly nothing)."""
+    if tp < 1 or not 0 <= rank < tp:
+        raise ValueError(f"rank {rank} of {tp}")
+    per = (-(-M // tp) + align - 1) // align * align
+    begin = min(rank * per, M)
+    return begin, max(0, min(per, M - begin))
+
+
 def gathered_to_row_major(y_all: np.ndarray) -> np.ndarray:
     """[tp, M, N/tp] (all-gather order) -> [M, N]."""
     tp, M, n_loc = y_all.shape

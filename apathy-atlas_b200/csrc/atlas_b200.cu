@@ -154,6 +154,7 @@ static bool shrink_takes_mma_path(const ShrinkParams& p) {
 static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool release_dependents = false,
                          bool dependent_leaves_sms_free = false) {
     p.release_dependents = release_dependents ? 1u : 0u;
+    p.profile = nullptr;
     if (p.M == 0 || p.max_rank == 0) return ATLAS_B200_OK;
     // Same shared-memory carve-out as the tcgen05 kernel, so that kernel's CTAs can become resident
     // next to this grid's instead of waiting for the SMs to drain and be reconfigured.
@@ -191,6 +192,7 @@ static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool
         p.a_pool_base = nullptr;      // host-side fields: not part of what the kernel reads
         if (p.m_begin % SHT_ROWS != 0 || p.m_begin >= p.M) return ATLAS_B200_ERR_DIMS;
         const uint32_t rows = p.m_count ? std::min(p.m_count, p.M - p.m_begin) : p.M - p.m_begin;
+        p.profile = (g_profile_buf && size_t((rows + SHT_ROWS - 1) / SHT_ROWS) * 8 <= g_profile_words) ? g_profile_buf : nullptr;
         lora_shrink_tc_kernel<<<(rows + SHT_ROWS - 1) / SHT_ROWS, SHT_THREADS, SHT_SMEM_BYTES, st>>>(map_x, map_a, p);
         return launch_status();
     }

@@ -64,6 +64,9 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t m0 = p.m_begin + blockIdx.x * SHT_ROWS;      // (m_begin: a multiple of SHT_ROWS)
     if (m0 >= p.M) return;
+    unsigned long long* prof = p.profile ? p.profile + size_t(blockIdx.x) * 8 : nullptr;
+    const long long t_start = clock64();
+    if (prof && tid == 0) prof[7] = tc::global_timer_ns();
     const uint32_t chunk = p.chunk ? p.chunk : 256u;     // token tile of the fused kernel (tile output only)
     const uint32_t tile_lo = m0 / chunk;                 // first token tile this CTA's rows lie in
     const uint32_t rank_pad = (p.max_rank + 15u) & ~15u; // accumulator columns per adapter
@@ -133,6 +136,8 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     __syncthreads();
     tc::tcgen05_fence_after();
     const uint32_t tmem_acc = tmem_base_s;
+    const long long t_setup = clock64();
+    long long t_wait = 0;
 
     // position of slot s among the granules of token tile tl: granules of all present slots below it
     auto granules_ahead = [&](uint32_t tl, uint32_t s) -> uint32_t {
@@ -194,7 +199,9 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             // ================================ TMA producer ================================
             for (uint32_t ks = 0; ok && ks < n_ks; ++ks) {
                 const uint32_t s = ks % n_stages;
+                const long long w0 = prof ? clock64() : 0;
                 ok = tc::mbar_wait(BAR_EMPTY + 8 * s, (empty_par >> s) & 1u, abort_flag, STATUS_WAIT_EXPIRED_PRODUCER, 20);
+                if (prof) t_wait += clock64() - w0;
                 if (!ok) break;
                 empty_par ^= 1u << s;
                 const uint32_t st = ring + s * stage_bytes;
@@ -210,7 +217,9 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             const uint32_t idesc = tc::make_idesc_bf16(rank_pad, 128u);
             for (uint32_t ks = 0; ok && ks < n_ks; ++ks) {
                 const uint32_t s = ks % n_stages;
+                const long long w0 = prof ? clock64() : 0;
                 ok = tc::mbar_wait(BAR_FULL + 8 * s, (full_par >> s) & 1u, abort_flag, STATUS_WAIT_EXPIRED_MMA, 20);
+                if (prof) t_wait += clock64() - w0;
                 if (!ok) break;
                 full_par ^= 1u << s;
                 tc::tcgen05_fence_after();
@@ -238,6 +247,7 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 ok = tc::mbar_wait(BAR_ACC, acc_phase, abort_flag, STATUS_WAIT_EXPIRED_EPILOGUE, 200) && ok;
                 tc::tcgen05_fence_after();
             }
+            if (prof && tid == 128 && pass == 0) { prof[1] = clock64() - t_setup; prof[6] = n_cs; }
             if (ok && has_rows) {
                 for (uint32_t ci = 0; ci < n_cs; ++ci) {
                     const uint32_t sl = cslot[ci];
@@ -296,6 +306,10 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             }
             tc::tcgen05_fence_before();
         }
+        if (prof && pass == 0) {
+            if (tid == 0) prof[3] = t_wait;
+            if (tid == 128) prof[4] = t_wait;
+        }
         if (n_cs > 0) acc_phase ^= 1u;
         __syncthreads();                                 // every MMA of the pass has completed (the epilogue waited for them): the ring is free
         if (*abort_flag) break;                          // (uniform: read after the barrier)
@@ -305,6 +319,12 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     // ---- teardown ----
     tc::tcgen05_fence_before();
     __syncthreads();
+    if (prof && tid == 128) {
+        const long long t_end = clock64();
+        prof[0] = t_setup - t_start;
+        prof[5] = t_end - t_start;
+        prof[2] = (t_end - t_setup) - (long long)prof[1];
+    }
     if (warp == 4) {
         tc::tcgen05_fence_after();
         tc::tmem_dealloc(tmem_acc, 512);

@@ -436,9 +436,8 @@ def main():
             collective_note = f"scratch could not be mapped to the peers ({type(e).__name__}: {e}); every rank runs the whole shrink"
     descs = [build_descs(mode, s) for s in sym_sets] if fused else [build_descs(mode)]
     descs_reuse = [build_descs(mode | ab.FLAG_REUSE_SHRINK, s) for s in sym_sets] if fused else None
-    rows_per_rank = (-(-M // tp) + 63) // 64 * 64
-    row_begin = rank * rows_per_rank
-    row_count = max(0, min(rows_per_rank, M - row_begin))
+    from atlas_b200 import tp as tpmod
+    row_begin, row_count = tpmod.token_shard(M, tp, rank)
     if ws_sym is not None:
         try:
             for i in range(n_proj):

@@ -43,7 +43,7 @@ def test_config4_wide_mlp_many_adapters(cuda, atlas, oracle):
     dc = DeviceCase(cuda, atlas, case)
     y, variant = dc.run(lora_ws=True)
     assert variant == atlas.VARIANT_TCGEN05
-    rows, cols = _sample(case, 24, 64, 4)
+    rows, cols = _sample(case, 64, 64, 4)
     assert_close(oracle, y[np.ix_(rows, cols)], ideal(oracle, case, rows=rows, cols=cols), "config4 sample")
     assert np.isfinite(oracle.bf16_to_f32(y)).all()                    # every element of the pre-filled buffer was written
     y_build, _ = dc.run()                                               # tiles built in the kernel from lora_t: same bits
@@ -54,17 +54,19 @@ def test_config4_wide_mlp_many_adapters(cuda, atlas, oracle):
     assert atlas.device_status() == 0
 
 
-def test_config3_prefill_segments(cuda, atlas, oracle):
+@pytest.mark.parametrize("fp4", [False, True])
+def test_config3_prefill_segments(cuda, atlas, oracle, fp4):
     """8192 tokens in 32 contiguous segments, 8 adapters of rank 64, K = 4096, N = 14336."""
     from atlas_b200 import synth
     case = synth.baseline_config(3)
     dc = DeviceCase(cuda, atlas, case)
-    y, variant = dc.run(lora_ws=True)
+    y, variant = dc.run(lora_ws=True, flags=atlas.FLAG_ACT_FP4 if fp4 else 0)
     assert variant == atlas.VARIANT_TCGEN05
     # rows on both sides of every segment boundary, plus a random sample
     cuts = np.flatnonzero(np.diff(case.seq_slot) != 0)
-    rows = np.unique(np.concatenate([cuts[:12], cuts[:12] + 1, _sample(case, 8, 1, 3)[0]])).astype(np.uint32)
-    cols = _sample(case, 1, 48, 5)[1]
-    assert_close(oracle, y[np.ix_(rows, cols)], ideal(oracle, case, rows=rows, cols=cols), "config3 sample")
+    rows = np.unique(np.concatenate([cuts[:12], cuts[:12] + 1, _sample(case, 48, 1, 3)[0]])).astype(np.uint32)
+    cols = _sample(case, 1, 64, 5)[1]
+    assert rows.size * cols.size >= 4096
+    assert_close(oracle, y[np.ix_(rows, cols)], ideal(oracle, case, rows=rows, cols=cols, act_fp4=fp4), "config3 sample")
     assert np.isfinite(oracle.bf16_to_f32(y)).all()
     assert atlas.device_status() == 0

@@ -76,3 +76,65 @@ def test_shard_case_rejects_indivisible_n():
     y = np.arange(2 * 3 * 4, dtype=np.uint16).reshape(2, 3, 4)
     rm = tp.gathered_to_row_major(y)
     assert rm.shape == (3, 8) and list(rm[1]) == [4, 5, 6, 7, 16, 17, 18, 19]
+
+
+def _shrink_worker(rank, world, port, out_path):
+    """Token-sharded shrink: every rank computes t = A_s x for its own rows only and the rows are all-gathered; the
+    result must equal the unsharded shrink bit for bit (a row's shrink does not depend on the other rows)."""
+    for p in (ROOT, os.path.join(ROOT, "apathy-atlas_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch
+    import torch.distributed as dist
+    from atlas_b200 import synth, tp
+    from oracle import oracle_ctypes as oc
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    M = 200                                                   # not a multiple of world * 64: the last rank gets a short share
+    case = synth.make_case("tok", M=M, K=128, N=64, ranks=[8, 16, 4], max_rank=16, none_frac=0.2, scale2=0.02, seed=6)
+    pool = oc.HostPool(case.K, case.N, case.max_rank, case.max_loras)
+    for s, ad in enumerate(case.adapters):
+        if ad is not None:
+            pool.pack(s, ad.a, ad.b, ad.scale)
+    begin, count = tp.token_shard(M, world, rank)
+    per = tp.token_shard(M, world, 0)[1]
+    mine = np.zeros((per, case.max_rank), dtype=np.uint16)
+    if count:
+        scratch = np.zeros((count, case.N), dtype=np.uint16)
+        mine[:count] = oc.lora_bgmv_staged(np.ascontiguousarray(case.x[begin:begin + count]), case.seq_slot[begin:begin + count],
+                                           pool, scratch, count)
+    t_all = torch.empty((world, per, case.max_rank * 2), dtype=torch.uint8)
+    dist.all_gather_into_tensor(t_all.view(world * per, case.max_rank * 2), torch.from_numpy(mine.view(np.uint8).copy()))
+    if rank == 0:
+        scratch = np.zeros((M, case.N), dtype=np.uint16)
+        want = oc.lora_bgmv_staged(case.x, case.seq_slot, pool, scratch, M)
+        got = t_all.numpy().view(np.uint16).reshape(world * per, case.max_rank)[:M]
+        np.save(out_path, np.array([int(np.array_equal(got, want)), int((want != 0).sum())]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_token_sharded_shrink_reassembles(world, tmp_path):
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "res.npy")
+    mp.spawn(_shrink_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    res = np.load(out)
+    assert res[0] == 1 and res[1] > 0
+
+
+def test_token_shard_ranges_tile_the_batch():
+    sys.path.insert(0, os.path.join(ROOT, "apathy-atlas_b200"))
+    from atlas_b200 import tp
+    for M in (1, 63, 64, 65, 200, 8192, 8193):
+        for world in (1, 2, 3, 4, 8):
+            at = 0
+            for r in range(world):
+                b, c = tp.token_shard(M, world, r)
+                assert b % 64 == 0 or c == 0
+                assert b == min(at, M) and c >= 0
+                at = b + c
+            assert at == M
+    with pytest.raises(ValueError):
+        tp.token_shard(64, 2, 2)
