@@ -171,7 +171,7 @@ static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool
     if (mma_ok && p.M >= 1024 && !release_dependents && p.k_in % SHT_KSTAGE == 0 && p.max_rank % 16 == 0 && p.max_rank <= 256 &&
         n_slots <= 4096 && dst && dst->sm100 && g_encode && a_base && aligned(a_base, 16) && a_stride % 16 == 0 &&
         (!p.tile_out || (p.part_rows && p.chunk % p.part_rows == 0))) {
-        // a prefill batch: one CTA per 128 tokens and all ranks of all their adapters on the tcgen05 tensor cores,
+        // a prefill batch: one cluster per 128 tokens and all ranks of all their adapters on the tcgen05 tensor cores,
         // x read once (kernel_shrink_tc.cuh)
         if (!dst->shrink_tc_attr_set) {
             cudaError_t e = cudaFuncSetAttribute(lora_shrink_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SHT_SMEM_BYTES);
@@ -190,11 +190,27 @@ static int launch_shrink(ShrinkParams p, uint32_t n_slots, cudaStream_t st, bool
                 return ATLAS_B200_ERR_DIMS;
         }
         p.a_pool_base = nullptr;      // host-side fields: not part of what the kernel reads
-        if (p.m_begin % SHT_ROWS != 0 || p.m_begin >= p.M) return ATLAS_B200_ERR_DIMS;
+        if (p.m_begin % 64 != 0 || p.m_begin >= p.M) return ATLAS_B200_ERR_DIMS;
+        if (p.tile_out && p.chunk && p.chunk < uint32_t(SHT_ROWS)) return ATLAS_B200_ERR_DIMS;   // a cluster's rows lie in at most two token tiles
         const uint32_t rows = p.m_count ? std::min(p.m_count, p.M - p.m_begin) : p.M - p.m_begin;
-        p.profile = (g_profile_buf && size_t((rows + SHT_ROWS - 1) / SHT_ROWS) * 8 <= g_profile_words) ? g_profile_buf : nullptr;
-        lora_shrink_tc_kernel<<<(rows + SHT_ROWS - 1) / SHT_ROWS, SHT_THREADS, SHT_SMEM_BYTES, st>>>(map_x, map_a, p);
-        return launch_status();
+        // two CTAs per 128 rows, each contracting half of K: fixed by K alone, so that a row's result does not depend on
+        // how the batch is cut into launches
+        p.ksplit = (p.k_in / SHT_KSTAGE >= 2) ? 2u : 1u;
+        const uint32_t n_ctas = p.ksplit * ((rows + SHT_ROWS - 1) / SHT_ROWS);
+        p.profile = (g_profile_buf && size_t(n_ctas) * 16 <= g_profile_words) ? g_profile_buf : nullptr;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(n_ctas);
+        cfg.blockDim = dim3(SHT_THREADS);
+        cfg.dynamicSmemBytes = SHT_SMEM_BYTES;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = p.ksplit;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        return cuda_status(cudaLaunchKernelEx(&cfg, lora_shrink_tc_kernel, map_x, map_a, p));
     }
     if (p.m_begin || p.m_count || p.n_tile_dest > 1) return ATLAS_B200_ERR_DIMS;      // a row range / several destinations: that kernel only
     if (mma_ok) {

@@ -178,8 +178,8 @@ struct ShrinkParams {
     // host side only: the A side of the adapter pool as a strided array (0: not known), for the launcher's tensor map
     const void* a_pool_base;
     size_t a_slot_stride;
-    // optional diagnostics (tcgen05 shrink only): 8 u64 words per CTA — set-up, K loop, epilogue and total cycles, the
-    // producer's and the MMA thread's wait cycles, adapters in the first pass, start time (ns)
+    // optional diagnostics (tcgen05 shrink only): 16 u64 words per CTA — set-up, K loop, epilogue and total cycles, the
+    // producer's and the MMA thread's wait cycles, adapters in the first pass, start time (ns), issue cycles of both
     unsigned long long* profile;
 };
 
