@@ -26,6 +26,7 @@
 #include "kernel_shrink_mma.cuh"
 #include "kernel_shrink_tc.cuh"
 #include "kernels_mlp_glue.cuh"
+#include "kernel_push.cuh"
 
 namespace atlas {
 
@@ -61,6 +62,7 @@ struct DeviceState {
     int persist_clusters[kPersistKernels] = {};
     bool carveout_set = false;
     bool shrink_tc_attr_set = false;
+    bool push_attr_set = false;
     bool dense_attr_set[5] = {};      // token tiles 16, 32, 64, 128, 256 of the dense-BF16 kernel
 };
 static DeviceState g_dev[kMaxDevices];
@@ -1012,6 +1014,39 @@ float atlas_b200_nvfp4_scale2_from_absmax(float global_max) { return global_max 
 float atlas_b200_nvfp4_combined_global_scale(float stored_scale, int is_reciprocal) {
     if (!is_reciprocal) return stored_scale;
     return stored_scale != 0.0f ? 1.0f / stored_scale : 0.0f;
+}
+
+int atlas_b200_push_columns(const void* src, uint32_t src_row_stride, void* const* dest, uint32_t n_dest, uint32_t dst_row_stride,
+                            uint32_t m, uint32_t n_cols, void* stream) {
+    if (!src || (!dest && n_dest)) return ATLAS_B200_ERR_NULL;
+    if (n_dest > uint32_t(PUSH_MAX_DEST)) return ATLAS_B200_ERR_LIMIT;
+    if (m == 0 || n_cols == 0 || n_dest == 0) return ATLAS_B200_OK;
+    if (n_cols > src_row_stride || n_cols > dst_row_stride) return ATLAS_B200_ERR_DIMS;
+    if (n_cols % 8 || src_row_stride % 8 || dst_row_stride % 8 || !aligned(src, 16)) return ATLAS_B200_ERR_ALIGN;
+    PushParams p{};
+    p.src = static_cast<const uint4*>(src);
+    for (uint32_t d = 0; d < n_dest; ++d) {
+        if (!dest[d]) return ATLAS_B200_ERR_NULL;
+        if (!aligned(dest[d], 16)) return ATLAS_B200_ERR_ALIGN;
+        p.dst[d] = static_cast<uint4*>(dest[d]);
+    }
+    p.n_dest = n_dest;
+    p.m = m;
+    p.chunks_per_row = n_cols / 8;
+    p.src_row_chunks = src_row_stride / 8;
+    p.dst_row_chunks = dst_row_stride / 8;
+    const uint64_t total = uint64_t(m) * p.chunks_per_row;
+    const uint64_t want = (total + uint64_t(PUSH_THREADS) * 4 - 1) / (uint64_t(PUSH_THREADS) * 4);
+    const uint32_t grid = uint32_t(std::min<uint64_t>(std::max<uint64_t>(want, 1), uint64_t(rt_sm_count()) * 2));
+    // same shared-memory carve-out as the tcgen05 kernels: an SM must not have to drain and be reconfigured before it can
+    // take one of these CTAs next to theirs
+    DeviceState* dst_state = device_state();
+    if (dst_state && !dst_state->push_attr_set) {
+        cudaFuncSetAttribute(push_columns_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        dst_state->push_attr_set = true;
+    }
+    push_columns_kernel<<<grid, PUSH_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return launch_status();
 }
 
 int atlas_b200_silu_mul(const void* gate_bf16, const void* up_bf16, void* out_bf16, float gate_scale, float up_scale, float swiglu_limit,

@@ -13,10 +13,12 @@ q/k/v LoRA modules into column segments of one fused-QKV output) and the single 
 
 With N > 1 (launched by torch.distributed.run, one rank per GPU) every projection is split column-parallel over
 the ranks — W, its scales and every B_s by output rows; x, A_s and seq_slot replicated: strong scaling.  Every
-rank's kernel stores its output tiles straight into all ranks' gathered [M, N] buffers over NVLink (peer
-mappings from torch's symmetric memory), so the exchange overlaps the compute tile by tile and what remains of
-the collective is one device-side barrier per step; `--collective nccl` (or a box where the peer mapping cannot
-be made) runs the projections followed by one NCCL all-gather each instead.
+rank's gathered [M, N] buffers live in symmetric memory mapped into every process.  `--collective push` (default):
+a projection's kernels store into the rank's own buffer and a small copy kernel on a second stream sends those
+columns to the peers over NVLink while the next projection computes; `--collective fused`: the kernel's own store
+phase writes each tile into all ranks' buffers; either way what remains of the collective is one device-side
+barrier per step.  `--collective nccl` (or a box where the peer mapping cannot be made) runs the projections
+followed by one NCCL all-gather each instead.
 
 Rank 0 prints one JSON line.  `value` is device-timed (CUDA events on the launching stream, L2 flushed between
 steps, inputs resident in HBM); `e2e` runs the same calls with host buffers, with the H2D copies of the step's
@@ -311,8 +313,10 @@ def main():
     ap.add_argument("--impl", default="atlas_b200", choices=["atlas_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU sample (0: sized for a few seconds per pass)")
-    ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
-                    help="N > 1: fused = the kernel's epilogue stores into every rank's buffer; nccl = all-gather after it")
+    ap.add_argument("--collective", default="push", choices=["push", "fused", "nccl"],
+                    help="N > 1: push = each projection's columns copied to the peers by a small kernel on a second stream while "
+                         "the next projection computes; fused = the kernel's own store phase writes into every rank's buffer; "
+                         "nccl = all-gather after each projection")
     ap.add_argument("--activations", default="bf16", choices=["bf16", "fp4"],
                     help="bf16: the layer as specified (exact activations); fp4: the opt-in W4A4 mode as the timed step")
     ap.add_argument("--op", default="fused", choices=["fused", "lora_bgmv"],
@@ -374,7 +378,7 @@ def main():
     # a rank that has passed step i's barrier may start step i+1's stores while a slower rank still reads step i's
     # result, so consecutive steps must not write the same buffers.
     fused, sym_sets, collective_note = False, [], None
-    if tp > 1 and args.collective == "fused":
+    if tp > 1 and args.collective in ("fused", "push"):
         try:
             import torch.distributed._symmetric_memory as symm_mem
             if hasattr(symm_mem, "enable_symm_mem_for_group"):
@@ -397,6 +401,10 @@ def main():
         ok = torch.tensor([1 if fused else 0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         fused = bool(int(ok.item()))
+    # push: the kernels store into this rank's own gathered buffer only; a copy kernel on a second stream sends each
+    # projection's columns to the peers while the next projection computes
+    pushed = fused and args.collective == "push"
+    side = torch.cuda.Stream(device=dev) if pushed else None
     y_all = ([torch.empty((tp, M, dw.n_local[i]), dtype=torch.bfloat16, device=dev) for i in range(n_proj)]
              if tp > 1 else None)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > L2 (126 MB)
@@ -413,7 +421,7 @@ def main():
             xin = None if x_of is None else x_of[work.projections[i].meta["input"]]
             if sym is not None:
                 j = 0 if work.fused_out else i
-                place = dict(y_dest=sym["ptrs"][j], out_row_stride=(work.n_total if work.fused_out else work.projections[i].N),
+                place = dict(y_dest=(sym["ptrs"][j] if not pushed else [sym["ptrs"][j][rank]]), out_row_stride=(work.n_total if work.fused_out else work.projections[i].N),
                              y_col_offset=(int(full_cols0[i]) if work.fused_out else 0) + rank * dw.n_local[i])
                 ds.append(dw.desc(i, None, flags, x=xin, seq_slot=seq_slot, **place))
             else:
@@ -453,18 +461,63 @@ def main():
     stream = torch.cuda.current_stream()
     step_no = [0]
 
-    def step():
+    push_events = [[torch.cuda.Event() for _ in range(n_proj + 1)] for _ in range(2)] if pushed else None
+    shrink_streams = [torch.cuda.Stream(device=dev) for _ in range(n_proj)] if sharded_shrink else None
+    shrink_fork = torch.cuda.Event()
+    shrink_join = [torch.cuda.Event() for _ in range(n_proj)]
+
+    def push(k, i):
+        """Projection i's columns of this rank's gathered buffer (set k) into the same columns of every peer's."""
+        j = 0 if work.fused_out else i
+        n_row = work.n_total if work.fused_out else work.projections[i].N
+        col = (int(full_cols0[i]) if work.fused_out else 0) + rank * dw.n_local[i]
+        ptrs = sym_sets[k]["ptrs"][j]
+        ab.push_columns(ptrs[rank] + col * 2, n_row, [ptrs[r] + col * 2 for r in range(tp) if r != rank], n_row, M, dw.n_local[i], side)
+
+    def step(marks=None):
+        """One step.  `marks`: optional list that receives CUDA events recorded between the step's phases."""
+        def mark():
+            if marks is not None:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record(stream)
+                marks.append(e)
         k = step_no[0] % len(descs)
         step_no[0] += 1
         v = None
+        mark()
         if sharded_shrink:
+            # the projections' shrinks are independent and, with the tokens split over the ranks, each fills only a part
+            # of the GPU: one stream each, so that they run side by side
+            shrink_fork.record(stream)
             for i in range(n_proj):
                 if row_count:
-                    ab.lora_shrink_tiles(descs[k][i], row_begin, row_count, ws_sym["ptrs"][i], stream)
+                    shrink_streams[i].wait_event(shrink_fork)
+                    ab.lora_shrink_tiles(descs[k][i], row_begin, row_count, ws_sym["ptrs"][i], shrink_streams[i])
+                    shrink_join[i].record(shrink_streams[i])
+                    stream.wait_event(shrink_join[i])
+            mark()
             ws_sym["handles"][0].barrier(channel=1)          # every rank's tiles are in every rank's scratch
+            mark()
+        if pushed:
+            dd = descs_reuse[k] if sharded_shrink else descs[k]
+            for i in range(n_proj):
+                v = ab.nvfp4_lora_linear(dd[i], stream)
+                push_events[k][i].record(stream)
+                side.wait_event(push_events[k][i])
+                push(k, i)
+            mark()
+            push_events[k][n_proj].record(side)
+            stream.wait_event(push_events[k][n_proj])
+            mark()
+            sym_sets[k]["handles"][0].barrier(channel=0)     # every rank's columns have landed in every buffer
+            mark()
+            return v
+        if sharded_shrink:
             for i in range(n_proj):
                 v = ab.nvfp4_lora_linear(descs_reuse[k][i], stream)
+            mark()
             sym_sets[k]["handles"][0].barrier(channel=0)     # every rank's output tiles have landed in every buffer
+            mark()
             return v
         for i in range(n_proj):
             v = ab.nvfp4_lora_linear(descs[k][i], stream)
@@ -523,6 +576,23 @@ def main():
         b.record(stream)
     barrier()
     step_ms = float(np.mean([a.elapsed_time(b) for a, b in ev]))
+
+    # ---- the phases of a step at N > 1 (token-sharded shrink, its barrier, the projections, what is left of the exchange) ----
+    phase_ms = None
+    if tp > 1 and sharded_shrink:
+        rows_ = []
+        for _ in range(min(args.steps, 10)):
+            flush.fill_(1)
+            mk = []
+            step(mk)
+            rows_.append(mk)
+        barrier()
+        names_ = (["shrink (this rank's tokens)", "barrier", "projections", "push tail", "barrier"] if pushed else
+                  ["shrink (this rank's tokens)", "barrier", "projections + peer stores", "barrier"])
+        pm = torch.tensor([float(np.mean([r[i].elapsed_time(r[i + 1]) for r in rows_])) for i in range(len(names_))],
+                          dtype=torch.float64, device=dev)
+        dist.all_reduce(pm, op=dist.ReduceOp.MAX)
+        phase_ms = [{"phase": n_, "ms": float(v_)} for n_, v_ in zip(names_, pm.tolist())]
 
     # ---- per projection (fused call = shrink + main kernel), then the dominant kernel instance alone with the
     #      shrink result reused: the roofline's kernel ----
@@ -651,7 +721,9 @@ def main():
     step_ms, main_ms, e2e_ms, other_ms, e2e_serial_ms = vals[:5]
     proj_ms = vals[5:]
 
-    args.collective_used = ("tiles stored into every rank's buffer by the kernel + one device barrier per step"
+    args.collective_used = (("each projection's columns copied into every rank's buffer by a push kernel on a second stream, beside the "
+                             "next projection's kernels + one device barrier per step" if pushed else
+                             "tiles stored into every rank's buffer by the kernel + one device barrier per step")
                             + ("; shrink sharded by tokens, its tiles stored into every rank's scratch + one device barrier" if sharded_shrink else "")
                             if fused else "NCCL all-gather per projection")
     if rank == 0:
@@ -678,7 +750,7 @@ def main():
                      "kernel_ms": main_ms, "algorithmic_bytes": dom_work["main_kernel"], "launch_shape": dom_shape})
         t_roof = max(work_all["flops"] / (FP4_PEAK_TFLOPS * 1e12), work_all["total"] / (hbm_gbs * 1e9))
         t_roof_bf16 = max(work_all["flops"] / (bf16_sustained * 1e12), work_all["total"] / (hbm_gbs * 1e9))
-        per_step_launches = sum((1 if c.seq_slot is not None else 0) + 1 + (1 if mode else 0) for c in work.projections) + (1 if fused else 0)
+        per_step_launches = sum((1 if c.seq_slot is not None else 0) + 1 + (1 if mode else 0) for c in work.projections) + (1 if fused else 0) + (len(work.projections) if pushed else 0)
         line = {
             "metric": METRIC, "value": M / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": tp,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
@@ -707,6 +779,8 @@ def main():
         }
         if collective_note:
             line["collective_note"] = collective_note
+        if phase_ms:
+            line["step_phases"] = phase_ms
         if have_other:
             line["other_activation_mode"] = {
                 "activations": "bf16" if mode else "fp4", "ms_per_step": other_ms, "value": M / (other_ms * 1e-3),

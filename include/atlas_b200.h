@@ -252,6 +252,19 @@ ATLAS_B200_API int atlas_b200_lora_shrink_tiles(const atlas_b200_linear_desc* de
  *   - ATLAS_B200_FLAG_REUSE_SHRINK through this entry point reuses whatever the array holds: it is only meaningful when
  *     no other call (of any descriptor, on any stream of the device) has gone through this entry point since the call
  *     whose shrink result is to be reused. */
+/* Tensor-parallel exchange as a copy that runs BESIDE the next projection's kernels: the [m, n_cols] BF16 block at `src`
+ * (row stride src_row_stride elements; this rank's columns of its own gathered buffer) is stored into the same block of
+ * each of the n_dest <= 8 buffers `dest[i]` (row stride dst_row_stride; the peers' gathered buffers as mapped into this
+ * process, each already offset to the block's first column).  One small kernel (128 threads per CTA, no shared memory):
+ * launched on a second stream after the projection that produced the block, its CTAs share the SMs with the following
+ * projection's kernels and its NVLink stores overlap their arithmetic.  Use it where a rank's share of a projection is a
+ * single wave of tiles, so that stores issued by the tiles themselves (n_dest > 1 in the descriptor) would all fall at
+ * the end of that wave.  Replaces the all-gather after a column-parallel linear
+ * (crates/spark-comm/src/nccl_backend/comm_impl.rs:130-145); the caller still synchronises the ranks before reading.
+ * n_cols and both strides multiples of 8, all addresses 16-byte aligned (-3 otherwise). */
+ATLAS_B200_API int atlas_b200_push_columns(const void* src, uint32_t src_row_stride, void* const* dest, uint32_t n_dest,
+                            uint32_t dst_row_stride, uint32_t m, uint32_t n_cols, void* stream);
+
 #define ATLAS_B200_STATIC_SCRATCH_ELEMS (512u * 1024u)
 ATLAS_B200_API int atlas_b200_nvfp4_lora_linear_noalloc(const atlas_b200_linear_desc* desc, void* stream);
 
