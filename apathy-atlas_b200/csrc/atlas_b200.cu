@@ -840,7 +840,18 @@ int nvfp4_lora_linear(const atlas_b200_linear_desc& d, cudaStream_t st, const Sh
                           (d.n_dest ? d.y_col_offset % 8 == 0 : aligned(d.y, 16));
         for (uint32_t r = 0; persistent && r < d.n_dest; ++r) persistent = aligned(d.y_dest[r], 16);
         // two token tiles of 192 per pass (the expanded weight operand is used twice) where the batch has several passes
-        const bool two_tiles = persistent && !act_fp4 && !(d.flags & ATLAS_B200_FLAG_ONE_TILE_PASS) && d.m >= 768;
+        bool two_tiles = persistent && !act_fp4 && !(d.flags & ATLAS_B200_FLAG_ONE_TILE_PASS) && d.m >= 768;
+        if (two_tiles) {
+            // ... unless whole waves say otherwise: a pass of two 192-token tiles takes about 977 cycles per K block, a pass
+            // of one 256-token tile about 725 (measured), and the last wave costs a full pass however few CTA pairs it holds
+            // (a 1024-feature projection over 8192 tokens: 88 two-tile passes or 128 one-tile passes on 74 pairs, two waves each)
+            const int c2 = persist_resident_clusters<192, 2, false>(2), c1 = persist_resident_clusters<256, 1, false>(0);
+            if (c1 > 0 && c2 > 0) {
+                const uint64_t w2 = (persist_tiles<192, 2>(d) + uint32_t(c2) - 1) / uint32_t(c2);
+                const uint64_t w1 = (persist_tiles<256, 1>(d) + uint32_t(c1) - 1) / uint32_t(c1);
+                if (w1 * 725 < w2 * 977) two_tiles = false;
+            }
+        }
         if (persistent) {
             const int clusters = act_fp4 ? persist_resident_clusters<256, 1, true>(1)
                                          : (two_tiles ? persist_resident_clusters<192, 2, false>(2) : persist_resident_clusters<256, 1, false>(0));

@@ -96,3 +96,26 @@ def test_shards_of_configuration_1_shape(cuda, atlas, oracle, tp_n, K, r):
     for b in bufs[1:]:
         assert np.array_equal(bits_from_dev(b), first)
     assert atlas.device_status() == 0
+
+
+def test_push_columns_copies_the_block_and_nothing_else(cuda, atlas):
+    """atlas_b200_push_columns: an [m, n_cols] block of a row-major buffer into the same columns of several others
+    (local buffers stand in for the peers' gathered buffers), ragged chunk counts included."""
+    torch = cuda
+    for m, n_total, col0, n_cols in ((8192, 4096, 512, 512), (77, 1536, 1024, 264), (3, 64, 8, 8)):
+        src = torch.randint(-30000, 30000, (m, n_total), dtype=torch.int16, device="cuda")
+        dests = [torch.full((m, n_total), 0x7FC0, dtype=torch.int16, device="cuda") for _ in range(3)]
+        atlas.push_columns(src.data_ptr() + col0 * 2, n_total, [d.data_ptr() + col0 * 2 for d in dests], n_total, m, n_cols)
+        torch.cuda.synchronize()
+        for d in dests:
+            assert torch.equal(d[:, col0:col0 + n_cols], src[:, col0:col0 + n_cols])
+            assert (d[:, :col0] == 0x7FC0).all() and (d[:, col0 + n_cols:] == 0x7FC0).all()
+    # rules: 16-byte chunks only, at most 8 destinations
+    src = torch.zeros((4, 64), dtype=torch.int16, device="cuda")
+    dst = torch.zeros((4, 64), dtype=torch.int16, device="cuda")
+    with pytest.raises(atlas.AtlasError):
+        atlas.push_columns(src.data_ptr(), 64, [dst.data_ptr()], 64, 4, 12)
+    with pytest.raises(atlas.AtlasError):
+        atlas.push_columns(src.data_ptr() + 2, 64, [dst.data_ptr()], 64, 4, 8)
+    with pytest.raises(atlas.AtlasError):
+        atlas.push_columns(src.data_ptr(), 64, [dst.data_ptr()] * 9, 64, 4, 8)

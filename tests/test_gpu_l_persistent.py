@@ -55,7 +55,7 @@ def test_base_only_and_second_call(cuda, atlas, oracle):
     assert atlas.device_status() == 0
 
 
-@pytest.mark.parametrize("M,K,N", [(3072, 512, 4864), (3100, 256, 4992)])
+@pytest.mark.parametrize("M,K,N", [(3072, 512, 9728), (3100, 256, 9600)])
 def test_two_token_tiles_per_pass(cuda, atlas, oracle, M, K, N):
     """Passes of two 192-token tiles sharing each expanded weight stage: a token's bits do not depend on the tiling."""
     from atlas_b200 import synth
