@@ -313,10 +313,11 @@ def main():
     ap.add_argument("--impl", default="atlas_b200", choices=["atlas_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU sample (0: sized for a few seconds per pass)")
-    ap.add_argument("--collective", default="push", choices=["push", "fused", "nccl"],
-                    help="N > 1: push = each projection's columns copied to the peers by a small kernel on a second stream while "
-                         "the next projection computes; fused = the kernel's own store phase writes into every rank's buffer; "
-                         "nccl = all-gather after each projection")
+    ap.add_argument("--collective", default="auto", choices=["auto", "push", "fused", "nccl"],
+                    help="N > 1: fused = the kernel's own store phase writes every tile into every rank's buffer; push = each "
+                         "projection's columns copied to the peers by a small kernel on a second stream while the next projection "
+                         "computes; auto = fused where the rank's share runs as the persistent kernel (stores hidden under the next "
+                         "tile), push where it is a single wave of tiles; nccl = all-gather after each projection")
     ap.add_argument("--activations", default="bf16", choices=["bf16", "fp4"],
                     help="bf16: the layer as specified (exact activations); fp4: the opt-in W4A4 mode as the timed step")
     ap.add_argument("--op", default="fused", choices=["fused", "lora_bgmv"],
@@ -378,7 +379,7 @@ def main():
     # a rank that has passed step i's barrier may start step i+1's stores while a slower rank still reads step i's
     # result, so consecutive steps must not write the same buffers.
     fused, sym_sets, collective_note = False, [], None
-    if tp > 1 and args.collective in ("fused", "push"):
+    if tp > 1 and args.collective in ("auto", "fused", "push"):
         try:
             import torch.distributed._symmetric_memory as symm_mem
             if hasattr(symm_mem, "enable_symm_mem_for_group"):
@@ -403,8 +404,8 @@ def main():
         fused = bool(int(ok.item()))
     # push: the kernels store into this rank's own gathered buffer only; a copy kernel on a second stream sends each
     # projection's columns to the peers while the next projection computes
-    pushed = fused and args.collective == "push"
-    side = torch.cuda.Stream(device=dev) if pushed else None
+    push_proj = [fused and args.collective == "push"] * n_proj          # per projection; "auto" decides below
+    side = torch.cuda.Stream(device=dev) if fused else None
     y_all = ([torch.empty((tp, M, dw.n_local[i]), dtype=torch.bfloat16, device=dev) for i in range(n_proj)]
              if tp > 1 else None)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > L2 (126 MB)
@@ -421,7 +422,7 @@ def main():
             xin = None if x_of is None else x_of[work.projections[i].meta["input"]]
             if sym is not None:
                 j = 0 if work.fused_out else i
-                place = dict(y_dest=(sym["ptrs"][j] if not pushed else [sym["ptrs"][j][rank]]), out_row_stride=(work.n_total if work.fused_out else work.projections[i].N),
+                place = dict(y_dest=(sym["ptrs"][j] if not push_proj[i] else [sym["ptrs"][j][rank]]), out_row_stride=(work.n_total if work.fused_out else work.projections[i].N),
                              y_col_offset=(int(full_cols0[i]) if work.fused_out else 0) + rank * dw.n_local[i])
                 ds.append(dw.desc(i, None, flags, x=xin, seq_slot=seq_slot, **place))
             else:
@@ -442,6 +443,14 @@ def main():
             ws_sym = dict(bufs=ws_bufs, handles=ws_handles, ptrs=ws_ptrs)
         except Exception as e:
             collective_note = f"scratch could not be mapped to the peers ({type(e).__name__}: {e}); every rank runs the whole shrink"
+    if fused and args.collective == "auto":
+        # which of this rank's shares run as the persistent kernel (the same on every rank: the shapes are)
+        for i, d_ in enumerate(build_descs(mode, sym_sets[0])):
+            ab.nvfp4_lora_linear(d_, torch.cuda.current_stream())
+            push_proj[i] = not ab.last_launch_shape()["persistent_tiles_per_pass"]
+        torch.cuda.synchronize()
+        dist.barrier()
+    pushed = any(push_proj)
     descs = [build_descs(mode, s) for s in sym_sets] if fused else [build_descs(mode)]
     descs_reuse = [build_descs(mode | ab.FLAG_REUSE_SHRINK, s) for s in sym_sets] if fused else None
     from atlas_b200 import tp as tpmod
@@ -502,9 +511,10 @@ def main():
             dd = descs_reuse[k] if sharded_shrink else descs[k]
             for i in range(n_proj):
                 v = ab.nvfp4_lora_linear(dd[i], stream)
-                push_events[k][i].record(stream)
-                side.wait_event(push_events[k][i])
-                push(k, i)
+                if push_proj[i]:
+                    push_events[k][i].record(stream)
+                    side.wait_event(push_events[k][i])
+                    push(k, i)
             mark()
             push_events[k][n_proj].record(side)
             stream.wait_event(push_events[k][n_proj])
@@ -721,8 +731,12 @@ def main():
     step_ms, main_ms, e2e_ms, other_ms, e2e_serial_ms = vals[:5]
     proj_ms = vals[5:]
 
-    args.collective_used = (("each projection's columns copied into every rank's buffer by a push kernel on a second stream, beside the "
-                             "next projection's kernels + one device barrier per step" if pushed else
+    names_p = [c.name.split("/")[-1] for c in work.projections]
+    args.collective_used = ((("columns of " + ",".join(n_ for n_, p_ in zip(names_p, push_proj) if p_) + " copied into every rank's buffer by a push "
+                              "kernel on a second stream beside the next projection's kernels"
+                              + ("; tiles of " + ",".join(n_ for n_, p_ in zip(names_p, push_proj) if not p_) + " stored into every rank's "
+                                 "buffer by the persistent kernel under its next tile" if not all(push_proj) else "")
+                              + " + one device barrier per step") if pushed else
                              "tiles stored into every rank's buffer by the kernel + one device barrier per step")
                             + ("; shrink sharded by tokens, its tiles stored into every rank's scratch + one device barrier" if sharded_shrink else "")
                             if fused else "NCCL all-gather per projection")
@@ -750,7 +764,7 @@ def main():
                      "kernel_ms": main_ms, "algorithmic_bytes": dom_work["main_kernel"], "launch_shape": dom_shape})
         t_roof = max(work_all["flops"] / (FP4_PEAK_TFLOPS * 1e12), work_all["total"] / (hbm_gbs * 1e9))
         t_roof_bf16 = max(work_all["flops"] / (bf16_sustained * 1e12), work_all["total"] / (hbm_gbs * 1e9))
-        per_step_launches = sum((1 if c.seq_slot is not None else 0) + 1 + (1 if mode else 0) for c in work.projections) + (1 if fused else 0) + (len(work.projections) if pushed else 0)
+        per_step_launches = sum((1 if c.seq_slot is not None else 0) + 1 + (1 if mode else 0) for c in work.projections) + (1 if fused else 0) + sum(1 for p_ in push_proj if p_)
         line = {
             "metric": METRIC, "value": M / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": tp,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
