@@ -43,7 +43,7 @@ EXPORTS = (
     "atlas_b200_nvfp4_scale2_from_absmax", "atlas_b200_nvfp4_combined_global_scale", "atlas_b200_silu_mul",
     "atlas_b200_silu_mul_quant_nvfp4",
     "atlas_b200_nvfp4_lora_linear", "atlas_b200_nvfp4_lora_linear_noalloc", "atlas_b200_lora_shrink_tiles",
-    "atlas_b200_push_columns", "atlas_b200_column_shard",
+    "atlas_b200_push_columns", "atlas_b200_copy_columns", "atlas_b200_column_shard",
     "atlas_b200_build_seq_slot", "atlas_b200_routed_prefill_slot_of", "atlas_b200_peft_scaling",
     "atlas_b200_module_dims", "atlas_b200_pool_slot_bytes", "atlas_b200_slot_base_offset",
     "atlas_b200_module_slot_offsets", "atlas_b200_pack_module", "atlas_b200_build_route_tables", "atlas_b200_select_victim_slot",
@@ -123,6 +123,7 @@ def lib() -> C.CDLL:
     L.atlas_b200_nvfp4_lora_linear_noalloc.argtypes = [C.POINTER(LinearDesc), vp]
     L.atlas_b200_lora_shrink_tiles.argtypes = [C.POINTER(LinearDesc), u32, u32, C.POINTER(vp), u32, vp]
     L.atlas_b200_push_columns.argtypes = [vp, u32, C.POINTER(vp), u32, u32, u32, u32, vp]
+    L.atlas_b200_copy_columns.argtypes = [vp, u32, C.POINTER(vp), u32, u32, u32, u32, vp]
     L.atlas_b200_column_shard.argtypes = [u32, u32, u32, C.POINTER(u32), C.POINTER(u32)]
     L.atlas_b200_build_seq_slot.argtypes = [C.POINTER(i32), sz, sz, i32, C.POINTER(i32)]
     L.atlas_b200_routed_prefill_slot_of.argtypes = [i32, sz, sz]
@@ -373,11 +374,13 @@ def lora_shrink_tiles(desc: LinearDesc, row_begin: int, row_count: int, ws_dest,
         C.byref(desc), row_begin, row_count, arr, len(ws_dest), _stream_ptr(stream)))
 
 
-def push_columns(src_ptr: int, src_row_stride: int, dest_ptrs, dst_row_stride: int, m: int, n_cols: int, stream=None) -> None:
+def push_columns(src_ptr: int, src_row_stride: int, dest_ptrs, dst_row_stride: int, m: int, n_cols: int, stream=None,
+                 copy_engines: bool = False) -> None:
     """Copy the [m, n_cols] BF16 block at device address `src_ptr` into the same block of every buffer in `dest_ptrs`
-    (addresses of the block's first element in the peers' gathered buffers)."""
+    (addresses of the block's first element in the peers' gathered buffers): by the push kernel, or by the copy engines."""
     arr = (C.c_void_p * len(dest_ptrs))(*[int(p) for p in dest_ptrs])
-    _check("atlas_b200_push_columns", lib().atlas_b200_push_columns(
+    fn = lib().atlas_b200_copy_columns if copy_engines else lib().atlas_b200_push_columns
+    _check("atlas_b200_copy_columns" if copy_engines else "atlas_b200_push_columns", fn(
         C.c_void_p(int(src_ptr)), src_row_stride, arr, len(dest_ptrs), dst_row_stride, m, n_cols, _stream_ptr(stream)))
 
 

@@ -1060,6 +1060,21 @@ int atlas_b200_push_columns(const void* src, uint32_t src_row_stride, void* cons
     return launch_status();
 }
 
+int atlas_b200_copy_columns(const void* src, uint32_t src_row_stride, void* const* dest, uint32_t n_dest, uint32_t dst_row_stride,
+                            uint32_t m, uint32_t n_cols, void* stream) {
+    if (!src || (!dest && n_dest)) return ATLAS_B200_ERR_NULL;
+    if (m == 0 || n_cols == 0 || n_dest == 0) return ATLAS_B200_OK;
+    if (n_cols > src_row_stride || n_cols > dst_row_stride) return ATLAS_B200_ERR_DIMS;
+    for (uint32_t d = 0; d < n_dest; ++d) {
+        if (!dest[d]) return ATLAS_B200_ERR_NULL;
+        // one strided copy per destination, carried by the copy engines
+        cudaError_t e = cudaMemcpy2DAsync(dest[d], size_t(dst_row_stride) * 2, src, size_t(src_row_stride) * 2, size_t(n_cols) * 2, m,
+                                          cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return cuda_status(e);
+    }
+    return ATLAS_B200_OK;
+}
+
 int atlas_b200_silu_mul(const void* gate_bf16, const void* up_bf16, void* out_bf16, float gate_scale, float up_scale, float swiglu_limit,
                         uint32_t m, uint32_t k, uint32_t in_row_stride, uint32_t out_row_stride, void* stream) {
     if (m == 0 || k == 0) return ATLAS_B200_OK;

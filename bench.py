@@ -313,11 +313,11 @@ def main():
     ap.add_argument("--impl", default="atlas_b200", choices=["atlas_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU sample (0: sized for a few seconds per pass)")
-    ap.add_argument("--collective", default="auto", choices=["auto", "push", "fused", "nccl"],
+    ap.add_argument("--collective", default="auto", choices=["auto", "copy", "push", "fused", "nccl"],
                     help="N > 1: fused = the kernel's own store phase writes every tile into every rank's buffer; push = each "
                          "projection's columns copied to the peers by a small kernel on a second stream while the next projection "
-                         "computes; auto = fused where the rank's share runs as the persistent kernel (stores hidden under the next "
-                         "tile), push where it is a single wave of tiles; nccl = all-gather after each projection")
+                         "computes; copy = the same by the copy engines (one strided copy per peer, no SM involved); auto = fused where the rank's share runs as the persistent kernel (stores hidden under the next "
+                         "tile), copy where it is a single wave of tiles; nccl = all-gather after each projection")
     ap.add_argument("--activations", default="bf16", choices=["bf16", "fp4"],
                     help="bf16: the layer as specified (exact activations); fp4: the opt-in W4A4 mode as the timed step")
     ap.add_argument("--op", default="fused", choices=["fused", "lora_bgmv"],
@@ -379,7 +379,7 @@ def main():
     # a rank that has passed step i's barrier may start step i+1's stores while a slower rank still reads step i's
     # result, so consecutive steps must not write the same buffers.
     fused, sym_sets, collective_note = False, [], None
-    if tp > 1 and args.collective in ("auto", "fused", "push"):
+    if tp > 1 and args.collective in ("auto", "copy", "fused", "push"):
         try:
             import torch.distributed._symmetric_memory as symm_mem
             if hasattr(symm_mem, "enable_symm_mem_for_group"):
@@ -404,8 +404,9 @@ def main():
         fused = bool(int(ok.item()))
     # push: the kernels store into this rank's own gathered buffer only; a copy kernel on a second stream sends each
     # projection's columns to the peers while the next projection computes
-    push_proj = [fused and args.collective == "push"] * n_proj          # per projection; "auto" decides below
-    side = torch.cuda.Stream(device=dev) if fused else None
+    push_proj = [fused and args.collective in ("push", "copy")] * n_proj          # per projection; "auto" decides below
+    by_copy_engines = args.collective in ("copy", "auto")
+    sides = [torch.cuda.Stream(device=dev) for _ in range(min(tp - 1, 4))] if fused else []
     y_all = ([torch.empty((tp, M, dw.n_local[i]), dtype=torch.bfloat16, device=dev) for i in range(n_proj)]
              if tp > 1 else None)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > L2 (126 MB)
@@ -471,17 +472,26 @@ def main():
     step_no = [0]
 
     push_events = [[torch.cuda.Event() for _ in range(n_proj + 1)] for _ in range(2)] if pushed else None
+    push_joins = [[torch.cuda.Event() for _ in sides] for _ in range(2)]
     shrink_streams = [torch.cuda.Stream(device=dev) for _ in range(n_proj)] if sharded_shrink else None
     shrink_fork = torch.cuda.Event()
     shrink_join = [torch.cuda.Event() for _ in range(n_proj)]
 
     def push(k, i):
-        """Projection i's columns of this rank's gathered buffer (set k) into the same columns of every peer's."""
+        """Projection i's columns of this rank's gathered buffer (set k) into the same columns of every peer's.  The peers
+        are taken in the order rank+1, rank+2, ...: at any moment every GPU is then the target of one sender, not of all."""
         j = 0 if work.fused_out else i
         n_row = work.n_total if work.fused_out else work.projections[i].N
         col = (int(full_cols0[i]) if work.fused_out else 0) + rank * dw.n_local[i]
         ptrs = sym_sets[k]["ptrs"][j]
-        ab.push_columns(ptrs[rank] + col * 2, n_row, [ptrs[r] + col * 2 for r in range(tp) if r != rank], n_row, M, dw.n_local[i], side)
+        peers = [(rank + o) % tp for o in range(1, tp)]
+        for s_ in sides:
+            s_.wait_event(push_events[k][i])
+        if by_copy_engines:
+            for o, r in enumerate(peers):           # one strided copy per peer, spread over the side streams (and so over copy engines)
+                ab.push_columns(ptrs[rank] + col * 2, n_row, [ptrs[r] + col * 2], n_row, M, dw.n_local[i], sides[o % len(sides)], copy_engines=True)
+        else:
+            ab.push_columns(ptrs[rank] + col * 2, n_row, [ptrs[r] + col * 2 for r in peers], n_row, M, dw.n_local[i], sides[0])
 
     def step(marks=None):
         """One step.  `marks`: optional list that receives CUDA events recorded between the step's phases."""
@@ -513,11 +523,11 @@ def main():
                 v = ab.nvfp4_lora_linear(dd[i], stream)
                 if push_proj[i]:
                     push_events[k][i].record(stream)
-                    side.wait_event(push_events[k][i])
                     push(k, i)
             mark()
-            push_events[k][n_proj].record(side)
-            stream.wait_event(push_events[k][n_proj])
+            for o, s_ in enumerate(sides):
+                push_joins[k][o].record(s_)
+                stream.wait_event(push_joins[k][o])
             mark()
             sym_sets[k]["handles"][0].barrier(channel=0)     # every rank's columns have landed in every buffer
             mark()
@@ -732,8 +742,8 @@ def main():
     proj_ms = vals[5:]
 
     names_p = [c.name.split("/")[-1] for c in work.projections]
-    args.collective_used = ((("columns of " + ",".join(n_ for n_, p_ in zip(names_p, push_proj) if p_) + " copied into every rank's buffer by a push "
-                              "kernel on a second stream beside the next projection's kernels"
+    args.collective_used = ((("columns of " + ",".join(n_ for n_, p_ in zip(names_p, push_proj) if p_) + " copied into every rank's buffer by "
+                              + ("the copy engines" if by_copy_engines else "a push kernel") + " on a second stream beside the next projection's kernels"
                               + ("; tiles of " + ",".join(n_ for n_, p_ in zip(names_p, push_proj) if not p_) + " stored into every rank's "
                                  "buffer by the persistent kernel under its next tile" if not all(push_proj) else "")
                               + " + one device barrier per step") if pushed else
@@ -764,7 +774,7 @@ def main():
                      "kernel_ms": main_ms, "algorithmic_bytes": dom_work["main_kernel"], "launch_shape": dom_shape})
         t_roof = max(work_all["flops"] / (FP4_PEAK_TFLOPS * 1e12), work_all["total"] / (hbm_gbs * 1e9))
         t_roof_bf16 = max(work_all["flops"] / (bf16_sustained * 1e12), work_all["total"] / (hbm_gbs * 1e9))
-        per_step_launches = sum((1 if c.seq_slot is not None else 0) + 1 + (1 if mode else 0) for c in work.projections) + (1 if fused else 0) + sum(1 for p_ in push_proj if p_)
+        per_step_launches = sum((1 if c.seq_slot is not None else 0) + 1 + (1 if mode else 0) for c in work.projections) + (1 if fused else 0) + (0 if by_copy_engines else sum(1 for p_ in push_proj if p_))
         line = {
             "metric": METRIC, "value": M / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": tp,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,

@@ -265,6 +265,12 @@ ATLAS_B200_API int atlas_b200_lora_shrink_tiles(const atlas_b200_linear_desc* de
 ATLAS_B200_API int atlas_b200_push_columns(const void* src, uint32_t src_row_stride, void* const* dest, uint32_t n_dest,
                             uint32_t dst_row_stride, uint32_t m, uint32_t n_cols, void* stream);
 
+/* The same exchange carried by the copy engines instead of a kernel: one strided device-to-device copy
+ * (cudaMemcpy2DAsync) per destination, no SM involved.  Same arguments as atlas_b200_push_columns, without its alignment
+ * rules. */
+ATLAS_B200_API int atlas_b200_copy_columns(const void* src, uint32_t src_row_stride, void* const* dest, uint32_t n_dest,
+                            uint32_t dst_row_stride, uint32_t m, uint32_t n_cols, void* stream);
+
 #define ATLAS_B200_STATIC_SCRATCH_ELEMS (512u * 1024u)
 ATLAS_B200_API int atlas_b200_nvfp4_lora_linear_noalloc(const atlas_b200_linear_desc* desc, void* stream);
 
