@@ -43,7 +43,7 @@ EXPORTS = (
     "atlas_b200_nvfp4_scale2_from_absmax", "atlas_b200_nvfp4_combined_global_scale", "atlas_b200_silu_mul",
     "atlas_b200_silu_mul_quant_nvfp4",
     "atlas_b200_nvfp4_lora_linear", "atlas_b200_nvfp4_lora_linear_noalloc", "atlas_b200_lora_shrink_tiles",
-    "atlas_b200_push_columns", "atlas_b200_copy_columns", "atlas_b200_column_shard",
+    "atlas_b200_push_columns", "atlas_b200_copy_columns", "atlas_b200_selftest_bounded_wait", "atlas_b200_column_shard",
     "atlas_b200_build_seq_slot", "atlas_b200_routed_prefill_slot_of", "atlas_b200_peft_scaling",
     "atlas_b200_module_dims", "atlas_b200_pool_slot_bytes", "atlas_b200_slot_base_offset",
     "atlas_b200_module_slot_offsets", "atlas_b200_pack_module", "atlas_b200_build_route_tables", "atlas_b200_select_victim_slot",
@@ -124,6 +124,7 @@ def lib() -> C.CDLL:
     L.atlas_b200_lora_shrink_tiles.argtypes = [C.POINTER(LinearDesc), u32, u32, C.POINTER(vp), u32, vp]
     L.atlas_b200_push_columns.argtypes = [vp, u32, C.POINTER(vp), u32, u32, u32, u32, vp]
     L.atlas_b200_copy_columns.argtypes = [vp, u32, C.POINTER(vp), u32, u32, u32, u32, vp]
+    L.atlas_b200_selftest_bounded_wait.argtypes = [C.c_uint64, C.POINTER(u32)]
     L.atlas_b200_column_shard.argtypes = [u32, u32, u32, C.POINTER(u32), C.POINTER(u32)]
     L.atlas_b200_build_seq_slot.argtypes = [C.POINTER(i32), sz, sz, i32, C.POINTER(i32)]
     L.atlas_b200_routed_prefill_slot_of.argtypes = [i32, sz, sz]
@@ -382,6 +383,13 @@ def push_columns(src_ptr: int, src_row_stride: int, dest_ptrs, dst_row_stride: i
     fn = lib().atlas_b200_copy_columns if copy_engines else lib().atlas_b200_push_columns
     _check("atlas_b200_copy_columns" if copy_engines else "atlas_b200_push_columns", fn(
         C.c_void_p(int(src_ptr)), src_row_stride, arr, len(dest_ptrs), dst_row_stride, m, n_cols, _stream_ptr(stream)))
+
+
+def selftest_bounded_wait(limit_ns: int):
+    """(first waiter gave up, second waiter gave up, ns the first waited) of the library's bounded-wait self-test."""
+    out = (C.c_uint32 * 3)()
+    _check("atlas_b200_selftest_bounded_wait", lib().atlas_b200_selftest_bounded_wait(limit_ns, out))
+    return int(out[0]), int(out[1]), int(out[2])
 
 
 STATIC_SCRATCH_ELEMS = 512 * 1024

@@ -1187,6 +1187,20 @@ int atlas_b200_device_status(uint32_t* out_word, int clear) {
     return cuda_status(e);
 }
 
+int atlas_b200_selftest_bounded_wait(uint64_t limit_ns, uint32_t out_host[3]) {
+    if (!out_host) return ATLAS_B200_ERR_NULL;
+    if (limit_ns == 0 || limit_ns > 100000000ull) return ATLAS_B200_ERR_LIMIT;        // at most 0.1 s: this is a test of giving up
+    uint32_t* out_dev = nullptr;
+    cudaError_t e = cudaMalloc(&out_dev, 3 * sizeof(uint32_t));
+    if (e != cudaSuccess) return cuda_status(e);
+    cudaMemset(out_dev, 0xFF, 3 * sizeof(uint32_t));
+    tc::bounded_wait_selftest_kernel<<<1, 64>>>(limit_ns, uint32_t(STATUS_WAIT_EXPIRED_PRODUCER), out_dev);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpy(out_host, out_dev, 3 * sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    cudaFree(out_dev);
+    return cuda_status(e);
+}
+
 int atlas_b200_last_variant(void) { return t_last_variant; }
 
 int atlas_b200_last_launch_shape(uint32_t out[4]) {

@@ -194,7 +194,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // epilogue warps during the main loop) sleep between polls: a polling warp otherwise takes issue
 // slots and shared-memory bandwidth from the warps that feed the tensor pipe.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code,
-                                          uint32_t backoff_ns = 0) {
+                                          uint32_t backoff_ns = 0, uint64_t limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     uint32_t spins = 0;
@@ -203,7 +203,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (global_timer_ns() - t0 > limit_ns) {
                 record_status(code);
                 *abort_flag = 1u;
                 return false;
@@ -220,6 +220,36 @@ __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, v
     const bool ok = mbar_wait(bar, parity, abort_flag, code, backoff_ns);
     acc += (unsigned long long)(clock64() - t0);
     return ok;
+}
+
+__device__ __forceinline__ void fence_barrier_init();
+
+// Self-test of the bounded wait, in the form every kernel of this library uses it: warp 0 waits for a phase of a
+// barrier on which nothing ever arrives, with a short limit; the wait must give up, record `code` in the status word and
+// raise the abort flag; warp 1 waits on the same barrier and must leave through the flag (or its own limit).  The kernel
+// then returns normally: no trap, the context stays usable.  out[0] = 1 if warp 0's wait returned false, out[1] the same
+// for warp 1, out[2] = nanoseconds warp 0 waited.
+__global__ void bounded_wait_selftest_kernel(uint64_t limit_ns, uint32_t code, uint32_t* out) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_s;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(b), "r"(1) : "memory");
+        abort_s = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    volatile uint32_t* abort_flag = &abort_s;
+    if (threadIdx.x == 0) {
+        const uint64_t t0 = global_timer_ns();
+        const bool ok = mbar_wait(b, 0, abort_flag, code, 32, limit_ns);
+        out[0] = ok ? 0u : 1u;
+        const uint64_t dt = global_timer_ns() - t0;
+        out[2] = uint32_t(dt > 0xFFFFFFFFull ? 0xFFFFFFFFull : dt);
+    } else if (threadIdx.x == 32) {
+        const bool ok = mbar_wait(b, 0, abort_flag, code + 1u, 64, 4 * limit_ns);
+        out[1] = ok ? 0u : 1u;
+    }
 }
 
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }

@@ -420,6 +420,12 @@ ATLAS_B200_API int32_t atlas_b200_registry_select_victim(const atlas_b200_regist
  * stream capture.  `clear` != 0 resets it. */
 ATLAS_B200_API int atlas_b200_device_status(uint32_t* out_word, int clear);
 /* Kernel family chosen by the most recent fused / base call on this thread. */
+/* Self-test of the bounded wait every kernel of this library is built on (not on any data path; allocates 12 bytes and
+ * synchronises): a one-CTA kernel waits, with the library's wait primitive and a limit of `limit_ns` (<= 0.1 s), on a
+ * barrier that nothing arrives on.  The wait must give up, record ATLAS_B200 status 0x100 in the device status word and
+ * raise the CTA's abort flag, through which a second waiter leaves; the kernel returns normally.
+ * out[0], out[1] = 1 if the first / second waiter gave up, out[2] = nanoseconds the first one waited. */
+ATLAS_B200_API int atlas_b200_selftest_bounded_wait(uint64_t limit_ns, uint32_t out[3]);
 ATLAS_B200_API int atlas_b200_last_variant(void);
 /* Launch shape of the most recent tcgen05 call on this thread (launcher audit, no counterpart in the reference):
  * out[0] = token tile, out[1] = 1 if CTAs were paired for two-CTA MMAs, out[2] = CTAs per output tile (K split),
