@@ -59,3 +59,25 @@ def test_small_batches_are_refused(cuda, atlas, oracle):
         atlas.lora_shrink_tiles(d, 0, 128, [sh._ws])
     assert e.value.status == -1
     cuda.cuda.synchronize()
+
+
+@pytest.mark.parametrize("rank,n_ad", [(64, 40), (16, 96)])
+def test_more_adapters_in_a_cluster_than_fit_into_one_pass(cuda, atlas, oracle, rank, n_ad):
+    """Uniformly mixed adapter ids: every 128-row cluster of the prefill shrink meets far more adapters than its 512
+    accumulator columns hold (8 of rank 64, 32 of rank 16), so it walks its rows in several passes, re-using the ring
+    and the exchange area each time.  Checked against the oracle, in both output forms (masked tiles for the fused
+    kernel, and rows of lora_t when no scratch is given), which must also agree bit for bit."""
+    from atlas_b200 import synth
+    from gpu_util import DeviceCase, assert_close, ideal
+    case = synth.make_case("mix", M=1280, K=512, N=512, ranks=[rank] * n_ad, max_rank=rank, ids="uniform", none_frac=0.05,
+                           scale2=0.02, b_std=0.1, seed=rank)
+    per_cluster = [len(set(int(s) for s in case.seq_slot[i:i + 128] if s >= 0)) for i in range(0, case.M, 128)]
+    assert min(per_cluster) > 512 // rank                      # every cluster needs more than one pass
+    dc = DeviceCase(cuda, atlas, case)
+    y_tiles, variant = dc.run(lora_ws=True)
+    assert variant == atlas.VARIANT_TCGEN05 and atlas.last_launch_shape()["lora_tiles_from_shrink"]
+    y_rows, _ = dc.run(lora_ws=False)
+    assert not atlas.last_launch_shape()["lora_tiles_from_shrink"]
+    assert np.array_equal(y_tiles, y_rows)
+    assert_close(oracle, y_tiles, ideal(oracle, case), "several passes per cluster")
+    assert atlas.device_status() == 0
