@@ -238,7 +238,21 @@ class DevWork:
             self.inputs, self.seq_slot = self.dl.inputs, self.dl.seq_slot
             self.n_local = [p["n_local"] for p in self.dl.proj]
             self.local_cases = [self.dl.local_case(i) for i in range(len(self.n_local))]
+            # Projections that read the same activations (q/k/v; gate/up) run one after the other over ONE scratch: the
+            # first one's quantised activations (FP4 mode) serve the others, which skip the quantiser
+            # (ATLAS_B200_FLAG_ACT_FP4_READY); each call's shrink overwrites the LoRA-tile part with its own tiles.
+            # (One GPU only: with N > 1 the scratch of every projection is a symmetric buffer of its own.)
+            self.shares_x_with = {}
+            if tp == 1:
+                first = {}
+                for i, c in enumerate(work.projections):
+                    key = c.meta["input"]
+                    if key in first and self.dl.proj[first[key]]["ws"].numel() == self.dl.proj[i]["ws"].numel():
+                        self.dl.proj[i]["ws"] = self.dl.proj[first[key]]["ws"]
+                        self.shares_x_with[i] = first[key]
+                    first.setdefault(key, i)
         else:
+            self.shares_x_with = {}
             self.ds = tpmod.DeviceShard(torch, ab, work.projections[0], tp, rank)
             self.inputs, self.seq_slot = {"x": self.ds.x}, self.ds.seq_slot
             self.n_local = [self.ds.n_local]
@@ -247,6 +261,8 @@ class DevWork:
 
     def desc(self, i, y, flags=0, x=None, seq_slot=None, **place):
         if self.work.kind == "layer":
+            if (flags & self.ab.FLAG_ACT_FP4) and i in self.shares_x_with:
+                flags |= self.ab.FLAG_ACT_FP4_READY
             return self.dl.desc(i, y, extra_flags=flags, x=x, seq_slot=seq_slot, **place)
         d = self.ds.desc(y, extra_flags=flags, **place)
         if x is not None:
@@ -629,6 +645,7 @@ def main():
     works_local = [algorithmic_work(c) for c in dw.local_cases]
     dom = int(np.argmax([w["flops"] for w in works_local]))
     desc_main_only = build_descs(mode | ab.FLAG_REUSE_SHRINK)[dom]
+    ab.nvfp4_lora_linear(descs_plain[dom], stream)      # the scratch holds this projection's own tiles again
     ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_sub)]
     for a, b in ev2:
         flush.fill_(1)
@@ -774,7 +791,7 @@ def main():
                      "kernel_ms": main_ms, "algorithmic_bytes": dom_work["main_kernel"], "launch_shape": dom_shape})
         t_roof = max(work_all["flops"] / (FP4_PEAK_TFLOPS * 1e12), work_all["total"] / (hbm_gbs * 1e9))
         t_roof_bf16 = max(work_all["flops"] / (bf16_sustained * 1e12), work_all["total"] / (hbm_gbs * 1e9))
-        per_step_launches = sum((1 if c.seq_slot is not None else 0) + 1 + (1 if mode else 0) for c in work.projections) + (1 if fused else 0) + (0 if by_copy_engines else sum(1 for p_ in push_proj if p_))
+        per_step_launches = sum((1 if c.seq_slot is not None else 0) + 1 + (1 if mode and i_ not in dw.shares_x_with else 0) for i_, c in enumerate(work.projections)) + (1 if fused else 0) + (0 if by_copy_engines else sum(1 for p_ in push_proj if p_))
         line = {
             "metric": METRIC, "value": M / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": tp,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
