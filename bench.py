@@ -678,8 +678,9 @@ def main():
         other_ms = float(np.mean([a.elapsed_time(b) for a, b in ev3]))
 
     # ---- end to end through the C ABI with host buffers: every step copies its inputs (every activation tensor and
-    #      seq_slot) from pinned host memory and copies its results back.  With N > 1 every rank copies the replicated
-    #      inputs to its own GPU and reads back its own column shard of every result. ----
+    #      seq_slot) from pinned host memory and copies its results back.  With N > 1 every rank uploads its own rows of
+    #      the (replicated) activations, the ranks all-gather them over NVLink, and every rank reads back its own column
+    #      shard of every result: the host traffic of the job is spread over the ranks' PCIe links. ----
     e2e_ms = e2e_serial_ms = float("nan")
     h2d = sum(int(v.size) * 2 for v in work.inputs.values()) + int(work.seq_slot.size) * 4
     d2h = sum(M * n * 2 for n in dw.n_local)
@@ -696,11 +697,22 @@ def main():
                 return [s["bufs"][0][:, int(full_cols0[i]) + rank * dw.n_local[i]: int(full_cols0[i]) + (rank + 1) * dw.n_local[i]] for i in range(n_proj)]
             return [s["bufs"][i][:, rank * dw.n_local[i]:(rank + 1) * dw.n_local[i]] for i in range(n_proj)]
         e2e_steps = max(3, min(args.steps, 10))
+        shard_h2d = tp > 1 and M % tp == 0
+        r0, r1 = (rank * (M // tp), (rank + 1) * (M // tp)) if shard_h2d else (0, M)
+        if shard_h2d:
+            h2d = sum((r1 - r0) * int(v.shape[1]) * 2 for v in work.inputs.values()) + int(work.seq_slot.size) * 4
         barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            for k_, t_ in dw.inputs.items():
-                t_.copy_(x_host[k_], non_blocking=True)
+            if shard_h2d:
+                # every rank uploads its own rows of each activation tensor over its own PCIe link; the ranks then
+                # exchange the rows over NVLink (in-place all-gather: plumbing, NCCL)
+                for k_, t_ in dw.inputs.items():
+                    t_[r0:r1].copy_(x_host[k_][r0:r1], non_blocking=True)
+                    dist.all_gather_into_tensor(t_.view(torch.bfloat16), t_[r0:r1].view(torch.bfloat16))
+            else:
+                for k_, t_ in dw.inputs.items():
+                    t_.copy_(x_host[k_], non_blocking=True)
             dw.seq_slot.copy_(slot_host, non_blocking=True)
             k = step_no[0] % len(descs)
             step()
@@ -708,6 +720,44 @@ def main():
                 y_host[i].copy_(r_.view(torch.int16), non_blocking=True)
             barrier()
         e2e_ms = e2e_serial_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+
+        # N > 1, as a serving loop would run it: the read-back of step i's results (set k of the rotating result buffers)
+        # runs on its own stream while step i+1 uploads, gathers and computes into the other set; a step waits for the
+        # read-back that last used the set it is about to overwrite.  Uploads and read-backs share no direction of PCIe.
+        if tp > 1:
+            def upload():
+                if shard_h2d:
+                    for k_, t_ in dw.inputs.items():
+                        t_[r0:r1].copy_(x_host[k_][r0:r1], non_blocking=True)
+                        dist.all_gather_into_tensor(t_.view(torch.bfloat16), t_[r0:r1].view(torch.bfloat16))
+                else:
+                    for k_, t_ in dw.inputs.items():
+                        t_.copy_(x_host[k_], non_blocking=True)
+                dw.seq_slot.copy_(slot_host, non_blocking=True)
+            n_set = len(descs)
+            s_out = torch.cuda.Stream(device=dev)
+            ev_step = [torch.cuda.Event() for _ in range(n_set)]
+            ev_out = [torch.cuda.Event() for _ in range(n_set)]
+            y_hosts = [[torch.empty((M, n), dtype=torch.int16).pin_memory() for n in dw.n_local] for _ in range(n_set)]
+            e2e_steps = max(6, min(args.steps, 16))
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                k = step_no[0] % n_set
+                upload()
+                stream.wait_event(ev_out[k])
+                step()
+                ev_step[k].record(stream)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_step[k])
+                    for i, r_ in enumerate(results(k)):
+                        y_hosts[k][i].copy_(r_.view(torch.int16), non_blocking=True)
+                    ev_out[k].record(s_out)
+            barrier()
+            e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+            for i in range(n_proj):
+                if not torch.equal(y_hosts[0][i], y_host[i]) or not torch.equal(y_hosts[-1][i], y_host[i]):
+                    raise RuntimeError("the overlapped end-to-end loop read back something else than the serial one")
 
         # The same as a serving loop would run it on one GPU: two sets of device buffers, the copy of step i+1's
         # inputs and of step i-1's results on their own streams while step i computes.  Every step still carries
@@ -812,8 +862,9 @@ def main():
                     "serial_ms_per_step": e2e_serial_ms,
                     "note": ("value: copies of neighbouring steps overlap the compute (two buffer sets, three streams); "
                              "serial_ms_per_step: copy in, compute, copy out, one step at a time") if tp == 1 else
-                            "per rank: copy the replicated inputs in, compute + exchange, copy this rank's column shard of every "
-                            "result out, one step at a time; byte counts are per rank"},
+                            "per rank: copy this rank's rows of the activations in, all-gather them over NVLink, compute + exchange, "
+                            "copy this rank's column shard of every result out; value: the read-back of step i overlaps step i+1 "
+                            "(two result buffer sets), serial_ms_per_step: one step at a time; byte counts are per rank"},
             "launch_shape": launch_shape,
             "gpu_launches": args.steps * per_step_launches + n_sub * (per_step_launches - (1 if fused else 0)) + n_sub * (2 if mode else 1),
             "clocks": clocks,
