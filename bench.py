@@ -745,7 +745,12 @@ def main():
             for _ in range(e2e_steps):
                 k = step_no[0] % n_set
                 upload()
+                # Set k is about to be overwritten — by this rank and, through their stores, by its peers: every rank's
+                # read-back of set k must have finished first.  Each rank waits for its own, then the ranks meet (the
+                # token-sharded shrink's barrier at the head of the step is that meeting; otherwise one is added).
                 stream.wait_event(ev_out[k])
+                if fused and not sharded_shrink:
+                    sym_sets[k]["handles"][0].barrier(channel=2)
                 step()
                 ev_step[k].record(stream)
                 with torch.cuda.stream(s_out):
