@@ -27,6 +27,7 @@
 #include "kernel_shrink_tc.cuh"
 #include "kernels_mlp_glue.cuh"
 #include "kernel_push.cuh"
+#include "kernel_kv_epilogue.cuh"
 
 namespace atlas {
 
@@ -1057,6 +1058,32 @@ int atlas_b200_push_columns(const void* src, uint32_t src_row_stride, void* cons
         dst_state->push_attr_set = true;
     }
     push_columns_kernel<<<grid, PUSH_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return launch_status();
+}
+
+int atlas_b200_kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint32_t in_row_stride, const void* k_norm_weight,
+                                        const uint32_t* positions, const long long* slot_mapping, void* k_cache, void* v_cache,
+                                        uint32_t tokens, uint32_t kv_heads, uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size,
+                                        float rms_eps, float theta, void* stream) {
+    if (!k_in || !k_norm_weight || !positions || !slot_mapping || !k_cache || (v_in && !v_cache)) return ATLAS_B200_ERR_NULL;
+    if (tokens == 0 || kv_heads == 0) return ATLAS_B200_OK;
+    if (head_dim == 0 || head_dim % 32 || head_dim > uint32_t(KVE_MAX_HEAD_DIM) || rotary_dim > head_dim || rotary_dim % 64 ||
+        block_size == 0 || in_row_stride < kv_heads * head_dim)
+        return ATLAS_B200_ERR_DIMS;
+    KvEpilogueParams p{};
+    p.k_in = static_cast<const uint16_t*>(k_in);
+    p.v_in = static_cast<const uint16_t*>(v_in);
+    p.k_norm_w = static_cast<const uint16_t*>(k_norm_weight);
+    p.positions = positions;
+    p.slot_mapping = slot_mapping;
+    p.k_cache = static_cast<uint16_t*>(k_cache);
+    p.v_cache = static_cast<uint16_t*>(v_cache);
+    p.tokens = tokens; p.kv_heads = kv_heads; p.head_dim = head_dim; p.rotary_dim = rotary_dim; p.block_size = block_size;
+    p.in_row_stride = in_row_stride; p.rms_eps = rms_eps; p.theta = theta;
+    const uint64_t items = uint64_t(tokens) * kv_heads * (v_in ? 2u : 1u);
+    const uint64_t grid = (items + KVE_WARPS - 1) / KVE_WARPS;
+    if (grid > 0x7FFFFFFFull) return ATLAS_B200_ERR_LIMIT;
+    kv_norm_rope_cache_kernel<<<uint32_t(grid), KVE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
     return launch_status();
 }
 

@@ -133,6 +133,22 @@ ATLAS_B200_API int atlas_b200_dequant_nvfp4_to_bf16(const void* packed, const vo
 ATLAS_B200_API int atlas_b200_quantize_bf16_to_nvfp4(const void* in_bf16, void* packed, void* scales,
                                       float scale2, uint32_t n, uint32_t k, void* stream);
 
+/* The K/V consumer of a fused QKV projection, one launch: for every token with slot_mapping[token] >= 0,
+ *   K heads:  k = bf16( rope( x * rsqrt(mean(x^2) + rms_eps) * (1 + w) ) )  into k_cache at the token's paged slot,
+ *   V heads:  copied into v_cache at the same slot (v_in NULL: K side only).
+ * Replaces `fused_k_norm_rope_cache_write_bf16` (kernels/gb10/common/fused_k_norm_rope_cache.cu:60-141; same FP32
+ * arithmetic and summation order, one rounding to BF16, same bits) and the V-side cache write that accompanies it.  Unlike
+ * the reference, k_in / v_in need not be contiguous copies: they point at the first K / V column of token 0 inside the fused
+ * QKV output and in_row_stride (elements) is that buffer's row stride.
+ *   k_norm_weight [head_dim] bf16 ("(1 + w)" convention);  positions [tokens] u32;  slot_mapping [tokens] i64;
+ *   k_cache / v_cache [blocks, block_size, kv_heads, head_dim] bf16;  rotary pairs (d, d + rotary_dim/2), frequency
+ *   theta^(-2 pair / rotary_dim) evaluated in FP64 as the reference does.
+ * head_dim a multiple of 32 up to 256, rotary_dim a multiple of 64 (0: no rotation), else -1. */
+ATLAS_B200_API int atlas_b200_kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint32_t in_row_stride, const void* k_norm_weight,
+                                        const uint32_t* positions, const long long* slot_mapping, void* k_cache, void* v_cache,
+                                        uint32_t tokens, uint32_t kv_heads, uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size,
+                                        float rms_eps, float theta, void* stream);
+
 /* First phase of the weight quantiser: *global_max (a device float the caller has zeroed) becomes max |in| over `total`
  * BF16 elements.  Replaces `nvfp4_global_absmax` (kernels/gb10/common/quantize_bf16_to_nvfp4.cu:131-167). */
 ATLAS_B200_API int atlas_b200_nvfp4_global_absmax(const void* in_bf16, float* global_max_dev, size_t total, void* stream);

@@ -589,3 +589,65 @@ void orc_quantize_f32_to_nvfp4_scale1(const float *in, uint8_t *packed, uint8_t 
         }
     }
 }
+
+/* The K side of the fused QKV epilogue, kernels/gb10/common/fused_k_norm_rope_cache.cu:60-141: per (token, kv head)
+ * RMS norm in the "(1 + w)" convention, rotary embedding of the pairs (d, d + rotary_dim/2) with the frequency
+ * theta^(-2 pair / rotary_dim) evaluated in double, and ONE rounding to BF16 into the paged cache
+ * [blocks, block_size, kv_heads, head_dim] at slot_mapping[token] (negative: token skipped).  The sum of squares follows
+ * the reference's order: an xor-butterfly over each group of 32 consecutive elements (:84-85), then a butterfly over the
+ * group sums padded with zeros (:93-98).  Two library calls differ from the device's by design and bound the agreement
+ * to the last FP32 bits (so to a rare flip of the last BF16 bit): 1/sqrtf for the device's rsqrtf, and the host's
+ * sinf / cosf. */
+static float orc_butterfly32(float *v) {
+    for (int o = 16; o > 0; o >>= 1) {
+        float n[32];
+        for (int l = 0; l < 32; l++) n[l] = v[l] + v[l ^ o];
+        memcpy(v, n, sizeof(n));
+    }
+    return v[0];
+}
+
+void orc_k_norm_rope_cache_write(const uint16_t *k_in, size_t in_row_stride, const uint16_t *k_norm_w, const uint32_t *positions,
+                                 const int64_t *slot_mapping, uint16_t *k_cache, uint32_t tokens, uint32_t kv_heads,
+                                 uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size, float rms_eps, float theta) {
+    for (uint32_t t = 0; t < tokens; t++) {
+        int64_t slot = slot_mapping[t];
+        if (slot < 0) continue;
+        for (uint32_t h = 0; h < kv_heads; h++) {
+            const uint16_t *row = k_in + (size_t)t * in_row_stride + (size_t)h * head_dim;
+            float x[256], nrm[256], grp[32];
+            uint32_t n_grp = (head_dim + 31) / 32;
+            for (uint32_t g = 0; g < 32; g++) grp[g] = 0.0f;
+            for (uint32_t g = 0; g < n_grp; g++) {
+                float v[32];
+                for (uint32_t l = 0; l < 32; l++) {
+                    uint32_t d = g * 32 + l;
+                    x[d < 256 ? d : 255] = d < head_dim ? orc_bf16_to_f32(row[d]) : 0.0f;
+                    float e = d < head_dim ? x[d] : 0.0f;
+                    v[l] = e * e;
+                }
+                grp[g] = orc_butterfly32(v);
+            }
+            float total = orc_butterfly32(grp);
+            float rms = 1.0f / sqrtf(total / (float)head_dim + rms_eps);
+            for (uint32_t d = 0; d < head_dim; d++) nrm[d] = x[d] * rms * (1.0f + orc_bf16_to_f32(k_norm_w[d]));
+            uint32_t half = rotary_dim / 2;
+            uint16_t *dst = k_cache + ((size_t)(slot / block_size) * block_size + (size_t)(slot % block_size)) * ((size_t)kv_heads * head_dim) +
+                            (size_t)h * head_dim;
+            for (uint32_t d = 0; d < head_dim; d++) {
+                float out = nrm[d];
+                if (d < rotary_dim) {
+                    int low = d < half;
+                    uint32_t pair = low ? d : d - half;
+                    float x0 = low ? nrm[d] : nrm[d - half], x1 = low ? nrm[d + half] : nrm[d];
+                    double fe = (double)(2u * pair) / (double)rotary_dim;
+                    float freq = (float)(1.0 / pow((double)theta, fe));
+                    float angle = (float)positions[t] * freq;
+                    float c = cosf(angle), s = sinf(angle);
+                    out = low ? (x0 * c - x1 * s) : (x1 * c + x0 * s);
+                }
+                dst[d] = orc_f32_to_bf16(out);
+            }
+        }
+    }
+}

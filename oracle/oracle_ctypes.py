@@ -91,6 +91,8 @@ def lib() -> C.CDLL:
         L.orc_reference_sequence.argtypes = [C.POINTER(FusedArgs), C.c_void_p, C.c_void_p, C.c_uint32]
         L.orc_num_threads.restype = C.c_int
         L.orc_silu_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_float, C.c_size_t]
+        L.orc_k_norm_rope_cache_write.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
+                                                  C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float]
         L.orc_quantize_f32_to_nvfp4_scale1.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32]
         L.orc_set_num_threads.restype = C.c_int
         L.orc_set_num_threads.argtypes = [C.c_int]
@@ -252,6 +254,15 @@ def reference_sequence(x, M, N, K, out_row_stride=None, **kw):
     xa = np.zeros((M, max(g.max_rank, 1)), dtype=np.uint16)
     lib().orc_reference_sequence(C.byref(g), _p(y), _p(xa), os_)
     return y, xa
+
+
+def k_norm_rope_cache_write(k_in, in_row_stride, k_norm_w, positions, slot_mapping, k_cache, kv_heads, head_dim, rotary_dim, block_size,
+                            rms_eps, theta) -> None:
+    """In place on k_cache (uint16 bits, [blocks, block_size, kv_heads, head_dim]); k_in [tokens, in_row_stride] bits."""
+    k_in = np.ascontiguousarray(k_in)
+    lib().orc_k_norm_rope_cache_write(_p(k_in), in_row_stride, _p(np.ascontiguousarray(k_norm_w)), _p(np.ascontiguousarray(positions, dtype=np.uint32)),
+                                      _p(np.ascontiguousarray(slot_mapping, dtype=np.int64)), _p(k_cache), len(positions), kv_heads, head_dim,
+                                      rotary_dim, block_size, rms_eps, theta)
 
 
 def silu_mul(gate, up, gate_scale=1.0, up_scale=1.0, limit=0.0) -> np.ndarray:

@@ -1,0 +1,91 @@
+"""The K/V consumer of the fused QKV projection (per-head RMS norm with (1 + w), rotary embedding, one rounding, paged
+cache write; V copied into its paged cache): bit for bit against the reference's own kernel
+(kernels/gb10/common/fused_k_norm_rope_cache.cu, compiled unchanged for sm_100a) on a contiguous K, the same bits when K
+and V are read in place from a strided fused QKV buffer, and against the CPU oracle to the last BF16 bit or one next to
+it (the oracle's 1/sqrtf, sinf and cosf are the host library's, the device's are its own)."""
+import numpy as np
+import pytest
+
+from gpu_util import RefModule, bits_from_dev, to_dev
+
+pytestmark = pytest.mark.gpu
+
+FILL = 0x7FC0
+
+
+def _inputs(oracle, tokens, kv_heads, head_dim, seed):
+    rng = np.random.default_rng(seed)
+    k = oracle.f32_to_bf16((rng.standard_normal((tokens, kv_heads * head_dim)) * rng.uniform(0.1, 18.0, (tokens, 1))).astype(np.float32))
+    v = oracle.f32_to_bf16(rng.standard_normal((tokens, kv_heads * head_dim)).astype(np.float32))
+    w = oracle.f32_to_bf16((rng.standard_normal(head_dim) * 0.1).astype(np.float32))
+    pos = rng.integers(0, 131072, tokens).astype(np.uint32)
+    n_slots = tokens + 37
+    slots = rng.permutation(n_slots)[:tokens].astype(np.int64)
+    slots[rng.random(tokens) < 0.1] = -1                        # padding tokens
+    return k, v, w, pos, slots, n_slots
+
+
+@pytest.mark.parametrize("head_dim,rotary_dim", [(128, 64), (128, 128), (256, 64), (64, 0)])
+def test_k_norm_rope_cache_write(cuda, atlas, oracle, head_dim, rotary_dim):
+    torch = cuda
+    tokens, kv_heads, block_size, eps, theta = 301, 4, 16, 1e-6, 1.0e7
+    k, v, w, pos, slots, n_slots = _inputs(oracle, tokens, kv_heads, head_dim, head_dim + rotary_dim)
+    n_blocks = (n_slots + block_size - 1) // block_size
+    width = kv_heads * head_dim
+    kd, vd, wd = to_dev(torch, k), to_dev(torch, v), to_dev(torch, w)
+    posd, slotd = to_dev(torch, pos), torch.from_numpy(slots).cuda()
+
+    def cache():
+        return torch.full((n_blocks, block_size, kv_heads, head_dim), np.int16(np.uint16(FILL).view(np.int16)), dtype=torch.int16, device="cuda")
+
+    # this library, K and V contiguous
+    kc, vc = cache(), cache()
+    atlas.kv_norm_rope_cache_write(kd, vd, width, wd, posd, slotd, kc, vc, tokens, kv_heads, head_dim, rotary_dim, block_size, eps, theta)
+    torch.cuda.synchronize()
+    got_k, got_v = bits_from_dev(kc), bits_from_dev(vc)
+    live = slots >= 0
+    blk, off = slots[live] // block_size, slots[live] % block_size
+    assert np.array_equal(got_v[blk, off].reshape(-1, width), v[live])                 # V: a plain copy
+    untouched = np.ones((n_blocks, block_size), dtype=bool)
+    untouched[blk, off] = False
+    assert (got_k[untouched] == FILL).all() and (got_v[untouched] == FILL).all()       # nothing else written
+
+    # the reference's kernel on the same contiguous K (rotary_dim = 0 is not a case it is launched with)
+    if rotary_dim:
+        ref = RefModule("fused_k_norm_rope_cache")
+        kc_ref = cache()
+        ref.launch("fused_k_norm_rope_cache_write_bf16", (tokens, kv_heads, 1), (head_dim, 1, 1),
+                   [kd.data_ptr(), wd.data_ptr(), posd.data_ptr(), kc_ref.data_ptr(), slotd.data_ptr(),
+                    ("u32", kv_heads), ("u32", head_dim), ("u32", rotary_dim), ("u32", block_size), float(eps), float(theta)])
+        torch.cuda.synchronize()
+        assert np.array_equal(got_k, bits_from_dev(kc_ref))                            # same bits as the reference
+
+    # K and V read in place from a fused QKV buffer: [tokens, q | k | v | pad]
+    q_w, pad = 3 * width, 24
+    stride = q_w + 2 * width + pad
+    qkv = torch.zeros((tokens, stride), dtype=torch.int16, device="cuda")
+    qkv[:, q_w:q_w + width].copy_(kd)
+    qkv[:, q_w + width:q_w + 2 * width].copy_(vd)
+    kc2, vc2 = cache(), cache()
+    atlas.kv_norm_rope_cache_write(qkv.data_ptr() + q_w * 2, qkv.data_ptr() + (q_w + width) * 2, stride, wd, posd, slotd, kc2, vc2,
+                                   tokens, kv_heads, head_dim, rotary_dim, block_size, eps, theta)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits_from_dev(kc2), got_k) and np.array_equal(bits_from_dev(vc2), got_v)
+
+    # the CPU oracle: equal, or next to it in the last BF16 bit
+    want = np.full((n_blocks, block_size, kv_heads, head_dim), FILL, dtype=np.uint16)
+    oracle.k_norm_rope_cache_write(k, width, w, pos, slots, want, kv_heads, head_dim, rotary_dim, block_size, eps, theta)
+    a, b = got_k[blk, off].astype(np.int32), want[blk, off].astype(np.int32)
+    assert np.abs(a - b).max() <= 1
+    assert (a != b).mean() < 0.02
+
+
+def test_shapes_the_kernel_does_not_take_are_refused(cuda, atlas):
+    torch = cuda
+    z = torch.zeros(4096, dtype=torch.int16, device="cuda")
+    pos = torch.zeros(4, dtype=torch.int32, device="cuda")
+    slot = torch.zeros(4, dtype=torch.int64, device="cuda")
+    for head_dim, rotary in ((48, 0), (128, 32), (512, 64), (128, 192)):
+        with pytest.raises(atlas.AtlasError) as e:
+            atlas.kv_norm_rope_cache_write(z, None, 1024, z, pos, slot, z, None, 4, 1, head_dim, rotary, 16, 1e-6, 1e4)
+        assert e.value.status == -1

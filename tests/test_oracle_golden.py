@@ -210,3 +210,34 @@ def test_staged_matches_fp32_ideal_within_tolerance(oracle):
             r = case.adapters[case.seq_slot[m]].rank
             assert not xa[m, r:].any()                                  # pad ranks come out zero
     assert np.abs(ideal - base).max() > 0.05                           # the LoRA term is visible in this case
+
+
+def test_k_norm_rope_cache_write_against_a_float64_formula(oracle):
+    """The oracle's K epilogue (RMS norm with (1 + w), rotary pairs (d, d + rotary_dim/2), paged write) against the textbook
+    formula in float64: within a BF16 rounding of it, skipped tokens untouched, slots mapped to [block, offset]."""
+    rng = np.random.default_rng(5)
+    tokens, kv_heads, hd, rot, bs, eps, theta = 9, 2, 128, 64, 4, 1e-6, 1.0e6
+    k = oracle.f32_to_bf16(rng.standard_normal((tokens, kv_heads * hd)).astype(np.float32) * 3)
+    w = oracle.f32_to_bf16((rng.standard_normal(hd) * 0.1).astype(np.float32))
+    pos = rng.integers(0, 5000, tokens).astype(np.uint32)
+    slots = np.array([5, 0, -1, 11, 2, 7, -1, 9, 3], dtype=np.int64)
+    cache = np.full((3, bs, kv_heads, hd), 0x7FC0, dtype=np.uint16)
+    oracle.k_norm_rope_cache_write(k, kv_heads * hd, w, pos, slots, cache, kv_heads, hd, rot, bs, eps, theta)
+    kf, wf = oracle.bf16_to_f32(k).astype(np.float64).reshape(tokens, kv_heads, hd), oracle.bf16_to_f32(w).astype(np.float64)
+    for t in range(tokens):
+        if slots[t] < 0:
+            continue
+        x = kf[t]
+        n = x / np.sqrt((x * x).mean(axis=1, keepdims=True) + eps) * (1.0 + wf)
+        out = n.copy()
+        half = rot // 2
+        ang = pos[t] * theta ** (-2.0 * np.arange(half) / rot)
+        out[:, :half] = n[:, :half] * np.cos(ang) - n[:, half:rot] * np.sin(ang)
+        out[:, half:rot] = n[:, half:rot] * np.cos(ang) + n[:, :half] * np.sin(ang)
+        got = oracle.bf16_to_f32(cache[slots[t] // bs, slots[t] % bs]).astype(np.float64)
+        assert np.abs(got - out).max() <= 2.0 ** -7 * np.abs(out).max() + 1e-3
+    written = {(int(s) // bs, int(s) % bs) for s in slots if s >= 0}
+    for b in range(3):
+        for o in range(bs):
+            if (b, o) not in written:
+                assert (cache[b, o] == 0x7FC0).all()
