@@ -1087,6 +1087,40 @@ int atlas_b200_kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint
     return launch_status();
 }
 
+int atlas_b200_qkv_norm_rope_cache_write(void* q, const void* k_in, const void* v_in, uint32_t q_row_stride, uint32_t kv_row_stride,
+                                         const void* q_norm_weight, const void* k_norm_weight, const uint32_t* positions,
+                                         const float* inv_freq, const long long* slot_mapping, void* k_cache, void* v_cache,
+                                         uint32_t tokens, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim, uint32_t rotary_dim,
+                                         uint32_t block_size, float rms_eps, float attention_factor, int norm_offset_one, void* stream) {
+    if (!q || !k_in || !v_in || !q_norm_weight || !k_norm_weight || !positions || !slot_mapping || !k_cache || !v_cache ||
+        (rotary_dim && !inv_freq))
+        return ATLAS_B200_ERR_NULL;
+    if (tokens == 0 || q_heads + kv_heads == 0) return ATLAS_B200_OK;
+    if (head_dim == 0 || head_dim % 2 || head_dim > uint32_t(KVE_MAX_HEAD_DIM) || rotary_dim > head_dim || rotary_dim % 2 ||
+        block_size == 0 || q_row_stride < q_heads * head_dim || kv_row_stride < kv_heads * head_dim)
+        return ATLAS_B200_ERR_DIMS;
+    // packed pairs are read as 32-bit words
+    if (!aligned(q, 4) || !aligned(k_in, 4) || !aligned(q_norm_weight, 4) || !aligned(k_norm_weight, 4) || q_row_stride % 2 || kv_row_stride % 2)
+        return ATLAS_B200_ERR_ALIGN;
+    QkvEpilogueParams p{};
+    p.q = static_cast<uint16_t*>(q);
+    p.k_in = static_cast<const uint16_t*>(k_in);
+    p.v_in = static_cast<const uint16_t*>(v_in);
+    p.q_norm_w = static_cast<const uint16_t*>(q_norm_weight);
+    p.k_norm_w = static_cast<const uint16_t*>(k_norm_weight);
+    p.positions = positions; p.inv_freq = inv_freq; p.slot_mapping = slot_mapping;
+    p.k_cache = static_cast<uint16_t*>(k_cache);
+    p.v_cache = static_cast<uint16_t*>(v_cache);
+    p.tokens = tokens; p.q_heads = q_heads; p.kv_heads = kv_heads; p.head_dim = head_dim; p.rotary_dim = rotary_dim;
+    p.block_size = block_size; p.q_row_stride = q_row_stride; p.kv_row_stride = kv_row_stride;
+    p.rms_eps = rms_eps; p.attention_factor = attention_factor; p.norm_offset_one = norm_offset_one ? 1u : 0u;
+    const uint64_t items = uint64_t(tokens) * (q_heads + 2u * kv_heads);
+    const uint64_t grid = (items + KVE_WARPS - 1) / KVE_WARPS;
+    if (grid > 0x7FFFFFFFull) return ATLAS_B200_ERR_LIMIT;
+    qkv_norm_rope_cache_kernel<<<uint32_t(grid), KVE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return launch_status();
+}
+
 int atlas_b200_copy_columns(const void* src, uint32_t src_row_stride, void* const* dest, uint32_t n_dest, uint32_t dst_row_stride,
                             uint32_t m, uint32_t n_cols, void* stream) {
     if (!src || (!dest && n_dest)) return ATLAS_B200_ERR_NULL;

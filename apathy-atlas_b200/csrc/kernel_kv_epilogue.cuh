@@ -114,4 +114,112 @@ kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
     }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// The decode-path consumer of the fused QKV projection, Q side included: per (token, head)
+//   Q head:  q = rope( bf16( rmsnorm(q) ) )  in place,
+//   K head:  the same chain, result into the paged K cache,
+//   V head:  copied into the paged V cache,
+// with the rounding points and the rotary form of the reference's `fused_qkv_norm_rope_cache_write_bf16`
+// (kernels/gb10/common/fused_verify_elemwise.cu:78-224): the normed head is rounded to BF16 before the rotation
+// (the chain it replaced stored it), the angle is position * inv_freq[pair] from a table, cosine and sine are scaled by
+// the attention factor (YaRN), and the weight is `w` or `1 + w`.  One warp per (token, head), Q, K and V read where the
+// projection wrote them (row strides given), the BF16 normed head staged in the warp's own shared-memory strip so that
+// a lane can read the partner element of its pair.
+//
+// Summation order of the reference (one block of head_dim threads, thread t squaring the packed pair (2t, 2t + 1), a
+// butterfly per warp, then a butterfly over the warp sums): group g of 64 elements = the reference's warp g, lane l of
+// the group = its thread 32 g + l.
+// ------------------------------------------------------------------------------------------------------------------
+struct QkvEpilogueParams {
+    uint16_t* q;                 // first Q column of token 0 (BF16, in/out), rows q_row_stride elements apart
+    const uint16_t* k_in;        // first K column of token 0, rows kv_row_stride apart
+    const uint16_t* v_in;
+    const uint16_t* q_norm_w;    // [head_dim]
+    const uint16_t* k_norm_w;    // [head_dim]
+    const uint32_t* positions;   // [tokens]
+    const float* inv_freq;       // [rotary_dim / 2]
+    const long long* slot_mapping;
+    uint16_t* k_cache;
+    uint16_t* v_cache;
+    uint32_t tokens, q_heads, kv_heads, head_dim, rotary_dim, block_size, q_row_stride, kv_row_stride;
+    float rms_eps, attention_factor;
+    uint32_t norm_offset_one;
+};
+
+__global__ void __launch_bounds__(KVE_WARPS * 32)
+qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
+    __shared__ uint16_t normed_s[KVE_WARPS][KVE_MAX_HEAD_DIM];
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t roles = p.q_heads + 2u * p.kv_heads;
+    const uint64_t item = uint64_t(blockIdx.x) * KVE_WARPS + warp;
+    if (item >= uint64_t(p.tokens) * roles) return;
+    const uint32_t token = uint32_t(item / roles), role = uint32_t(item - uint64_t(token) * roles);
+    const long long slot = p.slot_mapping[token];
+    const size_t cache_at = slot < 0 ? 0 : (size_t(slot / (long long)p.block_size) * p.block_size + size_t(slot % (long long)p.block_size)) *
+                                               (size_t(p.kv_heads) * p.head_dim);
+    if (role >= p.q_heads + p.kv_heads) {                                  // V: a copy
+        if (slot < 0) return;
+        const uint32_t head = role - p.q_heads - p.kv_heads;
+        const uint16_t* src = p.v_in + size_t(token) * p.kv_row_stride + size_t(head) * p.head_dim;
+        uint16_t* dst = p.v_cache + cache_at + size_t(head) * p.head_dim;
+        for (uint32_t d = lane; d < p.head_dim; d += 32) dst[d] = src[d];
+        return;
+    }
+    const bool is_q = role < p.q_heads;
+    const uint32_t head = is_q ? role : role - p.q_heads;
+    if (!is_q && slot < 0) return;                                         // (the reference computes and drops it)
+    uint16_t* qrow = p.q + size_t(token) * p.q_row_stride + size_t(head) * p.head_dim;
+    const uint16_t* x = is_q ? qrow : p.k_in + size_t(token) * p.kv_row_stride + size_t(head) * p.head_dim;
+    const uint16_t* w = is_q ? p.q_norm_w : p.k_norm_w;
+    const uint32_t n_grp = (p.head_dim + 63u) / 64u;                       // the reference's warps that hold data
+    constexpr uint32_t MAX_GRP = KVE_MAX_HEAD_DIM / 64;
+    float x0v[MAX_GRP], x1v[MAX_GRP];
+    float mine = 0.0f;
+#pragma unroll
+    for (uint32_t g = 0; g < MAX_GRP; ++g) {
+        if (g >= n_grp) continue;
+        const uint32_t e = 64u * g + 2u * lane;                            // this lane's packed pair of the group
+        float sq = 0.0f;
+        x0v[g] = x1v[g] = 0.0f;
+        if (e < p.head_dim) {
+            const uint32_t pk = *reinterpret_cast<const uint32_t*>(x + e);
+            x0v[g] = __uint_as_float(pk << 16);
+            x1v[g] = __uint_as_float(pk & 0xFFFF0000u);
+            sq = __fadd_rn(__fmul_rn(x0v[g], x0v[g]), __fmul_rn(x1v[g], x1v[g]));
+        }
+        const float s = kve_butterfly(sq);
+        if (lane == g) mine = s;
+    }
+    const float total = kve_butterfly(mine);
+    const float rms = rsqrtf(__fadd_rn(__fdiv_rn(total, float(p.head_dim)), p.rms_eps));
+#pragma unroll
+    for (uint32_t g = 0; g < MAX_GRP; ++g) {
+        if (g >= n_grp) continue;
+        const uint32_t e = 64u * g + 2u * lane;
+        if (e < p.head_dim) {
+            const uint32_t wk = *reinterpret_cast<const uint32_t*>(w + e);
+            const float w0 = __uint_as_float(wk << 16), w1 = __uint_as_float(wk & 0xFFFF0000u);
+            const float f0 = p.norm_offset_one ? __fadd_rn(1.0f, w0) : w0, f1 = p.norm_offset_one ? __fadd_rn(1.0f, w1) : w1;
+            normed_s[warp][e] = f32_to_bf16_bits(__fmul_rn(__fmul_rn(x0v[g], rms), f0));
+            normed_s[warp][e + 1] = f32_to_bf16_bits(__fmul_rn(__fmul_rn(x1v[g], rms), f1));
+        }
+    }
+    __syncwarp();
+    uint16_t* dst = is_q ? qrow : p.k_cache + cache_at + size_t(head) * p.head_dim;
+    const uint32_t pairs = p.rotary_dim / 2u;
+    const float pos = float(p.positions[token]);
+    for (uint32_t t = lane; t < p.head_dim; t += 32) {
+        if (t < pairs) {
+            const float a = __uint_as_float(uint32_t(normed_s[warp][t]) << 16);
+            const float b = __uint_as_float(uint32_t(normed_s[warp][t + pairs]) << 16);
+            const float angle = __fmul_rn(pos, p.inv_freq[t]);
+            const float c = __fmul_rn(cosf(angle), p.attention_factor), s = __fmul_rn(sinf(angle), p.attention_factor);
+            dst[t] = f32_to_bf16_bits(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)));
+            dst[t + pairs] = f32_to_bf16_bits(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s)));
+        } else if (t >= p.rotary_dim) {
+            dst[t] = normed_s[warp][t];                                    // channels beyond the rotary part pass through
+        }
+    }
+}
+
 }  // namespace atlas

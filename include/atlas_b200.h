@@ -149,6 +149,22 @@ ATLAS_B200_API int atlas_b200_kv_norm_rope_cache_write(const void* k_in, const v
                                         uint32_t tokens, uint32_t kv_heads, uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size,
                                         float rms_eps, float theta, void* stream);
 
+/* The decode-path consumer of the fused QKV projection, Q side included, one launch: per token and head
+ *   Q heads:  q = rope( bf16( rmsnorm(q) ) ) in place;   K heads: the same chain into k_cache at the token's paged slot;
+ *   V heads:  copied into v_cache.  Tokens with slot_mapping < 0 get their Q processed and write no cache.
+ * Replaces `fused_qkv_norm_rope_cache_write_bf16` (kernels/gb10/common/fused_verify_elemwise.cu:78-224) with its rounding
+ * points (the normed head is rounded to BF16 before the rotation), its rotary form (angle = position * inv_freq[pair] from a
+ * table of rotary_dim / 2 floats, cosine and sine multiplied by attention_factor, pairs (t, t + rotary_dim / 2)), its weight
+ * convention (norm_offset_one: 1 -> x * rms * (1 + w), 0 -> x * rms * w) and its summation order: same bits.  Unlike the
+ * reference, q / k_in / v_in point into the fused QKV output where the projection wrote it: first column of token 0 of each
+ * part, with row strides in elements (q_row_stride for q, kv_row_stride for k_in and v_in).
+ * head_dim and rotary_dim even, head_dim <= 256 (-1 otherwise); q, k_in and both strides 4-byte aligned (-3). */
+ATLAS_B200_API int atlas_b200_qkv_norm_rope_cache_write(void* q, const void* k_in, const void* v_in, uint32_t q_row_stride, uint32_t kv_row_stride,
+                                         const void* q_norm_weight, const void* k_norm_weight, const uint32_t* positions,
+                                         const float* inv_freq, const long long* slot_mapping, void* k_cache, void* v_cache,
+                                         uint32_t tokens, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim, uint32_t rotary_dim,
+                                         uint32_t block_size, float rms_eps, float attention_factor, int norm_offset_one, void* stream);
+
 /* First phase of the weight quantiser: *global_max (a device float the caller has zeroed) becomes max |in| over `total`
  * BF16 elements.  Replaces `nvfp4_global_absmax` (kernels/gb10/common/quantize_bf16_to_nvfp4.cu:131-167). */
 ATLAS_B200_API int atlas_b200_nvfp4_global_absmax(const void* in_bf16, float* global_max_dev, size_t total, void* stream);

@@ -651,3 +651,72 @@ void orc_k_norm_rope_cache_write(const uint16_t *k_in, size_t in_row_stride, con
         }
     }
 }
+
+/* The decode-path QKV consumer, kernels/gb10/common/fused_verify_elemwise.cu:78-224: per (token, head) the RMS norm with
+ * weight w or (1 + w) (:170-178), the normed head rounded to BF16 (:176-177), the rotation of the pairs (t, t + rotary_dim/2)
+ * by angle = position * inv_freq[t] with cosine and sine scaled by the attention factor (:186-194), Q back in place, K into
+ * the paged cache, V copied (:104-121).  Sum of squares in the reference's order: thread t squares the packed pair
+ * (2t, 2t + 1), butterfly per warp of 32 threads, butterfly over the warp sums (:139-163).  1/sqrtf, sinf, cosf are the
+ * host's (see orc_k_norm_rope_cache_write). */
+static void orc_norm_rope_head(const uint16_t *x, const uint16_t *w, uint32_t head_dim, uint32_t rotary_dim, float pos,
+                               const float *inv_freq, float eps, float factor, int offset_one, uint16_t *dst) {
+    float warp_sum[32];
+    for (int i = 0; i < 32; i++) warp_sum[i] = 0.0f;
+    uint32_t half = head_dim / 2, n_warps = (head_dim + 31) / 32;
+    for (uint32_t wi = 0; wi < n_warps && wi < 32; wi++) {
+        float v[32];
+        for (uint32_t l = 0; l < 32; l++) {
+            uint32_t t = wi * 32 + l;
+            if (t < half) {
+                float a = orc_bf16_to_f32(x[2 * t]), b = orc_bf16_to_f32(x[2 * t + 1]);
+                float aa = a * a, bb = b * b;
+                v[l] = aa + bb;
+            } else v[l] = 0.0f;
+        }
+        warp_sum[wi] = orc_butterfly32(v);
+    }
+    float total = orc_butterfly32(warp_sum);
+    float rms = 1.0f / sqrtf(total / (float)head_dim + eps);
+    uint16_t nb[256];
+    for (uint32_t d = 0; d < head_dim; d++) {
+        float wf = orc_bf16_to_f32(w[d]);
+        float weff = offset_one ? 1.0f + wf : wf;
+        float t1 = orc_bf16_to_f32(x[d]) * rms;
+        nb[d] = orc_f32_to_bf16(t1 * weff);
+    }
+    uint32_t pairs = rotary_dim / 2;
+    for (uint32_t t = 0; t < head_dim; t++) {
+        if (t < pairs) {
+            float a = orc_bf16_to_f32(nb[t]), b = orc_bf16_to_f32(nb[t + pairs]);
+            float angle = pos * inv_freq[t];
+            float c = cosf(angle) * factor, s = sinf(angle) * factor;
+            float ac = a * c, bs = b * s, bc = b * c, as = a * s;
+            dst[t] = orc_f32_to_bf16(ac - bs);
+            dst[t + pairs] = orc_f32_to_bf16(bc + as);
+        } else if (t >= rotary_dim) dst[t] = nb[t];
+    }
+}
+
+void orc_qkv_norm_rope_cache_write(uint16_t *q, size_t q_row_stride, const uint16_t *k_in, const uint16_t *v_in, size_t kv_row_stride,
+                                   const uint16_t *q_norm_w, const uint16_t *k_norm_w, const uint32_t *positions, const float *inv_freq,
+                                   const int64_t *slot_mapping, uint16_t *k_cache, uint16_t *v_cache, uint32_t tokens, uint32_t q_heads,
+                                   uint32_t kv_heads, uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size, float eps, float factor,
+                                   int offset_one) {
+    for (uint32_t t = 0; t < tokens; t++) {
+        float pos = (float)positions[t];
+        for (uint32_t h = 0; h < q_heads; h++) {
+            uint16_t *row = q + (size_t)t * q_row_stride + (size_t)h * head_dim;
+            uint16_t tmp[256];
+            memcpy(tmp, row, head_dim * 2);
+            orc_norm_rope_head(tmp, q_norm_w, head_dim, rotary_dim, pos, inv_freq, eps, factor, offset_one, row);
+        }
+        int64_t slot = slot_mapping[t];
+        if (slot < 0) continue;
+        size_t at = ((size_t)(slot / block_size) * block_size + (size_t)(slot % block_size)) * ((size_t)kv_heads * head_dim);
+        for (uint32_t h = 0; h < kv_heads; h++) {
+            orc_norm_rope_head(k_in + (size_t)t * kv_row_stride + (size_t)h * head_dim, k_norm_w, head_dim, rotary_dim, pos, inv_freq, eps,
+                               factor, offset_one, k_cache + at + (size_t)h * head_dim);
+            memcpy(v_cache + at + (size_t)h * head_dim, v_in + (size_t)t * kv_row_stride + (size_t)h * head_dim, head_dim * 2);
+        }
+    }
+}

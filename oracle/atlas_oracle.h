@@ -117,6 +117,11 @@ void orc_reference_sequence(const orc_fused_args *g, uint16_t *y, uint16_t *xa, 
 void orc_k_norm_rope_cache_write(const uint16_t *k_in, size_t in_row_stride, const uint16_t *k_norm_w, const uint32_t *positions,
                                  const int64_t *slot_mapping, uint16_t *k_cache, uint32_t tokens, uint32_t kv_heads,
                                  uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size, float rms_eps, float theta);
+void orc_qkv_norm_rope_cache_write(uint16_t *q, size_t q_row_stride, const uint16_t *k_in, const uint16_t *v_in, size_t kv_row_stride,
+                                   const uint16_t *q_norm_w, const uint16_t *k_norm_w, const uint32_t *positions, const float *inv_freq,
+                                   const int64_t *slot_mapping, uint16_t *k_cache, uint16_t *v_cache, uint32_t tokens, uint32_t q_heads,
+                                   uint32_t kv_heads, uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size, float eps, float factor,
+                                   int offset_one);
 void orc_silu_mul(const uint16_t *gate, const uint16_t *up, float *out_f32, float gate_scale, float up_scale, float limit, size_t total);
 void orc_quantize_f32_to_nvfp4_scale1(const float *in, uint8_t *packed, uint8_t *scales, uint32_t M, uint32_t K);
 int orc_num_threads(void);

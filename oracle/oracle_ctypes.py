@@ -91,6 +91,9 @@ def lib() -> C.CDLL:
         L.orc_reference_sequence.argtypes = [C.POINTER(FusedArgs), C.c_void_p, C.c_void_p, C.c_uint32]
         L.orc_num_threads.restype = C.c_int
         L.orc_silu_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_float, C.c_size_t]
+        L.orc_qkv_norm_rope_cache_write.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                                    C.c_uint32, C.c_uint32, C.c_float, C.c_float, C.c_int]
         L.orc_k_norm_rope_cache_write.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
                                                   C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float]
         L.orc_quantize_f32_to_nvfp4_scale1.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32]
@@ -263,6 +266,17 @@ def k_norm_rope_cache_write(k_in, in_row_stride, k_norm_w, positions, slot_mappi
     lib().orc_k_norm_rope_cache_write(_p(k_in), in_row_stride, _p(np.ascontiguousarray(k_norm_w)), _p(np.ascontiguousarray(positions, dtype=np.uint32)),
                                       _p(np.ascontiguousarray(slot_mapping, dtype=np.int64)), _p(k_cache), len(positions), kv_heads, head_dim,
                                       rotary_dim, block_size, rms_eps, theta)
+
+
+def qkv_norm_rope_cache_write(q, q_row_stride, k_in, v_in, kv_row_stride, q_norm_w, k_norm_w, positions, inv_freq, slot_mapping, k_cache, v_cache,
+                              q_heads, kv_heads, head_dim, rotary_dim, block_size, eps, factor=1.0, offset_one=True) -> None:
+    """In place on q (uint16 bits, [tokens, q_row_stride]) and on the two caches."""
+    assert q.flags["C_CONTIGUOUS"] and k_cache.flags["C_CONTIGUOUS"] and v_cache.flags["C_CONTIGUOUS"]
+    lib().orc_qkv_norm_rope_cache_write(_p(q), q_row_stride, _p(np.ascontiguousarray(k_in)), _p(np.ascontiguousarray(v_in)), kv_row_stride,
+                                        _p(np.ascontiguousarray(q_norm_w)), _p(np.ascontiguousarray(k_norm_w)),
+                                        _p(np.ascontiguousarray(positions, dtype=np.uint32)), _p(np.ascontiguousarray(inv_freq, dtype=np.float32)),
+                                        _p(np.ascontiguousarray(slot_mapping, dtype=np.int64)), _p(k_cache), _p(v_cache), len(positions),
+                                        q_heads, kv_heads, head_dim, rotary_dim, block_size, eps, factor, 1 if offset_one else 0)
 
 
 def silu_mul(gate, up, gate_scale=1.0, up_scale=1.0, limit=0.0) -> np.ndarray:

@@ -89,3 +89,64 @@ def test_shapes_the_kernel_does_not_take_are_refused(cuda, atlas):
         with pytest.raises(atlas.AtlasError) as e:
             atlas.kv_norm_rope_cache_write(z, None, 1024, z, pos, slot, z, None, 4, 1, head_dim, rotary, 16, 1e-6, 1e4)
         assert e.value.status == -1
+
+
+@pytest.mark.parametrize("head_dim,rotary_dim,offset_one,factor", [(128, 64, True, 1.0), (128, 128, False, 1.18), (256, 64, True, 1.0), (64, 32, True, 0.9)])
+def test_decode_qkv_norm_rope_cache_write(cuda, atlas, oracle, head_dim, rotary_dim, offset_one, factor):
+    """Q in place, K into the paged cache, V copied — against the reference's fused decode kernel
+    (kernels/gb10/common/fused_verify_elemwise.cu) bit for bit, in place on a strided fused QKV buffer, and against the
+    oracle."""
+    torch = cuda
+    tokens, q_heads, kv_heads, block_size, eps = 37, 6, 2, 16, 1e-6
+    k, v, wk, pos, slots, n_slots = _inputs(oracle, tokens, kv_heads, head_dim, 7 * head_dim + rotary_dim)
+    rng = np.random.default_rng(head_dim)
+    q = oracle.f32_to_bf16((rng.standard_normal((tokens, q_heads * head_dim)) * 4).astype(np.float32))
+    wq = oracle.f32_to_bf16((rng.standard_normal(head_dim) * (0.1 if offset_one else 1.0)).astype(np.float32))
+    if not offset_one:
+        wk = oracle.f32_to_bf16((rng.standard_normal(head_dim) + 1.0).astype(np.float32))
+    inv_freq = (1.0e6 ** (-2.0 * np.arange(rotary_dim // 2) / rotary_dim)).astype(np.float32)
+    n_blocks = (n_slots + block_size - 1) // block_size
+    qw, kw = q_heads * head_dim, kv_heads * head_dim
+    wqd, wkd, posd, slotd, fd = to_dev(torch, wq), to_dev(torch, wk), to_dev(torch, pos), torch.from_numpy(slots).cuda(), torch.from_numpy(inv_freq).cuda()
+
+    def cache():
+        return torch.full((n_blocks, block_size, kv_heads, head_dim), np.int16(np.uint16(FILL).view(np.int16)), dtype=torch.int16, device="cuda")
+
+    # the reference's kernel, contiguous q / k / v
+    ref = RefModule("fused_verify_elemwise")
+    q_ref, kd, vd = to_dev(torch, q), to_dev(torch, k), to_dev(torch, v)
+    kc_ref, vc_ref = cache(), cache()
+    ref.launch("fused_qkv_norm_rope_cache_write_bf16", (q_heads + 2 * kv_heads, tokens, 1), (head_dim, 1, 1),
+               [q_ref.data_ptr(), kd.data_ptr(), vd.data_ptr(), wqd.data_ptr(), wkd.data_ptr(), posd.data_ptr(), fd.data_ptr(),
+                kc_ref.data_ptr(), vc_ref.data_ptr(), slotd.data_ptr(), ("u32", q_heads), ("u32", kv_heads), ("u32", head_dim),
+                ("u32", rotary_dim), ("u32", block_size), float(eps), float(factor), ("u32", 1 if offset_one else 0)])
+    torch.cuda.synchronize()
+
+    # this library, in place on the fused buffer [tokens, q | k | v | pad]
+    stride = qw + 2 * kw + 40
+    qkv = torch.zeros((tokens, stride), dtype=torch.int16, device="cuda")
+    qkv[:, :qw].copy_(to_dev(torch, q)); qkv[:, qw:qw + kw].copy_(kd); qkv[:, qw + kw:qw + 2 * kw].copy_(vd)
+    kc, vc = cache(), cache()
+    atlas.qkv_norm_rope_cache_write(qkv.data_ptr(), qkv.data_ptr() + qw * 2, qkv.data_ptr() + (qw + kw) * 2, stride, stride, wqd, wkd, posd, fd,
+                                    slotd, kc, vc, tokens, q_heads, kv_heads, head_dim, rotary_dim, block_size, eps, factor, offset_one)
+    torch.cuda.synchronize()
+    got = bits_from_dev(qkv)
+    assert np.array_equal(got[:, :qw], bits_from_dev(q_ref))                            # Q: same bits as the reference
+    assert np.array_equal(bits_from_dev(kc), bits_from_dev(kc_ref))                     # K cache: same bits
+    assert np.array_equal(bits_from_dev(vc), bits_from_dev(vc_ref))
+    assert np.array_equal(got[:, qw:qw + 2 * kw], np.concatenate([k, v], axis=1))       # K and V inputs untouched
+    assert (got[:, qw + 2 * kw:] == 0).all()
+
+    # the oracle: equal, or a BF16 step or two away where its host-library rsqrt / sin / cos round the other way
+    q_o = q.copy()
+    kc_o = np.full((n_blocks, block_size, kv_heads, head_dim), FILL, dtype=np.uint16)
+    vc_o = kc_o.copy()
+    oracle.qkv_norm_rope_cache_write(q_o, qw, k, v, kw, wq, wk, pos, inv_freq, slots, kc_o, vc_o, q_heads, kv_heads, head_dim, rotary_dim,
+                                     block_size, eps, factor, offset_one)
+    assert np.array_equal(vc_o, bits_from_dev(vc))
+    for a, b in ((got[:, :qw], q_o), (bits_from_dev(kc), kc_o)):
+        fa, fb = oracle.bf16_to_f32(np.ascontiguousarray(a)), oracle.bf16_to_f32(np.ascontiguousarray(b))
+        live = np.isfinite(fb)
+        assert np.array_equal(np.isfinite(fa), live)
+        assert np.abs(fa[live] - fb[live]).max() <= 2.0 ** -6 * np.abs(fb[live]).max()
+        assert (a != b).mean() < 0.02

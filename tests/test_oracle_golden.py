@@ -241,3 +241,48 @@ def test_k_norm_rope_cache_write_against_a_float64_formula(oracle):
         for o in range(bs):
             if (b, o) not in written:
                 assert (cache[b, o] == 0x7FC0).all()
+
+
+def test_decode_qkv_epilogue_against_a_float64_formula(oracle):
+    """The oracle's decode-path QKV consumer: Q in place, K into the paged cache (normed head rounded to BF16, then rotated
+    by position * inv_freq with scaled cosine / sine), V copied — within BF16 roundings of the float64 formula."""
+    rng = np.random.default_rng(11)
+    tokens, nq, nkv, hd, rot, bs, eps, factor = 5, 3, 2, 64, 32, 4, 1e-6, 1.1
+    q = oracle.f32_to_bf16(rng.standard_normal((tokens, nq * hd)).astype(np.float32) * 2)
+    k = oracle.f32_to_bf16(rng.standard_normal((tokens, nkv * hd)).astype(np.float32) * 5)
+    v = oracle.f32_to_bf16(rng.standard_normal((tokens, nkv * hd)).astype(np.float32))
+    wq = oracle.f32_to_bf16((rng.standard_normal(hd) * 0.1).astype(np.float32))
+    wk = oracle.f32_to_bf16((rng.standard_normal(hd) * 0.1).astype(np.float32))
+    pos = np.array([0, 7, 100, 4095, 31], dtype=np.uint32)
+    inv_freq = (1.0e4 ** (-2.0 * np.arange(rot // 2) / rot)).astype(np.float32)
+    slots = np.array([2, -1, 0, 5, 7], dtype=np.int64)
+    kc = np.full((2, bs, nkv, hd), 0x7FC0, dtype=np.uint16)
+    vc = kc.copy()
+    q_out = q.copy()
+    oracle.qkv_norm_rope_cache_write(q_out, nq * hd, k, v, nkv * hd, wq, wk, pos, inv_freq, slots, kc, vc, nq, nkv, hd, rot, bs, eps, factor, True)
+
+    def chain(x, w, p):
+        x = x.astype(np.float64)
+        n = x / np.sqrt((x * x).mean() + eps) * (1.0 + w.astype(np.float64))
+        out = n.copy()
+        h = rot // 2
+        ang = p * inv_freq.astype(np.float64)
+        c, s = np.cos(ang) * factor, np.sin(ang) * factor
+        out[:h] = n[:h] * c - n[h:rot] * s
+        out[h:rot] = n[h:rot] * c + n[:h] * s
+        return out
+    qf, kf = oracle.bf16_to_f32(q).reshape(tokens, nq, hd), oracle.bf16_to_f32(k).reshape(tokens, nkv, hd)
+    wqf, wkf = oracle.bf16_to_f32(wq), oracle.bf16_to_f32(wk)
+    got_q = oracle.bf16_to_f32(q_out).reshape(tokens, nq, hd)
+    for t in range(tokens):
+        for h in range(nq):
+            want = chain(qf[t, h], wqf, float(pos[t]))
+            assert np.abs(got_q[t, h] - want).max() <= 2.0 ** -6 * np.abs(want).max() + 1e-3
+        if slots[t] < 0:
+            continue
+        b, o = slots[t] // bs, slots[t] % bs
+        assert np.array_equal(vc[b, o].reshape(-1), v[t])
+        for h in range(nkv):
+            want = chain(kf[t, h], wkf, float(pos[t]))
+            assert np.abs(oracle.bf16_to_f32(kc[b, o, h]) - want).max() <= 2.0 ** -6 * np.abs(want).max() + 1e-3
+    assert (kc[0, 1] == 0x7FC0).all() and (vc[0, 3] == 0x7FC0).all()          # slots nobody mapped stay as they were
