@@ -1061,8 +1061,8 @@ int atlas_b200_push_columns(const void* src, uint32_t src_row_stride, void* cons
     return launch_status();
 }
 
-int atlas_b200_kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint32_t in_row_stride, const void* k_norm_weight,
-                                        const uint32_t* positions, const long long* slot_mapping, void* k_cache, void* v_cache,
+static int kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint32_t in_row_stride, const void* k_norm_weight,
+                                    const uint32_t* positions, const uint32_t* positions_h, const uint32_t* positions_w, const long long* slot_mapping, void* k_cache, void* v_cache,
                                         uint32_t tokens, uint32_t kv_heads, uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size,
                                         float rms_eps, float theta, void* stream) {
     if (!k_in || !k_norm_weight || !positions || !slot_mapping || !k_cache || (v_in && !v_cache)) return ATLAS_B200_ERR_NULL;
@@ -1075,6 +1075,8 @@ int atlas_b200_kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint
     p.v_in = static_cast<const uint16_t*>(v_in);
     p.k_norm_w = static_cast<const uint16_t*>(k_norm_weight);
     p.positions = positions;
+    p.positions_h = positions_h;
+    p.positions_w = positions_w;
     p.slot_mapping = slot_mapping;
     p.k_cache = static_cast<uint16_t*>(k_cache);
     p.v_cache = static_cast<uint16_t*>(v_cache);
@@ -1085,6 +1087,23 @@ int atlas_b200_kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint
     if (grid > 0x7FFFFFFFull) return ATLAS_B200_ERR_LIMIT;
     kv_norm_rope_cache_kernel<<<uint32_t(grid), KVE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
     return launch_status();
+}
+
+int atlas_b200_kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint32_t in_row_stride, const void* k_norm_weight,
+                                        const uint32_t* positions, const long long* slot_mapping, void* k_cache, void* v_cache,
+                                        uint32_t tokens, uint32_t kv_heads, uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size,
+                                        float rms_eps, float theta, void* stream) {
+    return kv_norm_rope_cache_write(k_in, v_in, in_row_stride, k_norm_weight, positions, nullptr, nullptr, slot_mapping, k_cache, v_cache, tokens,
+                                    kv_heads, head_dim, rotary_dim, block_size, rms_eps, theta, stream);
+}
+
+int atlas_b200_kv_norm_mrope_cache_write(const void* k_in, const void* v_in, uint32_t in_row_stride, const void* k_norm_weight,
+                                         const uint32_t* pos_t, const uint32_t* pos_h, const uint32_t* pos_w, const long long* slot_mapping,
+                                         void* k_cache, void* v_cache, uint32_t tokens, uint32_t kv_heads, uint32_t head_dim,
+                                         uint32_t rotary_dim, uint32_t block_size, float rms_eps, float theta, void* stream) {
+    if (!pos_h || !pos_w) return ATLAS_B200_ERR_NULL;
+    return kv_norm_rope_cache_write(k_in, v_in, in_row_stride, k_norm_weight, pos_t, pos_h, pos_w, slot_mapping, k_cache, v_cache, tokens,
+                                    kv_heads, head_dim, rotary_dim, block_size, rms_eps, theta, stream);
 }
 
 int atlas_b200_qkv_norm_rope_cache_write(void* q, const void* k_in, const void* v_in, uint32_t q_row_stride, uint32_t kv_row_stride,

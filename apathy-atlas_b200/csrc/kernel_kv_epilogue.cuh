@@ -1,8 +1,9 @@
 // The K/V consumer of a fused QKV projection:  K heads go through the per-head RMS norm (Qwen3's "(1 + w)" form),
 // rotary embedding and ONE rounding to BF16 into the paged K cache; V heads are copied into the paged V cache.
 //
-// The reference does the K side in `fused_k_norm_rope_cache_write_bf16`
-// (kernels/gb10/common/fused_k_norm_rope_cache.cu:60-141: one block of head_dim threads per (token, head), K taken
+// The reference does the K side in `fused_k_norm_rope_cache_write_bf16` and, with three position streams (MRoPE: rotary
+// pair p takes the temporal, height or width position by p mod 3), `fused_k_norm_rope_mrope_cache_write_bf16`
+// (kernels/gb10/common/fused_k_norm_rope_cache.cu:60-141, :149-243: one block of head_dim threads per (token, head), K taken
 // from a contiguous [tokens, kv_heads, head_dim] copy) and the V side with a separate cache-write launch.  Here one
 // launch covers both and reads K and V where the projection left them — column ranges of the fused QKV output, with
 // its row stride — so no contiguous copies are made.  One warp owns one (token, head): lane l holds elements l, l+32,
@@ -29,6 +30,8 @@ struct KvEpilogueParams {
     const uint16_t* v_in;        // first V column of token 0, or nullptr: K side only
     const uint16_t* k_norm_w;    // [head_dim] BF16
     const uint32_t* positions;   // [tokens]
+    const uint32_t* positions_h; // MRoPE: the height and width position streams (pair p takes stream p mod 3: t, h, w), or both nullptr
+    const uint32_t* positions_w;
     const long long* slot_mapping;   // [tokens], < 0: token skipped
     uint16_t* k_cache;           // [blocks, block_size, kv_heads, head_dim] BF16
     uint16_t* v_cache;           // same layout, or nullptr
@@ -86,7 +89,8 @@ kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
             nrm[j] = __fmul_rn(__fmul_rn(x[j], rms), __fadd_rn(1.0f, w));
         }
     const uint32_t half = p.rotary_dim / 2u, half_grp = half / 32u;        // rotary_dim: a multiple of 64
-    const float pos = float(p.positions[token]);
+    const float pos_t = float(p.positions[token]);
+    const float pos_h = p.positions_h ? float(p.positions_h[token]) : pos_t, pos_w = p.positions_w ? float(p.positions_w[token]) : pos_t;
     uint16_t* dst = p.k_cache + dst_at;
 #pragma unroll
     for (uint32_t j = 0; j < uint32_t(KVE_MAX_HEAD_DIM / 32); ++j) {
@@ -106,7 +110,8 @@ kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
             }
             const double freq_exp = double(2u * pair) / double(p.rotary_dim);
             const float freq = float(1.0 / pow(double(p.theta), freq_exp));
-            const float angle = __fmul_rn(pos, freq);
+            const uint32_t section = pair % 3u;                            // (all three are the token's position without MRoPE)
+            const float angle = __fmul_rn(section == 0u ? pos_t : (section == 1u ? pos_h : pos_w), freq);
             const float c = cosf(angle), s = sinf(angle);
             out = low ? __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)) : __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
         }

@@ -149,6 +149,14 @@ ATLAS_B200_API int atlas_b200_kv_norm_rope_cache_write(const void* k_in, const v
                                         uint32_t tokens, uint32_t kv_heads, uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size,
                                         float rms_eps, float theta, void* stream);
 
+/* The same with three position streams (MRoPE): rotary pair p is rotated by the temporal, height or width position for
+ * p mod 3 = 0, 1, 2.  Replaces `fused_k_norm_rope_mrope_cache_write_bf16` (fused_k_norm_rope_cache.cu:149-243); with
+ * pos_h == pos_w == pos_t the result equals atlas_b200_kv_norm_rope_cache_write's. */
+ATLAS_B200_API int atlas_b200_kv_norm_mrope_cache_write(const void* k_in, const void* v_in, uint32_t in_row_stride, const void* k_norm_weight,
+                                         const uint32_t* pos_t, const uint32_t* pos_h, const uint32_t* pos_w, const long long* slot_mapping,
+                                         void* k_cache, void* v_cache, uint32_t tokens, uint32_t kv_heads, uint32_t head_dim,
+                                         uint32_t rotary_dim, uint32_t block_size, float rms_eps, float theta, void* stream);
+
 /* The decode-path consumer of the fused QKV projection, Q side included, one launch: per token and head
  *   Q heads:  q = rope( bf16( rmsnorm(q) ) ) in place;   K heads: the same chain into k_cache at the token's paged slot;
  *   V heads:  copied into v_cache.  Tokens with slot_mapping < 0 get their Q processed and write no cache.

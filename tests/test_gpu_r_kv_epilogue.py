@@ -150,3 +150,34 @@ def test_decode_qkv_norm_rope_cache_write(cuda, atlas, oracle, head_dim, rotary_
         assert np.array_equal(np.isfinite(fa), live)
         assert np.abs(fa[live] - fb[live]).max() <= 2.0 ** -6 * np.abs(fb[live]).max()
         assert (a != b).mean() < 0.02
+
+
+def test_k_norm_mrope_cache_write(cuda, atlas, oracle):
+    """Three position streams (MRoPE): rotary pair p takes the temporal, height or width position for p mod 3 = 0, 1, 2 —
+    bit for bit the reference's `fused_k_norm_rope_mrope_cache_write_bf16`; with equal streams, the scalar-position result."""
+    torch = cuda
+    tokens, kv_heads, head_dim, rotary_dim, block_size, eps, theta = 203, 2, 128, 64, 16, 1e-6, 1.0e7
+    k, v, w, pos, slots, n_slots = _inputs(oracle, tokens, kv_heads, head_dim, 99)
+    rng = np.random.default_rng(3)
+    pos_h, pos_w = rng.integers(0, 4096, tokens).astype(np.uint32), rng.integers(0, 4096, tokens).astype(np.uint32)
+    n_blocks = (n_slots + block_size - 1) // block_size
+    width = kv_heads * head_dim
+    kd, wd, slotd = to_dev(torch, k), to_dev(torch, w), torch.from_numpy(slots).cuda()
+    pt, ph, pw = to_dev(torch, pos), to_dev(torch, pos_h), to_dev(torch, pos_w)
+
+    def cache():
+        return torch.full((n_blocks, block_size, kv_heads, head_dim), np.int16(np.uint16(FILL).view(np.int16)), dtype=torch.int16, device="cuda")
+    kc, kc_ref, kc_same, kc_scalar = cache(), cache(), cache(), cache()
+    atlas.kv_norm_rope_cache_write(kd, None, width, wd, pt, slotd, kc, None, tokens, kv_heads, head_dim, rotary_dim, block_size, eps, theta,
+                                   positions_h=ph, positions_w=pw)
+    RefModule("fused_k_norm_rope_cache").launch(
+        "fused_k_norm_rope_mrope_cache_write_bf16", (tokens, kv_heads, 1), (head_dim, 1, 1),
+        [kd.data_ptr(), wd.data_ptr(), pt.data_ptr(), ph.data_ptr(), pw.data_ptr(), kc_ref.data_ptr(), slotd.data_ptr(),
+         ("u32", kv_heads), ("u32", head_dim), ("u32", rotary_dim), ("u32", block_size), float(eps), float(theta)])
+    atlas.kv_norm_rope_cache_write(kd, None, width, wd, pt, slotd, kc_same, None, tokens, kv_heads, head_dim, rotary_dim, block_size, eps, theta,
+                                   positions_h=pt, positions_w=pt)
+    atlas.kv_norm_rope_cache_write(kd, None, width, wd, pt, slotd, kc_scalar, None, tokens, kv_heads, head_dim, rotary_dim, block_size, eps, theta)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits_from_dev(kc), bits_from_dev(kc_ref))
+    assert np.array_equal(bits_from_dev(kc_same), bits_from_dev(kc_scalar))
+    assert not np.array_equal(bits_from_dev(kc), bits_from_dev(kc_scalar))
