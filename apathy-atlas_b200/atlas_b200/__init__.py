@@ -41,7 +41,7 @@ EXPORTS = (
     "atlas_b200_lora_bgmv", "atlas_b200_lora_delta", "atlas_b200_w4a16_gemm",
     "atlas_b200_dequant_nvfp4_to_bf16", "atlas_b200_quantize_bf16_to_nvfp4", "atlas_b200_nvfp4_global_absmax",
     "atlas_b200_nvfp4_scale2_from_absmax", "atlas_b200_nvfp4_combined_global_scale", "atlas_b200_silu_mul",
-    "atlas_b200_silu_mul_quant_nvfp4", "atlas_b200_kv_norm_rope_cache_write", "atlas_b200_kv_norm_mrope_cache_write", "atlas_b200_qkv_norm_rope_cache_write",
+    "atlas_b200_silu_mul_quant_nvfp4", "atlas_b200_kv_norm_rope_cache_write", "atlas_b200_kv_norm_mrope_cache_write", "atlas_b200_k_norm_rope_cache_write_fp8", "atlas_b200_qkv_norm_rope_cache_write",
     "atlas_b200_nvfp4_lora_linear", "atlas_b200_nvfp4_lora_linear_noalloc", "atlas_b200_lora_shrink_tiles",
     "atlas_b200_push_columns", "atlas_b200_copy_columns", "atlas_b200_selftest_bounded_wait", "atlas_b200_column_shard",
     "atlas_b200_build_seq_slot", "atlas_b200_routed_prefill_slot_of", "atlas_b200_peft_scaling",
@@ -123,6 +123,7 @@ def lib() -> C.CDLL:
     L.atlas_b200_nvfp4_lora_linear_noalloc.argtypes = [C.POINTER(LinearDesc), vp]
     L.atlas_b200_kv_norm_rope_cache_write.argtypes = [vp, vp, u32, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, f32, f32, vp]
     L.atlas_b200_kv_norm_mrope_cache_write.argtypes = [vp, vp, u32, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, f32, f32, vp]
+    L.atlas_b200_k_norm_rope_cache_write_fp8.argtypes = [vp, u32, vp, vp, vp, vp, u32, u32, u32, u32, u32, f32, f32, f32, vp]
     L.atlas_b200_qkv_norm_rope_cache_write.argtypes = [vp, vp, vp, u32, u32, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, f32, f32,
                                                        C.c_int, vp]
     L.atlas_b200_lora_shrink_tiles.argtypes = [C.POINTER(LinearDesc), u32, u32, C.POINTER(vp), u32, vp]
@@ -352,6 +353,14 @@ def kv_norm_rope_cache_write(k_in, v_in, in_row_stride: int, k_norm_weight, posi
     _check("atlas_b200_kv_norm_rope_cache_write", lib().atlas_b200_kv_norm_rope_cache_write(
         _ptr(k_in), _ptr(v_in), in_row_stride, _ptr(k_norm_weight), _ptr(positions), _ptr(slot_mapping), _ptr(k_cache),
         _ptr(v_cache), tokens, kv_heads, head_dim, rotary_dim, block_size, rms_eps, theta, _stream_ptr(stream)))
+
+
+def k_norm_rope_cache_write_fp8(k_in, in_row_stride: int, k_norm_weight, positions, slot_mapping, k_cache_fp8, tokens: int, kv_heads: int,
+                                head_dim: int, rotary_dim: int, block_size: int, rms_eps: float, theta: float, inv_scale: float, stream=None) -> None:
+    """The K side into an E4M3 paged cache (one byte per element): value * inv_scale, saturating cast."""
+    _check("atlas_b200_k_norm_rope_cache_write_fp8", lib().atlas_b200_k_norm_rope_cache_write_fp8(
+        _ptr(k_in), in_row_stride, _ptr(k_norm_weight), _ptr(positions), _ptr(slot_mapping), _ptr(k_cache_fp8), tokens, kv_heads, head_dim,
+        rotary_dim, block_size, rms_eps, theta, inv_scale, _stream_ptr(stream)))
 
 
 def qkv_norm_rope_cache_write(q, k_in, v_in, q_row_stride: int, kv_row_stride: int, q_norm_weight, k_norm_weight, positions, inv_freq,

@@ -1064,7 +1064,7 @@ int atlas_b200_push_columns(const void* src, uint32_t src_row_stride, void* cons
 static int kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint32_t in_row_stride, const void* k_norm_weight,
                                     const uint32_t* positions, const uint32_t* positions_h, const uint32_t* positions_w, const long long* slot_mapping, void* k_cache, void* v_cache,
                                         uint32_t tokens, uint32_t kv_heads, uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size,
-                                        float rms_eps, float theta, void* stream) {
+                                        float rms_eps, float theta, void* stream, float fp8_inv_scale = 0.0f) {
     if (!k_in || !k_norm_weight || !positions || !slot_mapping || !k_cache || (v_in && !v_cache)) return ATLAS_B200_ERR_NULL;
     if (tokens == 0 || kv_heads == 0) return ATLAS_B200_OK;
     if (head_dim == 0 || head_dim % 32 || head_dim > uint32_t(KVE_MAX_HEAD_DIM) || rotary_dim > head_dim || rotary_dim % 64 ||
@@ -1081,7 +1081,7 @@ static int kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint32_t
     p.k_cache = static_cast<uint16_t*>(k_cache);
     p.v_cache = static_cast<uint16_t*>(v_cache);
     p.tokens = tokens; p.kv_heads = kv_heads; p.head_dim = head_dim; p.rotary_dim = rotary_dim; p.block_size = block_size;
-    p.in_row_stride = in_row_stride; p.rms_eps = rms_eps; p.theta = theta;
+    p.in_row_stride = in_row_stride; p.rms_eps = rms_eps; p.theta = theta; p.fp8_inv_scale = fp8_inv_scale;
     const uint64_t items = uint64_t(tokens) * kv_heads * (v_in ? 2u : 1u);
     const uint64_t grid = (items + KVE_WARPS - 1) / KVE_WARPS;
     if (grid > 0x7FFFFFFFull) return ATLAS_B200_ERR_LIMIT;
@@ -1095,6 +1095,15 @@ int atlas_b200_kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint
                                         float rms_eps, float theta, void* stream) {
     return kv_norm_rope_cache_write(k_in, v_in, in_row_stride, k_norm_weight, positions, nullptr, nullptr, slot_mapping, k_cache, v_cache, tokens,
                                     kv_heads, head_dim, rotary_dim, block_size, rms_eps, theta, stream);
+}
+
+int atlas_b200_k_norm_rope_cache_write_fp8(const void* k_in, uint32_t in_row_stride, const void* k_norm_weight, const uint32_t* positions,
+                                           const long long* slot_mapping, void* k_cache_fp8, uint32_t tokens, uint32_t kv_heads,
+                                           uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size, float rms_eps, float theta,
+                                           float inv_scale, void* stream) {
+    if (!(inv_scale > 0.0f)) return ATLAS_B200_ERR_DIMS;
+    return kv_norm_rope_cache_write(k_in, nullptr, in_row_stride, k_norm_weight, positions, nullptr, nullptr, slot_mapping, k_cache_fp8, nullptr,
+                                    tokens, kv_heads, head_dim, rotary_dim, block_size, rms_eps, theta, stream, inv_scale);
 }
 
 int atlas_b200_kv_norm_mrope_cache_write(const void* k_in, const void* v_in, uint32_t in_row_stride, const void* k_norm_weight,

@@ -3,7 +3,8 @@
 //
 // The reference does the K side in `fused_k_norm_rope_cache_write_bf16` and, with three position streams (MRoPE: rotary
 // pair p takes the temporal, height or width position by p mod 3), `fused_k_norm_rope_mrope_cache_write_bf16`
-// (kernels/gb10/common/fused_k_norm_rope_cache.cu:60-141, :149-243: one block of head_dim threads per (token, head), K taken
+// (kernels/gb10/common/fused_k_norm_rope_cache.cu:60-141, :149-243; `fused_k_norm_rope_cache_write_fp8`, :253-338, is the
+// same chain ending in value * inv_scale cast to E4M3 with saturation: one block of head_dim threads per (token, head), K taken
 // from a contiguous [tokens, kv_heads, head_dim] copy) and the V side with a separate cache-write launch.  Here one
 // launch covers both and reads K and V where the projection left them — column ranges of the fused QKV output, with
 // its row stride — so no contiguous copies are made.  One warp owns one (token, head): lane l holds elements l, l+32,
@@ -16,6 +17,7 @@
 #pragma once
 
 #include <cstdint>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include "common.cuh"
@@ -37,6 +39,7 @@ struct KvEpilogueParams {
     uint16_t* v_cache;           // same layout, or nullptr
     uint32_t tokens, kv_heads, head_dim, rotary_dim, block_size, in_row_stride;
     float rms_eps, theta;
+    float fp8_inv_scale;         // != 0: k_cache is an E4M3 cache (one byte per element): value * fp8_inv_scale, saturating cast
 };
 
 __device__ __forceinline__ float kve_butterfly(float v) {
@@ -92,6 +95,8 @@ kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
     const float pos_t = float(p.positions[token]);
     const float pos_h = p.positions_h ? float(p.positions_h[token]) : pos_t, pos_w = p.positions_w ? float(p.positions_w[token]) : pos_t;
     uint16_t* dst = p.k_cache + dst_at;
+    uint8_t* dst8 = reinterpret_cast<uint8_t*>(p.k_cache) + dst_at;
+    const bool fp8 = p.fp8_inv_scale != 0.0f;
 #pragma unroll
     for (uint32_t j = 0; j < uint32_t(KVE_MAX_HEAD_DIM / 32); ++j) {
         if (j >= n_grp) continue;
@@ -115,7 +120,8 @@ kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
             const float c = cosf(angle), s = sinf(angle);
             out = low ? __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)) : __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
         }
-        dst[d] = f32_to_bf16_bits(out);
+        if (fp8) dst8[d] = uint8_t(__nv_cvt_float_to_fp8(__fmul_rn(out, p.fp8_inv_scale), __NV_SATFINITE, __NV_E4M3));
+        else dst[d] = f32_to_bf16_bits(out);
     }
 }
 

@@ -157,6 +157,13 @@ ATLAS_B200_API int atlas_b200_kv_norm_mrope_cache_write(const void* k_in, const 
                                          void* k_cache, void* v_cache, uint32_t tokens, uint32_t kv_heads, uint32_t head_dim,
                                          uint32_t rotary_dim, uint32_t block_size, float rms_eps, float theta, void* stream);
 
+/* The K side into an FP8 (E4M3) paged cache, one byte per element: the same chain, then value * inv_scale cast with
+ * saturation.  Replaces `fused_k_norm_rope_cache_write_fp8` (fused_k_norm_rope_cache.cu:253-338). */
+ATLAS_B200_API int atlas_b200_k_norm_rope_cache_write_fp8(const void* k_in, uint32_t in_row_stride, const void* k_norm_weight, const uint32_t* positions,
+                                           const long long* slot_mapping, void* k_cache_fp8, uint32_t tokens, uint32_t kv_heads,
+                                           uint32_t head_dim, uint32_t rotary_dim, uint32_t block_size, float rms_eps, float theta,
+                                           float inv_scale, void* stream);
+
 /* The decode-path consumer of the fused QKV projection, Q side included, one launch: per token and head
  *   Q heads:  q = rope( bf16( rmsnorm(q) ) ) in place;   K heads: the same chain into k_cache at the token's paged slot;
  *   V heads:  copied into v_cache.  Tokens with slot_mapping < 0 get their Q processed and write no cache.

@@ -181,3 +181,27 @@ def test_k_norm_mrope_cache_write(cuda, atlas, oracle):
     assert np.array_equal(bits_from_dev(kc), bits_from_dev(kc_ref))
     assert np.array_equal(bits_from_dev(kc_same), bits_from_dev(kc_scalar))
     assert not np.array_equal(bits_from_dev(kc), bits_from_dev(kc_scalar))
+
+
+def test_k_norm_rope_cache_write_fp8(cuda, atlas, oracle):
+    """The K side into an E4M3 paged cache: bit for bit the reference's `fused_k_norm_rope_cache_write_fp8`, values beyond the
+    format's range saturating at +-448."""
+    torch = cuda
+    tokens, kv_heads, head_dim, rotary_dim, block_size, eps, theta, inv_scale = 157, 2, 128, 64, 16, 1e-6, 1.0e6, 200.0
+    k, v, w, pos, slots, n_slots = _inputs(oracle, tokens, kv_heads, head_dim, 5)
+    n_blocks = (n_slots + block_size - 1) // block_size
+    width = kv_heads * head_dim
+    kd, wd, posd, slotd = to_dev(torch, k), to_dev(torch, w), to_dev(torch, pos), torch.from_numpy(slots).cuda()
+    c8, c8_ref = [torch.full((n_blocks, block_size, kv_heads, head_dim), 0x55, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    atlas.k_norm_rope_cache_write_fp8(kd, width, wd, posd, slotd, c8, tokens, kv_heads, head_dim, rotary_dim, block_size, eps, theta, inv_scale)
+    RefModule("fused_k_norm_rope_cache").launch(
+        "fused_k_norm_rope_cache_write_fp8", (tokens, kv_heads, 1), (head_dim, 1, 1),
+        [kd.data_ptr(), wd.data_ptr(), posd.data_ptr(), c8_ref.data_ptr(), slotd.data_ptr(), ("u32", kv_heads), ("u32", head_dim),
+         ("u32", rotary_dim), ("u32", block_size), float(eps), float(theta), float(inv_scale)])
+    torch.cuda.synchronize()
+    got, ref = c8.cpu().numpy(), c8_ref.cpu().numpy()
+    assert np.array_equal(got, ref)
+    live = slots >= 0
+    written = got[slots[live] // block_size, slots[live] % block_size]
+    assert ((written & 0x7F) == 0x7E).any()                 # normed magnitudes reach 3-4, times 200: some saturate at 448
+    assert not ((written & 0x7F) == 0x7F).any()             # and none becomes the NaN byte
