@@ -1082,10 +1082,7 @@ static int kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint32_t
     p.v_cache = static_cast<uint16_t*>(v_cache);
     p.tokens = tokens; p.kv_heads = kv_heads; p.head_dim = head_dim; p.rotary_dim = rotary_dim; p.block_size = block_size;
     p.in_row_stride = in_row_stride; p.rms_eps = rms_eps; p.theta = theta; p.fp8_inv_scale = fp8_inv_scale;
-    const uint64_t items = uint64_t(tokens) * kv_heads * (v_in ? 2u : 1u);
-    const uint64_t grid = (items + KVE_WARPS - 1) / KVE_WARPS;
-    if (grid > 0x7FFFFFFFull) return ATLAS_B200_ERR_LIMIT;
-    kv_norm_rope_cache_kernel<<<uint32_t(grid), KVE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    kv_norm_rope_cache_kernel<<<(tokens + KVE_TOKENS - 1) / KVE_TOKENS, KVE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
     return launch_status();
 }
 
@@ -1128,7 +1125,8 @@ int atlas_b200_qkv_norm_rope_cache_write(void* q, const void* k_in, const void* 
         block_size == 0 || q_row_stride < q_heads * head_dim || kv_row_stride < kv_heads * head_dim)
         return ATLAS_B200_ERR_DIMS;
     // packed pairs are read as 32-bit words
-    if (!aligned(q, 4) || !aligned(k_in, 4) || !aligned(q_norm_weight, 4) || !aligned(k_norm_weight, 4) || q_row_stride % 2 || kv_row_stride % 2)
+    if (!aligned(q, 4) || !aligned(k_in, 4) || !aligned(v_in, 4) || !aligned(v_cache, 4) || !aligned(q_norm_weight, 4) ||
+        !aligned(k_norm_weight, 4) || q_row_stride % 2 || kv_row_stride % 2)
         return ATLAS_B200_ERR_ALIGN;
     QkvEpilogueParams p{};
     p.q = static_cast<uint16_t*>(q);
@@ -1142,10 +1140,7 @@ int atlas_b200_qkv_norm_rope_cache_write(void* q, const void* k_in, const void* 
     p.tokens = tokens; p.q_heads = q_heads; p.kv_heads = kv_heads; p.head_dim = head_dim; p.rotary_dim = rotary_dim;
     p.block_size = block_size; p.q_row_stride = q_row_stride; p.kv_row_stride = kv_row_stride;
     p.rms_eps = rms_eps; p.attention_factor = attention_factor; p.norm_offset_one = norm_offset_one ? 1u : 0u;
-    const uint64_t items = uint64_t(tokens) * (q_heads + 2u * kv_heads);
-    const uint64_t grid = (items + KVE_WARPS - 1) / KVE_WARPS;
-    if (grid > 0x7FFFFFFFull) return ATLAS_B200_ERR_LIMIT;
-    qkv_norm_rope_cache_kernel<<<uint32_t(grid), KVE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    qkv_norm_rope_cache_kernel<<<tokens, KVE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
     return launch_status();
 }
 

@@ -24,7 +24,7 @@
 
 namespace atlas {
 
-constexpr int KVE_WARPS = 8;                 // (token, head) pairs per CTA
+constexpr int KVE_WARPS = 8;                 // warps per CTA (one CTA per token, its heads dealt out to the warps)
 constexpr int KVE_MAX_HEAD_DIM = 256;
 
 struct KvEpilogueParams {
@@ -48,80 +48,119 @@ __device__ __forceinline__ float kve_butterfly(float v) {
     return v;
 }
 
+constexpr int KVE_TOKENS = 8;                // tokens per CTA (prefill form)
+constexpr int KVE_INFLIGHT = 4;              // heads a warp has loaded before it starts on the first of them
+
 __global__ void __launch_bounds__(KVE_WARPS * 32)
 kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
+    // One CTA per KVE_TOKENS tokens.  The rotation's frequency depends on the pair only and its cosine and sine on
+    // (token, pair) only, so the FP64 power is evaluated once per CTA and pair, the two transcendental calls once per
+    // token and pair — the reference evaluates all three per element — and every head reads them from shared memory.
+    // Same calls on the same arguments: same bits.  The op is a stream; what limits it is the latency of a head's chain
+    // (load, two butterflies, rsqrt, store), so a warp loads KVE_INFLIGHT heads before it works on the first.
+    __shared__ float cos_s[KVE_TOKENS][KVE_MAX_HEAD_DIM / 2], sin_s[KVE_TOKENS][KVE_MAX_HEAD_DIM / 2];
+    __shared__ float freq_s[KVE_MAX_HEAD_DIM / 2];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-    const uint32_t heads_all = p.kv_heads * (p.v_in ? 2u : 1u);           // K heads, then V heads
-    const uint64_t item = uint64_t(blockIdx.x) * KVE_WARPS + warp;
-    if (item >= uint64_t(p.tokens) * heads_all) return;
-    const uint32_t token = uint32_t(item / heads_all), h = uint32_t(item - uint64_t(token) * heads_all);
-    const long long slot = p.slot_mapping[token];
-    if (slot < 0) return;                                                  // padding token
-    const bool is_v = h >= p.kv_heads;
-    const uint32_t head = is_v ? h - p.kv_heads : h;
-    const uint32_t n_grp = p.head_dim / 32u;                               // elements per lane (head_dim: a multiple of 32, <= 256)
-    const uint16_t* src = (is_v ? p.v_in : p.k_in) + size_t(token) * p.in_row_stride + size_t(head) * p.head_dim;
-    const size_t dst_at = (size_t(slot / (long long)p.block_size) * p.block_size + size_t(slot % (long long)p.block_size)) *
-                              (size_t(p.kv_heads) * p.head_dim) + size_t(head) * p.head_dim;
-    if (is_v) {
-        uint16_t* dst = p.v_cache + dst_at;
-        for (uint32_t j = 0; j < n_grp; ++j) dst[lane + 32u * j] = src[lane + 32u * j];
-        return;
-    }
-    float x[KVE_MAX_HEAD_DIM / 32];
-    float grp[KVE_MAX_HEAD_DIM / 32];
-#pragma unroll
-    for (uint32_t j = 0; j < uint32_t(KVE_MAX_HEAD_DIM / 32); ++j) {
-        if (j < n_grp) {
-            x[j] = __uint_as_float(uint32_t(src[lane + 32u * j]) << 16);
-            grp[j] = kve_butterfly(__fmul_rn(x[j], x[j]));                 // sum over elements 32 j .. 32 j + 31
-        }
-    }
-    // the group sums as lanes 0 .. n_grp-1 of one more butterfly
-    float mine = 0.0f;
-#pragma unroll
-    for (uint32_t j = 0; j < uint32_t(KVE_MAX_HEAD_DIM / 32); ++j)
-        if (j < n_grp && lane == j) mine = grp[j];
-    const float total = kve_butterfly(mine);
-    const float rms = rsqrtf(__fadd_rn(__fdiv_rn(total, float(p.head_dim)), p.rms_eps));
-    float nrm[KVE_MAX_HEAD_DIM / 32] = {};
-#pragma unroll
-    for (uint32_t j = 0; j < uint32_t(KVE_MAX_HEAD_DIM / 32); ++j)
-        if (j < n_grp) {
-            const float w = __uint_as_float(uint32_t(p.k_norm_w[lane + 32u * j]) << 16);
-            nrm[j] = __fmul_rn(__fmul_rn(x[j], rms), __fadd_rn(1.0f, w));
-        }
+    const uint32_t token0 = blockIdx.x * KVE_TOKENS;
+    const uint32_t n_tok = min(uint32_t(KVE_TOKENS), p.tokens - token0);
     const uint32_t half = p.rotary_dim / 2u, half_grp = half / 32u;        // rotary_dim: a multiple of 64
-    const float pos_t = float(p.positions[token]);
-    const float pos_h = p.positions_h ? float(p.positions_h[token]) : pos_t, pos_w = p.positions_w ? float(p.positions_w[token]) : pos_t;
-    uint16_t* dst = p.k_cache + dst_at;
-    uint8_t* dst8 = reinterpret_cast<uint8_t*>(p.k_cache) + dst_at;
+    for (uint32_t pair = threadIdx.x; pair < half; pair += KVE_WARPS * 32) {
+        const double freq_exp = double(2u * pair) / double(p.rotary_dim);
+        freq_s[pair] = float(1.0 / pow(double(p.theta), freq_exp));
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < n_tok * half; i += KVE_WARPS * 32) {
+        const uint32_t tk = i / half, pair = i - tk * half;
+        const uint32_t section = pair % 3u;                                // MRoPE: temporal / height / width stream by pair
+        const uint32_t* ps = (section == 0u || !p.positions_h) ? p.positions : (section == 1u ? p.positions_h : p.positions_w);
+        const float angle = __fmul_rn(float(ps[token0 + tk]), freq_s[pair]);
+        cos_s[tk][pair] = cosf(angle);
+        sin_s[tk][pair] = sinf(angle);
+    }
+    __syncthreads();
+    const uint32_t heads_all = p.kv_heads * (p.v_in ? 2u : 1u);           // K heads, then V heads
+    const uint32_t n_grp = p.head_dim / 32u;                               // elements per lane (head_dim: a multiple of 32, <= 256)
+    const uint32_t n_items = n_tok * heads_all;
     const bool fp8 = p.fp8_inv_scale != 0.0f;
+    constexpr uint32_t NG = KVE_MAX_HEAD_DIM / 32;
+    for (uint32_t base = warp; base < n_items; base += KVE_WARPS * KVE_INFLIGHT) {
+        uint16_t raw[KVE_INFLIGHT][NG];
+        long long slot_r[KVE_INFLIGHT];
 #pragma unroll
-    for (uint32_t j = 0; j < uint32_t(KVE_MAX_HEAD_DIM / 32); ++j) {
-        if (j >= n_grp) continue;
-        const uint32_t d = lane + 32u * j;
-        float out = nrm[j];
-        if (d < p.rotary_dim) {
-            const bool low = d < half;
-            const uint32_t pair = low ? d : d - half;
-            // the pair's two elements are in this lane: groups j and j +- half / 32 (constant indices keep them in registers)
-            const uint32_t j0 = low ? j : j - half_grp, j1 = low ? j + half_grp : j;
-            float x0 = 0.0f, x1 = 0.0f;
+        for (uint32_t r = 0; r < uint32_t(KVE_INFLIGHT); ++r) {
+            const uint32_t item = base + r * KVE_WARPS;
+            slot_r[r] = -1;
+            if (item >= n_items) continue;
+            const uint32_t tk = item / heads_all, h = item - tk * heads_all;
+            slot_r[r] = p.slot_mapping[token0 + tk];
+            if (slot_r[r] < 0) continue;                                   // padding token
+            const bool is_v = h >= p.kv_heads;
+            const uint16_t* src = (is_v ? p.v_in : p.k_in) + size_t(token0 + tk) * p.in_row_stride + size_t(is_v ? h - p.kv_heads : h) * p.head_dim;
 #pragma unroll
-            for (uint32_t q = 0; q < uint32_t(KVE_MAX_HEAD_DIM / 32); ++q) {
-                if (q == j0) x0 = nrm[q];
-                if (q == j1) x1 = nrm[q];
-            }
-            const double freq_exp = double(2u * pair) / double(p.rotary_dim);
-            const float freq = float(1.0 / pow(double(p.theta), freq_exp));
-            const uint32_t section = pair % 3u;                            // (all three are the token's position without MRoPE)
-            const float angle = __fmul_rn(section == 0u ? pos_t : (section == 1u ? pos_h : pos_w), freq);
-            const float c = cosf(angle), s = sinf(angle);
-            out = low ? __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)) : __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+            for (uint32_t j = 0; j < NG; ++j)
+                if (j < n_grp) raw[r][j] = src[lane + 32u * j];
         }
-        if (fp8) dst8[d] = uint8_t(__nv_cvt_float_to_fp8(__fmul_rn(out, p.fp8_inv_scale), __NV_SATFINITE, __NV_E4M3));
-        else dst[d] = f32_to_bf16_bits(out);
+#pragma unroll
+        for (uint32_t r = 0; r < uint32_t(KVE_INFLIGHT); ++r) {
+            const uint32_t item = base + r * KVE_WARPS;
+            if (item >= n_items || slot_r[r] < 0) continue;               // (warp-uniform)
+            const uint32_t tk = item / heads_all, h = item - tk * heads_all;
+            const bool is_v = h >= p.kv_heads;
+            const uint32_t head = is_v ? h - p.kv_heads : h;
+            const long long slot = slot_r[r];
+            const size_t dst_at = (size_t(slot / (long long)p.block_size) * p.block_size + size_t(slot % (long long)p.block_size)) *
+                                      (size_t(p.kv_heads) * p.head_dim) + size_t(head) * p.head_dim;
+            if (is_v) {
+                uint16_t* dst = p.v_cache + dst_at;
+#pragma unroll
+                for (uint32_t j = 0; j < NG; ++j)
+                    if (j < n_grp) dst[lane + 32u * j] = raw[r][j];
+                continue;
+            }
+            float x[NG];
+            float mine = 0.0f;
+#pragma unroll
+            for (uint32_t j = 0; j < NG; ++j) {
+                if (j < n_grp) {
+                    x[j] = __uint_as_float(uint32_t(raw[r][j]) << 16);
+                    const float g = kve_butterfly(__fmul_rn(x[j], x[j]));     // sum over elements 32 j .. 32 j + 31
+                    if (lane == j) mine = g;                                   // the group sums as lanes 0 .. n_grp-1 of one more butterfly
+                }
+            }
+            const float total = kve_butterfly(mine);
+            const float rms = rsqrtf(__fadd_rn(__fdiv_rn(total, float(p.head_dim)), p.rms_eps));
+            float nrm[NG] = {};
+#pragma unroll
+            for (uint32_t j = 0; j < NG; ++j)
+                if (j < n_grp) {
+                    const float w = __uint_as_float(uint32_t(p.k_norm_w[lane + 32u * j]) << 16);
+                    nrm[j] = __fmul_rn(__fmul_rn(x[j], rms), __fadd_rn(1.0f, w));
+                }
+            uint16_t* dst = p.k_cache + dst_at;
+            uint8_t* dst8 = reinterpret_cast<uint8_t*>(p.k_cache) + dst_at;
+#pragma unroll
+            for (uint32_t j = 0; j < NG; ++j) {
+                if (j >= n_grp) continue;
+                const uint32_t d = lane + 32u * j;
+                float out = nrm[j];
+                if (d < p.rotary_dim) {
+                    const bool low = d < half;
+                    const uint32_t pair = low ? d : d - half;
+                    // the pair's two elements are in this lane: groups j and j +- half / 32 (constant indices keep them in registers)
+                    const uint32_t j0 = low ? j : j - half_grp, j1 = low ? j + half_grp : j;
+                    float x0 = 0.0f, x1 = 0.0f;
+#pragma unroll
+                    for (uint32_t q = 0; q < NG; ++q) {
+                        if (q == j0) x0 = nrm[q];
+                        if (q == j1) x1 = nrm[q];
+                    }
+                    const float c = cos_s[tk][pair], s = sin_s[tk][pair];
+                    out = low ? __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)) : __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+                }
+                if (fp8) dst8[d] = uint8_t(__nv_cvt_float_to_fp8(__fmul_rn(out, p.fp8_inv_scale), __NV_SATFINITE, __NV_E4M3));
+                else dst[d] = f32_to_bf16_bits(out);
+            }
+        }
     }
 }
 
@@ -159,76 +198,98 @@ struct QkvEpilogueParams {
 
 __global__ void __launch_bounds__(KVE_WARPS * 32)
 qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
+    // one CTA per token; cosine and sine of the token's angles evaluated once for all its heads (see above)
     __shared__ uint16_t normed_s[KVE_WARPS][KVE_MAX_HEAD_DIM];
+    __shared__ float cos_s[KVE_MAX_HEAD_DIM / 2], sin_s[KVE_MAX_HEAD_DIM / 2];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t token = blockIdx.x;
+    const uint32_t pairs = p.rotary_dim / 2u;
+    {
+        const float pos = float(p.positions[token]);
+        for (uint32_t t = threadIdx.x; t < pairs; t += KVE_WARPS * 32) {
+            const float angle = __fmul_rn(pos, p.inv_freq[t]);
+            cos_s[t] = __fmul_rn(cosf(angle), p.attention_factor);
+            sin_s[t] = __fmul_rn(sinf(angle), p.attention_factor);
+        }
+    }
+    __syncthreads();
     const uint32_t roles = p.q_heads + 2u * p.kv_heads;
-    const uint64_t item = uint64_t(blockIdx.x) * KVE_WARPS + warp;
-    if (item >= uint64_t(p.tokens) * roles) return;
-    const uint32_t token = uint32_t(item / roles), role = uint32_t(item - uint64_t(token) * roles);
     const long long slot = p.slot_mapping[token];
     const size_t cache_at = slot < 0 ? 0 : (size_t(slot / (long long)p.block_size) * p.block_size + size_t(slot % (long long)p.block_size)) *
                                                (size_t(p.kv_heads) * p.head_dim);
-    if (role >= p.q_heads + p.kv_heads) {                                  // V: a copy
-        if (slot < 0) return;
-        const uint32_t head = role - p.q_heads - p.kv_heads;
-        const uint16_t* src = p.v_in + size_t(token) * p.kv_row_stride + size_t(head) * p.head_dim;
-        uint16_t* dst = p.v_cache + cache_at + size_t(head) * p.head_dim;
-        for (uint32_t d = lane; d < p.head_dim; d += 32) dst[d] = src[d];
-        return;
-    }
-    const bool is_q = role < p.q_heads;
-    const uint32_t head = is_q ? role : role - p.q_heads;
-    if (!is_q && slot < 0) return;                                         // (the reference computes and drops it)
-    uint16_t* qrow = p.q + size_t(token) * p.q_row_stride + size_t(head) * p.head_dim;
-    const uint16_t* x = is_q ? qrow : p.k_in + size_t(token) * p.kv_row_stride + size_t(head) * p.head_dim;
-    const uint16_t* w = is_q ? p.q_norm_w : p.k_norm_w;
     const uint32_t n_grp = (p.head_dim + 63u) / 64u;                       // the reference's warps that hold data
     constexpr uint32_t MAX_GRP = KVE_MAX_HEAD_DIM / 64;
-    float x0v[MAX_GRP], x1v[MAX_GRP];
-    float mine = 0.0f;
+    for (uint32_t base = warp; base < roles; base += KVE_WARPS * KVE_INFLIGHT) {
+        // the packed pairs of KVE_INFLIGHT heads first (Q, K or V alike), then the work on each
+        uint32_t raw[KVE_INFLIGHT][MAX_GRP];
 #pragma unroll
-    for (uint32_t g = 0; g < MAX_GRP; ++g) {
-        if (g >= n_grp) continue;
-        const uint32_t e = 64u * g + 2u * lane;                            // this lane's packed pair of the group
-        float sq = 0.0f;
-        x0v[g] = x1v[g] = 0.0f;
-        if (e < p.head_dim) {
-            const uint32_t pk = *reinterpret_cast<const uint32_t*>(x + e);
-            x0v[g] = __uint_as_float(pk << 16);
-            x1v[g] = __uint_as_float(pk & 0xFFFF0000u);
-            sq = __fadd_rn(__fmul_rn(x0v[g], x0v[g]), __fmul_rn(x1v[g], x1v[g]));
-        }
-        const float s = kve_butterfly(sq);
-        if (lane == g) mine = s;
-    }
-    const float total = kve_butterfly(mine);
-    const float rms = rsqrtf(__fadd_rn(__fdiv_rn(total, float(p.head_dim)), p.rms_eps));
+        for (uint32_t r = 0; r < uint32_t(KVE_INFLIGHT); ++r) {
+            const uint32_t role = base + r * KVE_WARPS;
+            if (role >= roles || (role >= p.q_heads && slot < 0)) continue;
+            const uint16_t* x = role < p.q_heads ? p.q + size_t(token) * p.q_row_stride + size_t(role) * p.head_dim
+                              : (role < p.q_heads + p.kv_heads ? p.k_in + size_t(token) * p.kv_row_stride + size_t(role - p.q_heads) * p.head_dim
+                                                               : p.v_in + size_t(token) * p.kv_row_stride + size_t(role - p.q_heads - p.kv_heads) * p.head_dim);
 #pragma unroll
-    for (uint32_t g = 0; g < MAX_GRP; ++g) {
-        if (g >= n_grp) continue;
-        const uint32_t e = 64u * g + 2u * lane;
-        if (e < p.head_dim) {
-            const uint32_t wk = *reinterpret_cast<const uint32_t*>(w + e);
-            const float w0 = __uint_as_float(wk << 16), w1 = __uint_as_float(wk & 0xFFFF0000u);
-            const float f0 = p.norm_offset_one ? __fadd_rn(1.0f, w0) : w0, f1 = p.norm_offset_one ? __fadd_rn(1.0f, w1) : w1;
-            normed_s[warp][e] = f32_to_bf16_bits(__fmul_rn(__fmul_rn(x0v[g], rms), f0));
-            normed_s[warp][e + 1] = f32_to_bf16_bits(__fmul_rn(__fmul_rn(x1v[g], rms), f1));
+            for (uint32_t g = 0; g < MAX_GRP; ++g) {
+                const uint32_t e = 64u * g + 2u * lane;
+                raw[r][g] = (g < n_grp && e < p.head_dim) ? *reinterpret_cast<const uint32_t*>(x + e) : 0u;
+            }
         }
-    }
-    __syncwarp();
-    uint16_t* dst = is_q ? qrow : p.k_cache + cache_at + size_t(head) * p.head_dim;
-    const uint32_t pairs = p.rotary_dim / 2u;
-    const float pos = float(p.positions[token]);
-    for (uint32_t t = lane; t < p.head_dim; t += 32) {
-        if (t < pairs) {
-            const float a = __uint_as_float(uint32_t(normed_s[warp][t]) << 16);
-            const float b = __uint_as_float(uint32_t(normed_s[warp][t + pairs]) << 16);
-            const float angle = __fmul_rn(pos, p.inv_freq[t]);
-            const float c = __fmul_rn(cosf(angle), p.attention_factor), s = __fmul_rn(sinf(angle), p.attention_factor);
-            dst[t] = f32_to_bf16_bits(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)));
-            dst[t + pairs] = f32_to_bf16_bits(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s)));
-        } else if (t >= p.rotary_dim) {
-            dst[t] = normed_s[warp][t];                                    // channels beyond the rotary part pass through
+#pragma unroll
+        for (uint32_t r = 0; r < uint32_t(KVE_INFLIGHT); ++r) {
+            const uint32_t role = base + r * KVE_WARPS;
+            if (role >= roles || (role >= p.q_heads && slot < 0)) continue;          // (the reference computes a padding token's K and drops it)
+            if (role >= p.q_heads + p.kv_heads) {                                    // V: a copy
+                uint16_t* dst = p.v_cache + cache_at + size_t(role - p.q_heads - p.kv_heads) * p.head_dim;
+#pragma unroll
+                for (uint32_t g = 0; g < MAX_GRP; ++g) {
+                    const uint32_t e = 64u * g + 2u * lane;
+                    if (g < n_grp && e < p.head_dim) *reinterpret_cast<uint32_t*>(dst + e) = raw[r][g];
+                }
+                continue;
+            }
+            const bool is_q = role < p.q_heads;
+            const uint32_t head = is_q ? role : role - p.q_heads;
+            const uint16_t* w = is_q ? p.q_norm_w : p.k_norm_w;
+            float x0v[MAX_GRP], x1v[MAX_GRP];
+            float mine = 0.0f;
+#pragma unroll
+            for (uint32_t g = 0; g < MAX_GRP; ++g) {
+                if (g >= n_grp) continue;
+                x0v[g] = __uint_as_float(raw[r][g] << 16);
+                x1v[g] = __uint_as_float(raw[r][g] & 0xFFFF0000u);
+                const float s = kve_butterfly(__fadd_rn(__fmul_rn(x0v[g], x0v[g]), __fmul_rn(x1v[g], x1v[g])));
+                if (lane == g) mine = s;
+            }
+            const float total = kve_butterfly(mine);
+            const float rms = rsqrtf(__fadd_rn(__fdiv_rn(total, float(p.head_dim)), p.rms_eps));
+            __syncwarp();                                                  // the strip's previous head has been read
+#pragma unroll
+            for (uint32_t g = 0; g < MAX_GRP; ++g) {
+                if (g >= n_grp) continue;
+                const uint32_t e = 64u * g + 2u * lane;
+                if (e < p.head_dim) {
+                    const uint32_t wk = *reinterpret_cast<const uint32_t*>(w + e);
+                    const float w0 = __uint_as_float(wk << 16), w1 = __uint_as_float(wk & 0xFFFF0000u);
+                    const float f0 = p.norm_offset_one ? __fadd_rn(1.0f, w0) : w0, f1 = p.norm_offset_one ? __fadd_rn(1.0f, w1) : w1;
+                    normed_s[warp][e] = f32_to_bf16_bits(__fmul_rn(__fmul_rn(x0v[g], rms), f0));
+                    normed_s[warp][e + 1] = f32_to_bf16_bits(__fmul_rn(__fmul_rn(x1v[g], rms), f1));
+                }
+            }
+            __syncwarp();
+            uint16_t* dst = is_q ? p.q + size_t(token) * p.q_row_stride + size_t(head) * p.head_dim
+                                 : p.k_cache + cache_at + size_t(head) * p.head_dim;
+            for (uint32_t t = lane; t < p.head_dim; t += 32) {
+                if (t < pairs) {
+                    const float a = __uint_as_float(uint32_t(normed_s[warp][t]) << 16);
+                    const float b = __uint_as_float(uint32_t(normed_s[warp][t + pairs]) << 16);
+                    const float c = cos_s[t], s = sin_s[t];
+                    dst[t] = f32_to_bf16_bits(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)));
+                    dst[t + pairs] = f32_to_bf16_bits(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s)));
+                } else if (t >= p.rotary_dim) {
+                    dst[t] = normed_s[warp][t];                            // channels beyond the rotary part pass through
+                }
+            }
         }
     }
 }
