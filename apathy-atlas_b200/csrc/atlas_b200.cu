@@ -1082,7 +1082,11 @@ static int kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint32_t
     p.v_cache = static_cast<uint16_t*>(v_cache);
     p.tokens = tokens; p.kv_heads = kv_heads; p.head_dim = head_dim; p.rotary_dim = rotary_dim; p.block_size = block_size;
     p.in_row_stride = in_row_stride; p.rms_eps = rms_eps; p.theta = theta; p.fp8_inv_scale = fp8_inv_scale;
-    kv_norm_rope_cache_kernel<<<(tokens + KVE_TOKENS - 1) / KVE_TOKENS, KVE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    const dim3 grid((tokens + KVE_TOKENS - 1) / KVE_TOKENS), block(KVE_WARPS * 32);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (head_dim <= 64) kv_norm_rope_cache_kernel<2><<<grid, block, 0, st>>>(p);
+    else if (head_dim <= 128) kv_norm_rope_cache_kernel<4><<<grid, block, 0, st>>>(p);
+    else kv_norm_rope_cache_kernel<8><<<grid, block, 0, st>>>(p);
     return launch_status();
 }
 
@@ -1140,7 +1144,10 @@ int atlas_b200_qkv_norm_rope_cache_write(void* q, const void* k_in, const void* 
     p.tokens = tokens; p.q_heads = q_heads; p.kv_heads = kv_heads; p.head_dim = head_dim; p.rotary_dim = rotary_dim;
     p.block_size = block_size; p.q_row_stride = q_row_stride; p.kv_row_stride = kv_row_stride;
     p.rms_eps = rms_eps; p.attention_factor = attention_factor; p.norm_offset_one = norm_offset_one ? 1u : 0u;
-    qkv_norm_rope_cache_kernel<<<tokens, KVE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (head_dim <= 64) qkv_norm_rope_cache_kernel<1><<<tokens, KVE_WARPS * 32, 0, st>>>(p);
+    else if (head_dim <= 128) qkv_norm_rope_cache_kernel<2><<<tokens, KVE_WARPS * 32, 0, st>>>(p);
+    else qkv_norm_rope_cache_kernel<4><<<tokens, KVE_WARPS * 32, 0, st>>>(p);
     return launch_status();
 }
 

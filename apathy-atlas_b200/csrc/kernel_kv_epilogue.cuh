@@ -51,6 +51,8 @@ __device__ __forceinline__ float kve_butterfly(float v) {
 constexpr int KVE_TOKENS = 8;                // tokens per CTA (prefill form)
 constexpr int KVE_INFLIGHT = 4;              // heads a warp has loaded before it starts on the first of them
 
+// NG: head_dim / 32 rounded up to 2, 4 or 8 (register arrays sized for the head at hand)
+template <uint32_t NG>
 __global__ void __launch_bounds__(KVE_WARPS * 32)
 kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
     // One CTA per KVE_TOKENS tokens.  The rotation's frequency depends on the pair only and its cosine and sine on
@@ -82,7 +84,6 @@ kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
     const uint32_t n_grp = p.head_dim / 32u;                               // elements per lane (head_dim: a multiple of 32, <= 256)
     const uint32_t n_items = n_tok * heads_all;
     const bool fp8 = p.fp8_inv_scale != 0.0f;
-    constexpr uint32_t NG = KVE_MAX_HEAD_DIM / 32;
     for (uint32_t base = warp; base < n_items; base += KVE_WARPS * KVE_INFLIGHT) {
         uint16_t raw[KVE_INFLIGHT][NG];
         long long slot_r[KVE_INFLIGHT];
@@ -196,6 +197,8 @@ struct QkvEpilogueParams {
     uint32_t norm_offset_one;
 };
 
+// MAX_GRP: head_dim / 64 rounded up to 1, 2 or 4
+template <uint32_t MAX_GRP>
 __global__ void __launch_bounds__(KVE_WARPS * 32)
 qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
     // one CTA per token; cosine and sine of the token's angles evaluated once for all its heads (see above)
@@ -218,7 +221,6 @@ qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
     const size_t cache_at = slot < 0 ? 0 : (size_t(slot / (long long)p.block_size) * p.block_size + size_t(slot % (long long)p.block_size)) *
                                                (size_t(p.kv_heads) * p.head_dim);
     const uint32_t n_grp = (p.head_dim + 63u) / 64u;                       // the reference's warps that hold data
-    constexpr uint32_t MAX_GRP = KVE_MAX_HEAD_DIM / 64;
     for (uint32_t base = warp; base < roles; base += KVE_WARPS * KVE_INFLIGHT) {
         // the packed pairs of KVE_INFLIGHT heads first (Q, K or V alike), then the work on each
         uint32_t raw[KVE_INFLIGHT][MAX_GRP];
