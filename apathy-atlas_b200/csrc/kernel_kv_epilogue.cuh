@@ -7,7 +7,7 @@
 // same chain ending in value * inv_scale cast to E4M3 with saturation: one block of head_dim threads per (token, head), K taken
 // from a contiguous [tokens, kv_heads, head_dim] copy) and the V side with a separate cache-write launch.  Here one
 // launch covers both and reads K and V where the projection left them — column ranges of the fused QKV output, with
-// its row stride — so no contiguous copies are made.  One warp owns one (token, head): lane l holds elements l, l+32,
+// its row stride — so no contiguous copies are made.  One warp works on one (token, head) at a time: lane l holds elements l, l+32,
 // l+64, ... of the head, so the sum of squares needs only shuffles and, for rotary_dim a multiple of 64, both
 // elements of every rotated pair (d, d + rotary_dim/2) sit in the same lane.
 //
@@ -24,7 +24,7 @@
 
 namespace atlas {
 
-constexpr int KVE_WARPS = 8;                 // warps per CTA (one CTA per token, its heads dealt out to the warps)
+constexpr int KVE_WARPS = 8;                 // warps per CTA; the (token, head) items of a CTA are dealt out to them
 constexpr int KVE_MAX_HEAD_DIM = 256;
 
 struct KvEpilogueParams {
