@@ -320,6 +320,61 @@ def run_lora_bgmv(args, torch, ab, work, dw, outs, out_stride, flush):
     print(json.dumps(line), flush=True)
 
 
+def run_qkv_epilogue(args, form):
+    """The consumers of the fused QKV projection on the Llama-3-8B shape of the default workload (8192 tokens, 32 Q + 8 KV
+    heads of 128, rotary 64, pages of 16): `prefill` = K norm + RoPE + paged K cache write and V cache write
+    (atlas_b200_kv_norm_rope_cache_write); `decode` = Q norm + RoPE in place, K into the cache, V copied
+    (atlas_b200_qkv_norm_rope_cache_write).  K and V (and Q) are read in place from [tokens, q | k | v] buffers; six sets of
+    buffers (600 MB) are rotated so that no launch finds its input in L2.  One GPU."""
+    import torch
+    import atlas_b200 as ab
+    torch.cuda.set_device(0)
+    tokens, nq, nkv, hd, rot, bs, n_set = 8192, 32, 8, 128, 64, 16, 6
+    stride = (nq + 2 * nkv) * hd
+    g = torch.Generator(device="cuda").manual_seed(1)
+    qkv = [torch.randn((tokens, stride), device="cuda", generator=g).to(torch.bfloat16) for _ in range(n_set)]
+    wq = (torch.randn(hd, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    wk = (torch.randn(hd, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    pos = torch.arange(tokens, dtype=torch.int32, device="cuda")
+    slot = torch.arange(tokens, dtype=torch.int64, device="cuda")
+    inv_freq = torch.tensor((1e6 ** (-2.0 * np.arange(rot // 2) / rot)).astype(np.float32), device="cuda")
+    caches = [(torch.empty((tokens // bs, bs, nkv, hd), dtype=torch.bfloat16, device="cuda"),
+               torch.empty((tokens // bs, bs, nkv, hd), dtype=torch.bfloat16, device="cuda")) for _ in range(n_set)]
+    stream = torch.cuda.current_stream()
+
+    def step(i):
+        b, (kc, vc) = qkv[i % n_set], caches[i % n_set]
+        k_at, v_at = b.data_ptr() + nq * hd * 2, b.data_ptr() + (nq + nkv) * hd * 2
+        if form == "prefill":
+            ab.kv_norm_rope_cache_write(k_at, v_at, stride, wk, pos, slot, kc, vc, tokens, nkv, hd, rot, bs, 1e-6, 1e6, stream)
+        else:
+            ab.qkv_norm_rope_cache_write(b.data_ptr(), k_at, v_at, stride, stride, wq, wk, pos, inv_freq, slot, kc, vc, tokens, nq, nkv, hd, rot,
+                                         bs, 1e-6, 1.0, True, stream)
+    for i in range(max(args.warmup, n_set)):
+        step(i)
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for i, (a, b) in enumerate(ev):
+        a.record(stream)
+        step(i)
+        b.record(stream)
+    torch.cuda.synchronize()
+    ms = float(np.mean([a.elapsed_time(b) for a, b in ev]))
+    hbm_gbs, _, _, peak_kind = peaks()
+    # bytes: K and V read and written once (prefill form); Q read and written in place as well (decode form)
+    byts = float(tokens * hd * 2 * (4 * nkv + (2 * nq if form == "decode" else 0)))
+    kernel = "kv_norm_rope_cache_kernel" if form == "prefill" else "qkv_norm_rope_cache_kernel"
+    print(json.dumps({"metric": f"QKV consumer ({form} form) tokens/s", "op": f"qkv_epilogue_{form}", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16",
+                      "data": "synthetic",
+                      "config": {"workload": "qkv-epilogue", "tokens": tokens, "q_heads": nq, "kv_heads": nkv, "head_dim": hd, "rotary_dim": rot,
+                                 "block_size": bs, "l2": f"{n_set} buffer sets rotated (600 MB)"},
+                      "roofline": {"bound": "hbm", "achieved": byts / (ms * 1e-3) / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                                   "frac": byts / (ms * 1e-3) / 1e9 / hbm_gbs, "peak_kind": f"{peak_kind} HBM copy", "algorithmic_bytes": byts,
+                                   "kernel": kernel},
+                      "gpu_launches": args.steps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -336,9 +391,10 @@ def main():
                          "tile), copy where it is a single wave of tiles; nccl = all-gather after each projection")
     ap.add_argument("--activations", default="bf16", choices=["bf16", "fp4"],
                     help="bf16: the layer as specified (exact activations); fp4: the opt-in W4A4 mode as the timed step")
-    ap.add_argument("--op", default="fused", choices=["fused", "lora_bgmv"],
+    ap.add_argument("--op", default="fused", choices=["fused", "lora_bgmv", "qkv_epilogue_prefill", "qkv_epilogue_decode"],
                     help="fused: the fused layer (the benchmark); lora_bgmv: the routed LoRA op alone (shrink + expand/fold in place, "
-                         "the reference's apply_lora_bgmv) on the workload's projections, 1 GPU")
+                         "the reference's apply_lora_bgmv) on the workload's projections, 1 GPU; qkv_epilogue_*: the consumers of the fused "
+                         "QKV projection (norm + RoPE + paged cache writes) on the 8B shape, 1 GPU")
     ap.add_argument("--only", default="", help="layer workloads: run these projections only, e.g. --only gate or --only q,k,v (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end loops (profiling runs)")
     ap.add_argument("--no-other-mode", action="store_true", help="skip the secondary activation-mode timing (profiling runs)")
@@ -349,6 +405,9 @@ def main():
     if args.warmup is None:
         args.warmup = 1 if reference else 5
 
+    if args.op.startswith("qkv_epilogue_") and not reference:
+        run_qkv_epilogue(args, args.op[len("qkv_epilogue_"):])
+        return
     work = HostWork(args.workload, only=[m for m in args.only.split(",") if m] or None)
     if reference:
         run_reference_arm(args, work)
