@@ -388,7 +388,10 @@ def main():
                     help="N > 1: fused = the kernel's own store phase writes every tile into every rank's buffer; push = each "
                          "projection's columns copied to the peers by a small kernel on a second stream while the next projection "
                          "computes; copy = the same by the copy engines (one strided copy per peer, no SM involved); auto = fused where the rank's share runs as the persistent kernel (stores hidden under the next "
-                         "tile), copy where it is a single wave of tiles; nccl = all-gather after each projection")
+                         "tile), push where it is a single wave of tiles; nccl = all-gather after each projection")
+    ap.add_argument("--gather", default="consumer", choices=["consumer", "outputs"],
+                    help="N >= 4, layers with gate and up: consumer = SwiGLU on the rank's own columns of gate and up, then gather "
+                         "h = silu(gate) * up (what the down projection reads) instead of both outputs; outputs = gather every output")
     ap.add_argument("--activations", default="bf16", choices=["bf16", "fp4"],
                     help="bf16: the layer as specified (exact activations); fp4: the opt-in W4A4 mode as the timed step")
     ap.add_argument("--op", default="fused", choices=["fused", "lora_bgmv", "qkv_epilogue_prefill", "qkv_epilogue_decode"],
@@ -480,8 +483,25 @@ def main():
     # push: the kernels store into this rank's own gathered buffer only; a copy kernel on a second stream sends each
     # projection's columns to the peers while the next projection computes
     push_proj = [fused and args.collective in ("push", "copy")] * n_proj          # per projection; "auto" decides below
-    by_copy_engines = args.collective in ("copy", "auto")
+    by_copy_engines = args.collective == "copy"
     sides = [torch.cuda.Stream(device=dev) for _ in range(min(tp - 1, 4))] if fused else []
+    # Gather what the consumer needs: gate and up are read by nothing but the element-wise SwiGLU, and a rank owns the same
+    # columns of both — so the rank applies SwiGLU to its own columns and the ranks gather h = silu(gate) * up (the down
+    # projection's input, [M, intermediate]) instead of gate AND up: a third less to exchange for the 8B layer.
+    names_all = [c.name.split("/")[-1] for c in work.projections]
+    mlp_h = None
+    # (from four ranks on, where the step is bound by the exchange; at two ranks it is bound by the arithmetic and the extra
+    #  kernel and copies cost more than they save: 1.84 against 1.77 ms)
+    if fused and args.gather == "consumer" and tp >= 4 and not work.fused_out and "gate" in names_all and "up" in names_all:
+        gi_, ui_ = names_all.index("gate"), names_all.index("up")
+        try:
+            h_bufs = [symm_mem.empty((M, work.projections[gi_].N), dtype=torch.bfloat16, device=dev) for _ in sym_sets]
+            h_handles = [symm_mem.rendezvous(b, dist.group.WORLD) for b in h_bufs]
+            mlp_h = dict(gate=gi_, up=ui_, bufs=h_bufs, handles=h_handles, ptrs=[[int(p_) for p_ in h_.buffer_ptrs] for h_ in h_handles],
+                         event=[torch.cuda.Event() for _ in sym_sets])
+        except Exception as e:
+            collective_note = f"h could not be mapped to the peers ({type(e).__name__}: {e}); every output is gathered"
+    local_only = set((mlp_h["gate"], mlp_h["up"])) if mlp_h else set()      # projections whose output stays on the rank
     y_all = ([torch.empty((tp, M, dw.n_local[i]), dtype=torch.bfloat16, device=dev) for i in range(n_proj)]
              if tp > 1 else None)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > L2 (126 MB)
@@ -498,7 +518,7 @@ def main():
             xin = None if x_of is None else x_of[work.projections[i].meta["input"]]
             if sym is not None:
                 j = 0 if work.fused_out else i
-                place = dict(y_dest=(sym["ptrs"][j] if not push_proj[i] else [sym["ptrs"][j][rank]]), out_row_stride=(work.n_total if work.fused_out else work.projections[i].N),
+                place = dict(y_dest=(sym["ptrs"][j] if not (push_proj[i] or i in local_only) else [sym["ptrs"][j][rank]]), out_row_stride=(work.n_total if work.fused_out else work.projections[i].N),
                              y_col_offset=(int(full_cols0[i]) if work.fused_out else 0) + rank * dw.n_local[i])
                 ds.append(dw.desc(i, None, flags, x=xin, seq_slot=seq_slot, **place))
             else:
@@ -523,10 +543,12 @@ def main():
         # which of this rank's shares run as the persistent kernel (the same on every rank: the shapes are)
         for i, d_ in enumerate(build_descs(mode, sym_sets[0])):
             ab.nvfp4_lora_linear(d_, torch.cuda.current_stream())
-            push_proj[i] = not ab.last_launch_shape()["persistent_tiles_per_pass"]
+            push_proj[i] = i not in local_only and not ab.last_launch_shape()["persistent_tiles_per_pass"]
         torch.cuda.synchronize()
         dist.barrier()
-    pushed = any(push_proj)
+    for i in local_only:
+        push_proj[i] = False
+    pushed = any(push_proj) or bool(mlp_h)
     descs = [build_descs(mode, s) for s in sym_sets] if fused else [build_descs(mode)]
     descs_reuse = [build_descs(mode | ab.FLAG_REUSE_SHRINK, s) for s in sym_sets] if fused else None
     from atlas_b200 import tp as tpmod
@@ -552,21 +574,34 @@ def main():
     shrink_fork = torch.cuda.Event()
     shrink_join = [torch.cuda.Event() for _ in range(n_proj)]
 
+    def push_block(ptrs, n_row, col, width, event):
+        """Columns [col, col + width) of this rank's buffer into the same columns of every peer's buffer (`ptrs`: the buffer
+        on every rank), once `event` has passed.  The peers are taken in the order rank+1, rank+2, ...: at any moment every
+        GPU is then the target of one sender, not of all."""
+        peers = [(rank + o) % tp for o in range(1, tp)]
+        for s_ in sides:
+            s_.wait_event(event)
+        if by_copy_engines:
+            for o, r in enumerate(peers):           # one strided copy per peer, spread over the side streams (and so over copy engines)
+                ab.push_columns(ptrs[rank] + col * 2, n_row, [ptrs[r] + col * 2], n_row, M, width, sides[o % len(sides)], copy_engines=True)
+        else:
+            ab.push_columns(ptrs[rank] + col * 2, n_row, [ptrs[r] + col * 2 for r in peers], n_row, M, width, sides[0])
+
     def push(k, i):
-        """Projection i's columns of this rank's gathered buffer (set k) into the same columns of every peer's.  The peers
-        are taken in the order rank+1, rank+2, ...: at any moment every GPU is then the target of one sender, not of all."""
+        """Projection i's columns of this rank's gathered buffer (set k) to the peers."""
         j = 0 if work.fused_out else i
         n_row = work.n_total if work.fused_out else work.projections[i].N
         col = (int(full_cols0[i]) if work.fused_out else 0) + rank * dw.n_local[i]
-        ptrs = sym_sets[k]["ptrs"][j]
-        peers = [(rank + o) % tp for o in range(1, tp)]
-        for s_ in sides:
-            s_.wait_event(push_events[k][i])
-        if by_copy_engines:
-            for o, r in enumerate(peers):           # one strided copy per peer, spread over the side streams (and so over copy engines)
-                ab.push_columns(ptrs[rank] + col * 2, n_row, [ptrs[r] + col * 2], n_row, M, dw.n_local[i], sides[o % len(sides)], copy_engines=True)
-        else:
-            ab.push_columns(ptrs[rank] + col * 2, n_row, [ptrs[r] + col * 2 for r in peers], n_row, M, dw.n_local[i], sides[0])
+        push_block(sym_sets[k]["ptrs"][j], n_row, col, dw.n_local[i], push_events[k][i])
+
+    def swiglu_and_push(k):
+        """h = silu(gate) * up on this rank's columns (read from its own gate / up buffers of set k), then those columns to the peers."""
+        gi_, ui_ = mlp_h["gate"], mlp_h["up"]
+        n_loc, n_row, col = dw.n_local[gi_], work.projections[gi_].N, rank * dw.n_local[gi_]
+        g_ptr, u_ptr = sym_sets[k]["ptrs"][gi_][rank] + col * 2, sym_sets[k]["ptrs"][ui_][rank] + col * 2
+        ab.silu_mul(g_ptr, u_ptr, mlp_h["ptrs"][k][rank] + col * 2, M, n_loc, in_row_stride=n_row, out_row_stride=n_row, stream=stream)
+        mlp_h["event"][k].record(stream)
+        push_block(mlp_h["ptrs"][k], n_row, col, n_loc, mlp_h["event"][k])
 
     def step(marks=None):
         """One step.  `marks`: optional list that receives CUDA events recorded between the step's phases."""
@@ -599,6 +634,8 @@ def main():
                 if push_proj[i]:
                     push_events[k][i].record(stream)
                     push(k, i)
+                if mlp_h and i == max(mlp_h["gate"], mlp_h["up"]):
+                    swiglu_and_push(k)
             mark()
             for o, s_ in enumerate(sides):
                 push_joins[k][o].record(s_)
@@ -656,8 +693,24 @@ def main():
                 for i in range(n_proj):
                     got = s["bufs"][0][:, int(full_cols0[i]):int(full_cols0[i + 1])] if work.fused_out else s["bufs"][i]
                     want = y_all[i].permute(1, 0, 2).reshape(M, tp * dw.n_local[i])
-                    if not torch.equal(got.view(torch.int16), want.contiguous().view(torch.int16)):
+                    if i in local_only:                  # only the rank's own columns of gate / up are kept
+                        lo_, hi_ = rank * dw.n_local[i], (rank + 1) * dw.n_local[i]
+                        got, want = got[:, lo_:hi_], want[:, lo_:hi_]
+                    if not torch.equal(got.contiguous().view(torch.int16), want.contiguous().view(torch.int16)):
                         raise RuntimeError(f"rank {rank}: gathered buffer of projection {i} differs from the ranks' own shard results")
+            if mlp_h:
+                # h on every rank = SwiGLU of the ranks' own gate / up shards, gathered (by NCCL for this check)
+                gi_, ui_ = mlp_h["gate"], mlp_h["up"]
+                n_loc = dw.n_local[gi_]
+                h_loc = torch.empty((M, n_loc), dtype=torch.bfloat16, device=dev)
+                ab.silu_mul(y_loc[gi_].contiguous(), y_loc[ui_].contiguous(), h_loc, M, n_loc, stream=stream)
+                h_all = torch.empty((tp, M, n_loc), dtype=torch.bfloat16, device=dev)
+                dist.all_gather_into_tensor(h_all.view(tp * M, n_loc), h_loc)
+                torch.cuda.synchronize()
+                want = h_all.permute(1, 0, 2).reshape(M, tp * n_loc).contiguous().view(torch.int16)
+                for hb in mlp_h["bufs"]:
+                    if not torch.equal(hb.view(torch.int16), want):
+                        raise RuntimeError(f"rank {rank}: gathered h differs from SwiGLU of the ranks' own gate / up shards")
 
     # ---- device-timed steps ----
     sampler = ClockSampler(local_rank)
@@ -875,14 +928,24 @@ def main():
     proj_ms = vals[5:]
 
     names_p = [c.name.split("/")[-1] for c in work.projections]
-    args.collective_used = ((("columns of " + ",".join(n_ for n_, p_ in zip(names_p, push_proj) if p_) + " copied into every rank's buffer by "
-                              + ("the copy engines" if by_copy_engines else "a push kernel") + " on a second stream beside the next projection's kernels"
-                              + ("; tiles of " + ",".join(n_ for n_, p_ in zip(names_p, push_proj) if not p_) + " stored into every rank's "
-                                 "buffer by the persistent kernel under its next tile" if not all(push_proj) else "")
-                              + " + one device barrier per step") if pushed else
-                             "tiles stored into every rank's buffer by the kernel + one device barrier per step")
-                            + ("; shrink sharded by tokens, its tiles stored into every rank's scratch + one device barrier" if sharded_shrink else "")
-                            if fused else "NCCL all-gather per projection")
+    pushed_names = [n_ for i_, n_ in enumerate(names_p) if push_proj[i_]]
+    stored_names = [n_ for i_, n_ in enumerate(names_p) if not push_proj[i_] and i_ not in local_only]
+    mover = "the copy engines" if by_copy_engines else "a push kernel"
+    if not fused:
+        args.collective_used = "NCCL all-gather per projection"
+    else:
+        parts = []
+        if stored_names:
+            parts.append("tiles of " + ",".join(stored_names) + " stored into every rank's buffer by the kernel" + (" under its next tile" if pushed else ""))
+        if pushed_names:
+            parts.append("columns of " + ",".join(pushed_names) + f" copied into every rank's buffer by {mover} on a second stream beside the next "
+                         "projection's kernels")
+        if mlp_h:
+            parts.append(f"gate and up stay on their rank: h = silu(gate) * up of the rank's columns is gathered instead ({mover})")
+        parts.append("one device barrier per step")
+        if sharded_shrink:
+            parts.append("shrink sharded by tokens, its tiles stored into every rank's scratch + one device barrier")
+        args.collective_used = "; ".join(parts)
     if rank == 0:
         hbm_gbs, bf16_burst, bf16_sustained, peak_kind = peaks()
         work_all = total_work(work.projections)
@@ -907,7 +970,7 @@ def main():
                      "kernel_ms": main_ms, "algorithmic_bytes": dom_work["main_kernel"], "launch_shape": dom_shape})
         t_roof = max(work_all["flops"] / (FP4_PEAK_TFLOPS * 1e12), work_all["total"] / (hbm_gbs * 1e9))
         t_roof_bf16 = max(work_all["flops"] / (bf16_sustained * 1e12), work_all["total"] / (hbm_gbs * 1e9))
-        per_step_launches = sum((1 if c.seq_slot is not None else 0) + 1 + (1 if mode and i_ not in dw.shares_x_with else 0) for i_, c in enumerate(work.projections)) + (1 if fused else 0) + (0 if by_copy_engines else sum(1 for p_ in push_proj if p_))
+        per_step_launches = sum((1 if c.seq_slot is not None else 0) + 1 + (1 if mode and i_ not in dw.shares_x_with else 0) for i_, c in enumerate(work.projections)) + (1 if fused else 0) + (0 if by_copy_engines else sum(1 for p_ in push_proj if p_)) + ((1 if by_copy_engines else 2) if mlp_h else 0)
         line = {
             "metric": METRIC, "value": M / (step_ms * 1e-3), "unit": "tokens/s", "n_gpus": tp,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
