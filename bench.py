@@ -13,12 +13,15 @@ q/k/v LoRA modules into column segments of one fused-QKV output) and the single 
 
 With N > 1 (launched by torch.distributed.run, one rank per GPU) every projection is split column-parallel over
 the ranks — W, its scales and every B_s by output rows; x, A_s and seq_slot replicated: strong scaling.  Every
-rank's gathered [M, N] buffers live in symmetric memory mapped into every process.  `--collective push` (default):
-a projection's kernels store into the rank's own buffer and a small copy kernel on a second stream sends those
-columns to the peers over NVLink while the next projection computes; `--collective fused`: the kernel's own store
-phase writes each tile into all ranks' buffers; either way what remains of the collective is one device-side
-barrier per step.  `--collective nccl` (or a box where the peer mapping cannot be made) runs the projections
-followed by one NCCL all-gather each instead.
+rank's gathered [M, N] buffers live in symmetric memory mapped into every process.  `--collective fused`: the kernel's
+own store phase writes each tile into all ranks' buffers; `--collective push`: a projection's kernels store into the
+rank's own buffer and a small copy kernel on a second stream sends those columns to the peers over NVLink while the next
+projection computes (`copy`: the same by the copy engines); `--collective auto` (default) takes the first where the
+rank's share runs as the persistent kernel and the second where it is a single wave of tiles.  What remains of the
+collective is one device-side barrier per step.  From four ranks on (`--gather consumer`, default) gate and up stay on
+their rank, which applies SwiGLU to its own columns, and h = silu(gate) * up is gathered instead of the two.
+`--collective nccl` (or a box where the peer mapping cannot be made) runs the projections followed by one NCCL
+all-gather each instead.
 
 Rank 0 prints one JSON line.  `value` is device-timed (CUDA events on the launching stream, L2 flushed between
 steps, inputs resident in HBM); `e2e` runs the same calls with host buffers, with the H2D copies of the step's
