@@ -138,3 +138,43 @@ def test_token_shard_ranges_tile_the_batch():
             assert at == M
     with pytest.raises(ValueError):
         tp.token_shard(64, 2, 2)
+
+
+def _swiglu_worker(rank, world, port, out_path):
+    """Gathering what the consumer reads: SwiGLU applied by every rank to its own columns of gate and up and the results
+    all-gathered must equal SwiGLU of the gathered gate and up (the op is element-wise and a rank owns the same columns of
+    both), bit for bit after the BF16 rounding."""
+    for p in (ROOT, os.path.join(ROOT, "apathy-atlas_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch
+    import torch.distributed as dist
+    from atlas_b200 import tp
+    from oracle import oracle_ctypes as oc
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    M, N = 24, 64 * world
+    rng = np.random.default_rng(9)
+    gate = oc.f32_to_bf16(rng.standard_normal((M, N)).astype(np.float32) * 3)
+    up = oc.f32_to_bf16(rng.standard_normal((M, N)).astype(np.float32))
+    n_loc = N // world
+    lo = rank * n_loc
+    h_loc = oc.f32_to_bf16(oc.silu_mul(np.ascontiguousarray(gate[:, lo:lo + n_loc]), np.ascontiguousarray(up[:, lo:lo + n_loc])))
+    h_all = torch.empty((world, M, n_loc * 2), dtype=torch.uint8)
+    dist.all_gather_into_tensor(h_all.view(world * M, n_loc * 2), torch.from_numpy(h_loc.view(np.uint8).copy()))
+    if rank == 0:
+        got = tp.gathered_to_row_major(h_all.numpy().view(np.uint16).reshape(world, M, n_loc))
+        want = oc.f32_to_bf16(oc.silu_mul(gate, up))
+        np.save(out_path, np.array([int(np.array_equal(got, want)), int((want != 0).sum())]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_swiglu_on_own_columns_then_gather_equals_swiglu_of_the_gathered(world, tmp_path):
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "res.npy")
+    mp.spawn(_swiglu_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    res = np.load(out)
+    assert res[0] == 1 and res[1] > 0
