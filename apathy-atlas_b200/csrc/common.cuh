@@ -33,7 +33,8 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
     return __bfloat16_as_ushort(__float2bfloat16_rn(f));
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    return uint32_t(f32_to_bf16_bits(lo)) | (uint32_t(f32_to_bf16_bits(hi)) << 16);
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);               // one conversion for the pair, each rounded to nearest even
+    return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 // ---- E2M1 / E4M3, scalar forms (bit-for-bit the arithmetic of

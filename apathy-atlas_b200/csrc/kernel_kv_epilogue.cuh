@@ -42,9 +42,47 @@ struct KvEpilogueParams {
     float fp8_inv_scale;         // != 0: k_cache is an E4M3 cache (one byte per element): value * fp8_inv_scale, saturating cast
 };
 
-__device__ __forceinline__ float kve_butterfly(float v) {
+// The head's sum of squares from N per-lane partial sums (one per group of lanes' elements), bit for bit the two-level
+// form: each group summed over the 32 lanes by offsets 16, 8, 4, 2, 1, then the group sums, held by lanes 0 .. N-1 of a
+// zero-filled warp, summed the same way (for N = 8 that is ((s0+s4)+(s2+s6)) + ((s1+s5)+(s3+s7)); a zero stands in for a
+// group the head does not have).  Addition commutes, so a lane may keep one of two values at a level and pass the other
+// one to its partner: N groups take N-1 + (5 - log2 N) + log2 N shuffles instead of 5 (N + 1).  After the first part the
+// lane whose bits 16, 8, 4 spell the group's index bits 0, 1, 2 holds that group's sum.
+template <uint32_t N>
+__device__ __forceinline__ float kve_group_total(float (&s)[N], const uint32_t lane) {
+    static_assert(N == 1 || N == 2 || N == 4 || N == 8, "group count");
+    constexpr uint32_t FULL = 0xFFFFFFFFu;
+    uint32_t o = 16;
+    if constexpr (N >= 2) {
+        const bool up = (lane & 16u) != 0u;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+        for (uint32_t k = 0; k < N / 2; ++k) {
+            const float keep = up ? s[2 * k + 1] : s[2 * k], send = up ? s[2 * k] : s[2 * k + 1];
+            s[k] = __fadd_rn(keep, __shfl_xor_sync(FULL, send, 16));
+        }
+        o = 8;
+    }
+    if constexpr (N >= 4) {
+        const bool up = (lane & 8u) != 0u;
+#pragma unroll
+        for (uint32_t k = 0; k < N / 4; ++k) {
+            const float keep = up ? s[2 * k + 1] : s[2 * k], send = up ? s[2 * k] : s[2 * k + 1];
+            s[k] = __fadd_rn(keep, __shfl_xor_sync(FULL, send, 8));
+        }
+        o = 4;
+    }
+    if constexpr (N >= 8) {
+        const bool up = (lane & 4u) != 0u;
+        const float keep = up ? s[1] : s[0], send = up ? s[0] : s[1];
+        s[0] = __fadd_rn(keep, __shfl_xor_sync(FULL, send, 4));
+        o = 2;
+    }
+    float v = s[0];
+#pragma unroll
+    for (; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(FULL, v, o));
+    if constexpr (N >= 8) v = __fadd_rn(v, __shfl_xor_sync(FULL, v, 4));
+    if constexpr (N >= 4) v = __fadd_rn(v, __shfl_xor_sync(FULL, v, 8));
+    if constexpr (N >= 2) v = __fadd_rn(v, __shfl_xor_sync(FULL, v, 16));
     return v;
 }
 
@@ -118,17 +156,13 @@ kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
                     if (j < n_grp) dst[lane + 32u * j] = raw[r][j];
                 continue;
             }
-            float x[NG];
-            float mine = 0.0f;
+            float x[NG], sq[NG];
 #pragma unroll
             for (uint32_t j = 0; j < NG; ++j) {
-                if (j < n_grp) {
-                    x[j] = __uint_as_float(uint32_t(raw[r][j]) << 16);
-                    const float g = kve_butterfly(__fmul_rn(x[j], x[j]));     // sum over elements 32 j .. 32 j + 31
-                    if (lane == j) mine = g;                                   // the group sums as lanes 0 .. n_grp-1 of one more butterfly
-                }
+                x[j] = j < n_grp ? __uint_as_float(uint32_t(raw[r][j]) << 16) : 0.0f;
+                sq[j] = __fmul_rn(x[j], x[j]);                                 // group j = elements 32 j .. 32 j + 31
             }
-            const float total = kve_butterfly(mine);
+            const float total = kve_group_total<NG>(sq, lane);
             const float rms = rsqrtf(__fadd_rn(__fdiv_rn(total, float(p.head_dim)), p.rms_eps));
             float nrm[NG] = {};
 #pragma unroll
@@ -221,6 +255,7 @@ qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
     const size_t cache_at = slot < 0 ? 0 : (size_t(slot / (long long)p.block_size) * p.block_size + size_t(slot % (long long)p.block_size)) *
                                                (size_t(p.kv_heads) * p.head_dim);
     const uint32_t n_grp = (p.head_dim + 63u) / 64u;                       // the reference's warps that hold data
+    const bool in_lanes = p.rotary_dim == 64u && (p.head_dim & 63u) == 0u;
     for (uint32_t base = warp; base < roles; base += KVE_WARPS * KVE_INFLIGHT) {
         // the packed pairs of KVE_INFLIGHT heads first (Q, K or V alike), then the work on each
         uint32_t raw[KVE_INFLIGHT][MAX_GRP];
@@ -253,18 +288,45 @@ qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
             const bool is_q = role < p.q_heads;
             const uint32_t head = is_q ? role : role - p.q_heads;
             const uint16_t* w = is_q ? p.q_norm_w : p.k_norm_w;
-            float x0v[MAX_GRP], x1v[MAX_GRP];
-            float mine = 0.0f;
+            float x0v[MAX_GRP], x1v[MAX_GRP], sq[MAX_GRP];
 #pragma unroll
-            for (uint32_t g = 0; g < MAX_GRP; ++g) {
-                if (g >= n_grp) continue;
+            for (uint32_t g = 0; g < MAX_GRP; ++g) {                       // (a group the head does not have was loaded as zero)
                 x0v[g] = __uint_as_float(raw[r][g] << 16);
                 x1v[g] = __uint_as_float(raw[r][g] & 0xFFFF0000u);
-                const float s = kve_butterfly(__fadd_rn(__fmul_rn(x0v[g], x0v[g]), __fmul_rn(x1v[g], x1v[g])));
-                if (lane == g) mine = s;
+                sq[g] = __fadd_rn(__fmul_rn(x0v[g], x0v[g]), __fmul_rn(x1v[g], x1v[g]));
             }
-            const float total = kve_butterfly(mine);
+            const float total = kve_group_total<MAX_GRP>(sq, lane);
             const float rms = rsqrtf(__fadd_rn(__fdiv_rn(total, float(p.head_dim)), p.rms_eps));
+            uint16_t* dst = is_q ? p.q + size_t(token) * p.q_row_stride + size_t(head) * p.head_dim
+                                 : p.k_cache + cache_at + size_t(head) * p.head_dim;
+            if (in_lanes) {
+                // rotary_dim = 64 over whole 64-channel groups: a pair's two halves sit 16 lanes apart in group 0, so they
+                // meet by one shuffle and nothing goes through shared memory; the arithmetic is that of the general form
+#pragma unroll
+                for (uint32_t g = 0; g < MAX_GRP; ++g) {
+                    if (g >= n_grp) continue;
+                    const uint32_t e = 64u * g + 2u * lane;
+                    const uint32_t wk = *reinterpret_cast<const uint32_t*>(w + e);
+                    const float w0 = __uint_as_float(wk << 16), w1 = __uint_as_float(wk & 0xFFFF0000u);
+                    const float f0 = p.norm_offset_one ? __fadd_rn(1.0f, w0) : w0, f1 = p.norm_offset_one ? __fadd_rn(1.0f, w1) : w1;
+                    const uint32_t own = pack_bf16x2(__fmul_rn(__fmul_rn(x0v[g], rms), f0), __fmul_rn(__fmul_rn(x1v[g], rms), f1));
+                    uint32_t out = own;
+                    if (g == 0) {
+                        const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, own, 16);
+                        const bool low = lane < 16u;
+                        const uint32_t first = low ? own : other, second = low ? other : own;   // channels t and t + 32
+                        const uint32_t t = (2u * lane) & 31u;
+                        const float a0 = __uint_as_float(first << 16), a1 = __uint_as_float(first & 0xFFFF0000u);
+                        const float b0 = __uint_as_float(second << 16), b1 = __uint_as_float(second & 0xFFFF0000u);
+                        const float c0 = cos_s[t], s0 = sin_s[t], c1 = cos_s[t + 1], s1 = sin_s[t + 1];
+                        const float r0 = low ? __fsub_rn(__fmul_rn(a0, c0), __fmul_rn(b0, s0)) : __fadd_rn(__fmul_rn(b0, c0), __fmul_rn(a0, s0));
+                        const float r1 = low ? __fsub_rn(__fmul_rn(a1, c1), __fmul_rn(b1, s1)) : __fadd_rn(__fmul_rn(b1, c1), __fmul_rn(a1, s1));
+                        out = pack_bf16x2(r0, r1);
+                    }
+                    *reinterpret_cast<uint32_t*>(dst + e) = out;
+                }
+                continue;
+            }
             __syncwarp();                                                  // the strip's previous head has been read
 #pragma unroll
             for (uint32_t g = 0; g < MAX_GRP; ++g) {
@@ -279,8 +341,6 @@ qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
                 }
             }
             __syncwarp();
-            uint16_t* dst = is_q ? p.q + size_t(token) * p.q_row_stride + size_t(head) * p.head_dim
-                                 : p.k_cache + cache_at + size_t(head) * p.head_dim;
             for (uint32_t t = lane; t < p.head_dim; t += 32) {
                 if (t < pairs) {
                     const float a = __uint_as_float(uint32_t(normed_s[warp][t]) << 16);
