@@ -86,6 +86,12 @@ __device__ __forceinline__ float kve_group_total(float (&s)[N], const uint32_t l
     return v;
 }
 
+// total / head_dim rounded to nearest; for a power of two the product with the exact reciprocal is the same number
+__device__ __forceinline__ float kve_mean(const float total, const uint32_t head_dim) {
+    return (head_dim & (head_dim - 1u)) == 0u ? __fmul_rn(total, __uint_as_float((127u - (31u - __clz(head_dim))) << 23))
+                                              : __fdiv_rn(total, float(head_dim));
+}
+
 constexpr int KVE_TOKENS = 8;                // tokens per CTA (prefill form)
 constexpr int KVE_INFLIGHT = 4;              // heads a warp has loaded before it starts on the first of them
 
@@ -147,8 +153,8 @@ kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
             const bool is_v = h >= p.kv_heads;
             const uint32_t head = is_v ? h - p.kv_heads : h;
             const long long slot = slot_r[r];
-            const size_t dst_at = (size_t(slot / (long long)p.block_size) * p.block_size + size_t(slot % (long long)p.block_size)) *
-                                      (size_t(p.kv_heads) * p.head_dim) + size_t(head) * p.head_dim;
+            // page slot / block_size, offset slot % block_size in a cache of [pages, block_size, kv_heads, head_dim]: row `slot`
+            const size_t dst_at = size_t(slot) * (size_t(p.kv_heads) * p.head_dim) + size_t(head) * p.head_dim;
             if (is_v) {
                 uint16_t* dst = p.v_cache + dst_at;
 #pragma unroll
@@ -163,7 +169,7 @@ kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
                 sq[j] = __fmul_rn(x[j], x[j]);                                 // group j = elements 32 j .. 32 j + 31
             }
             const float total = kve_group_total<NG>(sq, lane);
-            const float rms = rsqrtf(__fadd_rn(__fdiv_rn(total, float(p.head_dim)), p.rms_eps));
+            const float rms = rsqrtf(__fadd_rn(kve_mean(total, p.head_dim), p.rms_eps));
             float nrm[NG] = {};
 #pragma unroll
             for (uint32_t j = 0; j < NG; ++j)
@@ -233,7 +239,7 @@ struct QkvEpilogueParams {
 
 // MAX_GRP: head_dim / 64 rounded up to 1, 2 or 4
 template <uint32_t MAX_GRP>
-__global__ void __launch_bounds__(KVE_WARPS * 32)
+__global__ void __launch_bounds__(KVE_WARPS * 32, MAX_GRP == 4 ? 4 : 6)     // (occupancy matters more here than a few held values)
 qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
     // one CTA per token; cosine and sine of the token's angles evaluated once for all its heads (see above)
     __shared__ uint16_t normed_s[KVE_WARPS][KVE_MAX_HEAD_DIM];
@@ -252,10 +258,16 @@ qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
     __syncthreads();
     const uint32_t roles = p.q_heads + 2u * p.kv_heads;
     const long long slot = p.slot_mapping[token];
-    const size_t cache_at = slot < 0 ? 0 : (size_t(slot / (long long)p.block_size) * p.block_size + size_t(slot % (long long)p.block_size)) *
-                                               (size_t(p.kv_heads) * p.head_dim);
+    // page slot / block_size, offset slot % block_size in a cache of [pages, block_size, kv_heads, head_dim]: row `slot`
+    const size_t cache_at = slot < 0 ? 0 : size_t(slot) * (size_t(p.kv_heads) * p.head_dim);
     const uint32_t n_grp = (p.head_dim + 63u) / 64u;                       // the reference's warps that hold data
     const bool in_lanes = p.rotary_dim == 64u && (p.head_dim & 63u) == 0u;
+    // in-lane form: this lane's two angles, held for all of the token's heads
+    float c0 = 0.0f, s0 = 0.0f, c1 = 0.0f, s1 = 0.0f;
+    if (in_lanes) {
+        const uint32_t t = (2u * lane) & 31u;
+        c0 = cos_s[t], s0 = sin_s[t], c1 = cos_s[t + 1], s1 = sin_s[t + 1];
+    }
     for (uint32_t base = warp; base < roles; base += KVE_WARPS * KVE_INFLIGHT) {
         // the packed pairs of KVE_INFLIGHT heads first (Q, K or V alike), then the work on each
         uint32_t raw[KVE_INFLIGHT][MAX_GRP];
@@ -296,7 +308,7 @@ qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
                 sq[g] = __fadd_rn(__fmul_rn(x0v[g], x0v[g]), __fmul_rn(x1v[g], x1v[g]));
             }
             const float total = kve_group_total<MAX_GRP>(sq, lane);
-            const float rms = rsqrtf(__fadd_rn(__fdiv_rn(total, float(p.head_dim)), p.rms_eps));
+            const float rms = rsqrtf(__fadd_rn(kve_mean(total, p.head_dim), p.rms_eps));
             uint16_t* dst = is_q ? p.q + size_t(token) * p.q_row_stride + size_t(head) * p.head_dim
                                  : p.k_cache + cache_at + size_t(head) * p.head_dim;
             if (in_lanes) {
@@ -315,10 +327,8 @@ qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
                         const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, own, 16);
                         const bool low = lane < 16u;
                         const uint32_t first = low ? own : other, second = low ? other : own;   // channels t and t + 32
-                        const uint32_t t = (2u * lane) & 31u;
                         const float a0 = __uint_as_float(first << 16), a1 = __uint_as_float(first & 0xFFFF0000u);
                         const float b0 = __uint_as_float(second << 16), b1 = __uint_as_float(second & 0xFFFF0000u);
-                        const float c0 = cos_s[t], s0 = sin_s[t], c1 = cos_s[t + 1], s1 = sin_s[t + 1];
                         const float r0 = low ? __fsub_rn(__fmul_rn(a0, c0), __fmul_rn(b0, s0)) : __fadd_rn(__fmul_rn(b0, c0), __fmul_rn(a0, s0));
                         const float r1 = low ? __fsub_rn(__fmul_rn(a1, c1), __fmul_rn(b1, s1)) : __fadd_rn(__fmul_rn(b1, c1), __fmul_rn(a1, s1));
                         out = pack_bf16x2(r0, r1);
