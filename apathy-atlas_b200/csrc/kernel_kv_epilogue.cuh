@@ -256,10 +256,7 @@ qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
         }
     }
     __syncthreads();
-    const uint32_t roles = p.q_heads + 2u * p.kv_heads;
     const long long slot = p.slot_mapping[token];
-    // page slot / block_size, offset slot % block_size in a cache of [pages, block_size, kv_heads, head_dim]: row `slot`
-    const size_t cache_at = slot < 0 ? 0 : size_t(slot) * (size_t(p.kv_heads) * p.head_dim);
     const uint32_t n_grp = (p.head_dim + 63u) / 64u;                       // the reference's warps that hold data
     const bool in_lanes = p.rotary_dim == 64u && (p.head_dim & 63u) == 0u;
     // in-lane form: this lane's two angles, held for all of the token's heads
@@ -268,99 +265,118 @@ qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
         const uint32_t t = (2u * lane) & 31u;
         c0 = cos_s[t], s0 = sin_s[t], c1 = cos_s[t + 1], s1 = sin_s[t + 1];
     }
-    for (uint32_t base = warp; base < roles; base += KVE_WARPS * KVE_INFLIGHT) {
-        // the packed pairs of KVE_INFLIGHT heads first (Q, K or V alike), then the work on each
-        uint32_t raw[KVE_INFLIGHT][MAX_GRP];
+    uint32_t have = 0;                                                     // bit g: this lane holds a pair of group g
 #pragma unroll
-        for (uint32_t r = 0; r < uint32_t(KVE_INFLIGHT); ++r) {
-            const uint32_t role = base + r * KVE_WARPS;
-            if (role >= roles || (role >= p.q_heads && slot < 0)) continue;
-            const uint16_t* x = role < p.q_heads ? p.q + size_t(token) * p.q_row_stride + size_t(role) * p.head_dim
-                              : (role < p.q_heads + p.kv_heads ? p.k_in + size_t(token) * p.kv_row_stride + size_t(role - p.q_heads) * p.head_dim
-                                                               : p.v_in + size_t(token) * p.kv_row_stride + size_t(role - p.q_heads - p.kv_heads) * p.head_dim);
+    for (uint32_t g = 0; g < MAX_GRP; ++g)
+        if (g < n_grp && 64u * g + 2u * lane < p.head_dim) have |= 1u << g;
+
+    auto load_head = [&](uint32_t (&rw)[MAX_GRP], const uint16_t* x) {
 #pragma unroll
-            for (uint32_t g = 0; g < MAX_GRP; ++g) {
-                const uint32_t e = 64u * g + 2u * lane;
-                raw[r][g] = (g < n_grp && e < p.head_dim) ? *reinterpret_cast<const uint32_t*>(x + e) : 0u;
-            }
+        for (uint32_t g = 0; g < MAX_GRP; ++g)
+            rw[g] = ((have >> g) & 1u) ? *reinterpret_cast<const uint32_t*>(x + 64u * g + 2u * lane) : 0u;
+    };
+    // per-head RMS norm, rotation and one rounding of the head held as packed pairs in rw; result to dst
+    auto norm_rope_head = [&](const uint32_t (&rw)[MAX_GRP], const uint16_t* w, uint16_t* dst) {
+        float x0v[MAX_GRP], x1v[MAX_GRP], sq[MAX_GRP];
+#pragma unroll
+        for (uint32_t g = 0; g < MAX_GRP; ++g) {                           // (a group the head does not have was loaded as zero)
+            x0v[g] = __uint_as_float(rw[g] << 16);
+            x1v[g] = __uint_as_float(rw[g] & 0xFFFF0000u);
+            sq[g] = __fadd_rn(__fmul_rn(x0v[g], x0v[g]), __fmul_rn(x1v[g], x1v[g]));
         }
-#pragma unroll
-        for (uint32_t r = 0; r < uint32_t(KVE_INFLIGHT); ++r) {
-            const uint32_t role = base + r * KVE_WARPS;
-            if (role >= roles || (role >= p.q_heads && slot < 0)) continue;          // (the reference computes a padding token's K and drops it)
-            if (role >= p.q_heads + p.kv_heads) {                                    // V: a copy
-                uint16_t* dst = p.v_cache + cache_at + size_t(role - p.q_heads - p.kv_heads) * p.head_dim;
-#pragma unroll
-                for (uint32_t g = 0; g < MAX_GRP; ++g) {
-                    const uint32_t e = 64u * g + 2u * lane;
-                    if (g < n_grp && e < p.head_dim) *reinterpret_cast<uint32_t*>(dst + e) = raw[r][g];
-                }
-                continue;
-            }
-            const bool is_q = role < p.q_heads;
-            const uint32_t head = is_q ? role : role - p.q_heads;
-            const uint16_t* w = is_q ? p.q_norm_w : p.k_norm_w;
-            float x0v[MAX_GRP], x1v[MAX_GRP], sq[MAX_GRP];
-#pragma unroll
-            for (uint32_t g = 0; g < MAX_GRP; ++g) {                       // (a group the head does not have was loaded as zero)
-                x0v[g] = __uint_as_float(raw[r][g] << 16);
-                x1v[g] = __uint_as_float(raw[r][g] & 0xFFFF0000u);
-                sq[g] = __fadd_rn(__fmul_rn(x0v[g], x0v[g]), __fmul_rn(x1v[g], x1v[g]));
-            }
-            const float total = kve_group_total<MAX_GRP>(sq, lane);
-            const float rms = rsqrtf(__fadd_rn(kve_mean(total, p.head_dim), p.rms_eps));
-            uint16_t* dst = is_q ? p.q + size_t(token) * p.q_row_stride + size_t(head) * p.head_dim
-                                 : p.k_cache + cache_at + size_t(head) * p.head_dim;
-            if (in_lanes) {
-                // rotary_dim = 64 over whole 64-channel groups: a pair's two halves sit 16 lanes apart in group 0, so they
-                // meet by one shuffle and nothing goes through shared memory; the arithmetic is that of the general form
-#pragma unroll
-                for (uint32_t g = 0; g < MAX_GRP; ++g) {
-                    if (g >= n_grp) continue;
-                    const uint32_t e = 64u * g + 2u * lane;
-                    const uint32_t wk = *reinterpret_cast<const uint32_t*>(w + e);
-                    const float w0 = __uint_as_float(wk << 16), w1 = __uint_as_float(wk & 0xFFFF0000u);
-                    const float f0 = p.norm_offset_one ? __fadd_rn(1.0f, w0) : w0, f1 = p.norm_offset_one ? __fadd_rn(1.0f, w1) : w1;
-                    const uint32_t own = pack_bf16x2(__fmul_rn(__fmul_rn(x0v[g], rms), f0), __fmul_rn(__fmul_rn(x1v[g], rms), f1));
-                    uint32_t out = own;
-                    if (g == 0) {
-                        const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, own, 16);
-                        const bool low = lane < 16u;
-                        const uint32_t first = low ? own : other, second = low ? other : own;   // channels t and t + 32
-                        const float a0 = __uint_as_float(first << 16), a1 = __uint_as_float(first & 0xFFFF0000u);
-                        const float b0 = __uint_as_float(second << 16), b1 = __uint_as_float(second & 0xFFFF0000u);
-                        const float r0 = low ? __fsub_rn(__fmul_rn(a0, c0), __fmul_rn(b0, s0)) : __fadd_rn(__fmul_rn(b0, c0), __fmul_rn(a0, s0));
-                        const float r1 = low ? __fsub_rn(__fmul_rn(a1, c1), __fmul_rn(b1, s1)) : __fadd_rn(__fmul_rn(b1, c1), __fmul_rn(a1, s1));
-                        out = pack_bf16x2(r0, r1);
-                    }
-                    *reinterpret_cast<uint32_t*>(dst + e) = out;
-                }
-                continue;
-            }
-            __syncwarp();                                                  // the strip's previous head has been read
+        const float total = kve_group_total<MAX_GRP>(sq, lane);
+        const float rms = rsqrtf(__fadd_rn(kve_mean(total, p.head_dim), p.rms_eps));
+        if (in_lanes) {
+            // rotary_dim = 64 over whole 64-channel groups: a pair's two halves sit 16 lanes apart in group 0, so they
+            // meet by one shuffle and nothing goes through shared memory; the arithmetic is that of the general form
 #pragma unroll
             for (uint32_t g = 0; g < MAX_GRP; ++g) {
                 if (g >= n_grp) continue;
                 const uint32_t e = 64u * g + 2u * lane;
-                if (e < p.head_dim) {
-                    const uint32_t wk = *reinterpret_cast<const uint32_t*>(w + e);
-                    const float w0 = __uint_as_float(wk << 16), w1 = __uint_as_float(wk & 0xFFFF0000u);
-                    const float f0 = p.norm_offset_one ? __fadd_rn(1.0f, w0) : w0, f1 = p.norm_offset_one ? __fadd_rn(1.0f, w1) : w1;
-                    normed_s[warp][e] = f32_to_bf16_bits(__fmul_rn(__fmul_rn(x0v[g], rms), f0));
-                    normed_s[warp][e + 1] = f32_to_bf16_bits(__fmul_rn(__fmul_rn(x1v[g], rms), f1));
+                const uint32_t wk = *reinterpret_cast<const uint32_t*>(w + e);
+                const float w0 = __uint_as_float(wk << 16), w1 = __uint_as_float(wk & 0xFFFF0000u);
+                const float f0 = p.norm_offset_one ? __fadd_rn(1.0f, w0) : w0, f1 = p.norm_offset_one ? __fadd_rn(1.0f, w1) : w1;
+                const uint32_t own = pack_bf16x2(__fmul_rn(__fmul_rn(x0v[g], rms), f0), __fmul_rn(__fmul_rn(x1v[g], rms), f1));
+                uint32_t out = own;
+                if (g == 0) {
+                    const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, own, 16);
+                    const bool low = lane < 16u;
+                    const uint32_t first = low ? own : other, second = low ? other : own;   // channels t and t + 32
+                    const float a0 = __uint_as_float(first << 16), a1 = __uint_as_float(first & 0xFFFF0000u);
+                    const float b0 = __uint_as_float(second << 16), b1 = __uint_as_float(second & 0xFFFF0000u);
+                    const float r0 = low ? __fsub_rn(__fmul_rn(a0, c0), __fmul_rn(b0, s0)) : __fadd_rn(__fmul_rn(b0, c0), __fmul_rn(a0, s0));
+                    const float r1 = low ? __fsub_rn(__fmul_rn(a1, c1), __fmul_rn(b1, s1)) : __fadd_rn(__fmul_rn(b1, c1), __fmul_rn(a1, s1));
+                    out = pack_bf16x2(r0, r1);
                 }
+                *reinterpret_cast<uint32_t*>(dst + e) = out;
             }
-            __syncwarp();
-            for (uint32_t t = lane; t < p.head_dim; t += 32) {
-                if (t < pairs) {
-                    const float a = __uint_as_float(uint32_t(normed_s[warp][t]) << 16);
-                    const float b = __uint_as_float(uint32_t(normed_s[warp][t + pairs]) << 16);
-                    const float c = cos_s[t], s = sin_s[t];
-                    dst[t] = f32_to_bf16_bits(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)));
-                    dst[t + pairs] = f32_to_bf16_bits(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s)));
-                } else if (t >= p.rotary_dim) {
-                    dst[t] = normed_s[warp][t];                            // channels beyond the rotary part pass through
-                }
+            return;
+        }
+        __syncwarp();                                                      // the strip's previous head has been read
+#pragma unroll
+        for (uint32_t g = 0; g < MAX_GRP; ++g) {
+            if (!((have >> g) & 1u)) continue;
+            const uint32_t e = 64u * g + 2u * lane;
+            const uint32_t wk = *reinterpret_cast<const uint32_t*>(w + e);
+            const float w0 = __uint_as_float(wk << 16), w1 = __uint_as_float(wk & 0xFFFF0000u);
+            const float f0 = p.norm_offset_one ? __fadd_rn(1.0f, w0) : w0, f1 = p.norm_offset_one ? __fadd_rn(1.0f, w1) : w1;
+            normed_s[warp][e] = f32_to_bf16_bits(__fmul_rn(__fmul_rn(x0v[g], rms), f0));
+            normed_s[warp][e + 1] = f32_to_bf16_bits(__fmul_rn(__fmul_rn(x1v[g], rms), f1));
+        }
+        __syncwarp();
+        for (uint32_t t = lane; t < p.head_dim; t += 32) {
+            if (t < pairs) {
+                const float a = __uint_as_float(uint32_t(normed_s[warp][t]) << 16);
+                const float b = __uint_as_float(uint32_t(normed_s[warp][t + pairs]) << 16);
+                const float c = cos_s[t], s = sin_s[t];
+                dst[t] = f32_to_bf16_bits(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)));
+                dst[t + pairs] = f32_to_bf16_bits(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s)));
+            } else if (t >= p.rotary_dim) {
+                dst[t] = normed_s[warp][t];                                // channels beyond the rotary part pass through
+            }
+        }
+    };
+
+    // Q heads, in place: a warp loads KVE_INFLIGHT heads, then works on each
+    uint16_t* const q_tok = p.q + size_t(token) * p.q_row_stride;
+    for (uint32_t h0 = warp; h0 < p.q_heads; h0 += KVE_WARPS * KVE_INFLIGHT) {
+        uint32_t raw[KVE_INFLIGHT][MAX_GRP];
+#pragma unroll
+        for (uint32_t r = 0; r < uint32_t(KVE_INFLIGHT); ++r) {
+            const uint32_t head = h0 + r * KVE_WARPS;
+            if (head < p.q_heads) load_head(raw[r], q_tok + head * p.head_dim);
+        }
+#pragma unroll
+        for (uint32_t r = 0; r < uint32_t(KVE_INFLIGHT); ++r) {
+            const uint32_t head = h0 + r * KVE_WARPS;
+            if (head < p.q_heads) norm_rope_head(raw[r], p.q_norm_w, q_tok + head * p.head_dim);
+        }
+    }
+    if (slot < 0) return;                                                  // (the reference computes a padding token's K and drops it)
+    // K heads into the cache row `slot` (page slot / block_size, offset slot % block_size of [pages, block_size, kv_heads,
+    // head_dim]), V heads copied beside them: items 0 .. kv_heads-1 are K, the rest V
+    const uint16_t* const k_tok = p.k_in + size_t(token) * p.kv_row_stride;
+    const uint16_t* const v_tok = p.v_in + size_t(token) * p.kv_row_stride;
+    const size_t cache_at = size_t(slot) * (size_t(p.kv_heads) * p.head_dim);
+    for (uint32_t i0 = warp; i0 < 2u * p.kv_heads; i0 += KVE_WARPS * KVE_INFLIGHT) {
+        uint32_t raw[KVE_INFLIGHT][MAX_GRP];
+#pragma unroll
+        for (uint32_t r = 0; r < uint32_t(KVE_INFLIGHT); ++r) {
+            const uint32_t item = i0 + r * KVE_WARPS;
+            if (item < 2u * p.kv_heads)
+                load_head(raw[r], item < p.kv_heads ? k_tok + item * p.head_dim : v_tok + (item - p.kv_heads) * p.head_dim);
+        }
+#pragma unroll
+        for (uint32_t r = 0; r < uint32_t(KVE_INFLIGHT); ++r) {
+            const uint32_t item = i0 + r * KVE_WARPS;
+            if (item >= 2u * p.kv_heads) continue;
+            if (item < p.kv_heads) {
+                norm_rope_head(raw[r], p.k_norm_w, p.k_cache + cache_at + item * p.head_dim);
+            } else {
+                uint16_t* dst = p.v_cache + cache_at + (item - p.kv_heads) * p.head_dim;
+#pragma unroll
+                for (uint32_t g = 0; g < MAX_GRP; ++g)
+                    if ((have >> g) & 1u) *reinterpret_cast<uint32_t*>(dst + 64u * g + 2u * lane) = raw[r][g];
             }
         }
     }
