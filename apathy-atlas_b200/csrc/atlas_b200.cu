@@ -1145,9 +1145,13 @@ int atlas_b200_qkv_norm_rope_cache_write(void* q, const void* k_in, const void* 
     p.block_size = block_size; p.q_row_stride = q_row_stride; p.kv_row_stride = kv_row_stride;
     p.rms_eps = rms_eps; p.attention_factor = attention_factor; p.norm_offset_one = norm_offset_one ? 1u : 0u;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (head_dim <= 64) qkv_norm_rope_cache_kernel<1><<<tokens, KVE_WARPS * 32, 0, st>>>(p);
-    else if (head_dim <= 128) qkv_norm_rope_cache_kernel<2><<<tokens, KVE_WARPS * 32, 0, st>>>(p);
-    else qkv_norm_rope_cache_kernel<4><<<tokens, KVE_WARPS * 32, 0, st>>>(p);
+    const bool exact = rotary_dim == 64 && (head_dim == 64 || head_dim == 128 || head_dim == 256);
+    if (head_dim <= 64) exact ? qkv_norm_rope_cache_kernel<1, true><<<tokens, KVE_WARPS * 32, 0, st>>>(p)
+                              : qkv_norm_rope_cache_kernel<1, false><<<tokens, KVE_WARPS * 32, 0, st>>>(p);
+    else if (head_dim <= 128) exact ? qkv_norm_rope_cache_kernel<2, true><<<tokens, KVE_WARPS * 32, 0, st>>>(p)
+                                    : qkv_norm_rope_cache_kernel<2, false><<<tokens, KVE_WARPS * 32, 0, st>>>(p);
+    else exact ? qkv_norm_rope_cache_kernel<4, true><<<tokens, KVE_WARPS * 32, 0, st>>>(p)
+               : qkv_norm_rope_cache_kernel<4, false><<<tokens, KVE_WARPS * 32, 0, st>>>(p);
     return launch_status();
 }
 

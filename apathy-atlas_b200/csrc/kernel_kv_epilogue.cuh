@@ -237,12 +237,15 @@ struct QkvEpilogueParams {
     uint32_t norm_offset_one;
 };
 
-// MAX_GRP: head_dim / 64 rounded up to 1, 2 or 4
-template <uint32_t MAX_GRP>
+// MAX_GRP: head_dim / 64 rounded up to 1, 2 or 4.  EXACT: head_dim = 64 MAX_GRP and rotary_dim = 64 (the common shapes),
+// known when the kernel is compiled, so that no lane is masked, a pair's halves meet by one shuffle and the general
+// form with its shared-memory strip drops out.
+template <uint32_t MAX_GRP, bool EXACT>
 __global__ void __launch_bounds__(KVE_WARPS * 32, MAX_GRP == 4 ? 4 : 6)     // (occupancy matters more here than a few held values)
-qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
+qkv_norm_rope_cache_kernel(QkvEpilogueParams p) {
+    if constexpr (EXACT) { p.head_dim = 64u * MAX_GRP; p.rotary_dim = 64u; }
     // one CTA per token; cosine and sine of the token's angles evaluated once for all its heads (see above)
-    __shared__ uint16_t normed_s[KVE_WARPS][KVE_MAX_HEAD_DIM];
+    __shared__ uint16_t normed_s[EXACT ? 1 : KVE_WARPS][EXACT ? 2 : KVE_MAX_HEAD_DIM];
     __shared__ float cos_s[KVE_MAX_HEAD_DIM / 2], sin_s[KVE_MAX_HEAD_DIM / 2];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t token = blockIdx.x;
@@ -257,18 +260,20 @@ qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
     }
     __syncthreads();
     const long long slot = p.slot_mapping[token];
-    const uint32_t n_grp = (p.head_dim + 63u) / 64u;                       // the reference's warps that hold data
-    const bool in_lanes = p.rotary_dim == 64u && (p.head_dim & 63u) == 0u;
+    const uint32_t n_grp = EXACT ? MAX_GRP : (p.head_dim + 63u) / 64u;     // the reference's warps that hold data
+    const bool in_lanes = EXACT || (p.rotary_dim == 64u && (p.head_dim & 63u) == 0u);
     // in-lane form: this lane's two angles, held for all of the token's heads
     float c0 = 0.0f, s0 = 0.0f, c1 = 0.0f, s1 = 0.0f;
     if (in_lanes) {
         const uint32_t t = (2u * lane) & 31u;
         c0 = cos_s[t], s0 = sin_s[t], c1 = cos_s[t + 1], s1 = sin_s[t + 1];
     }
-    uint32_t have = 0;                                                     // bit g: this lane holds a pair of group g
+    uint32_t have = EXACT ? (1u << MAX_GRP) - 1u : 0u;                     // bit g: this lane holds a pair of group g
+    if constexpr (!EXACT) {
 #pragma unroll
-    for (uint32_t g = 0; g < MAX_GRP; ++g)
-        if (g < n_grp && 64u * g + 2u * lane < p.head_dim) have |= 1u << g;
+        for (uint32_t g = 0; g < MAX_GRP; ++g)
+            if (g < n_grp && 64u * g + 2u * lane < p.head_dim) have |= 1u << g;
+    }
 
     auto load_head = [&](uint32_t (&rw)[MAX_GRP], const uint16_t* x) {
 #pragma unroll
@@ -312,6 +317,7 @@ qkv_norm_rope_cache_kernel(const QkvEpilogueParams p) {
             }
             return;
         }
+        if constexpr (EXACT) return;
         __syncwarp();                                                      // the strip's previous head has been read
 #pragma unroll
         for (uint32_t g = 0; g < MAX_GRP; ++g) {

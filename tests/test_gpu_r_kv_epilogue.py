@@ -91,7 +91,7 @@ def test_shapes_the_kernel_does_not_take_are_refused(cuda, atlas):
         assert e.value.status == -1
 
 
-@pytest.mark.parametrize("head_dim,rotary_dim,offset_one,factor", [(128, 64, True, 1.0), (128, 128, False, 1.18), (256, 64, True, 1.0), (64, 32, True, 0.9)])
+@pytest.mark.parametrize("head_dim,rotary_dim,offset_one,factor", [(128, 64, True, 1.0), (128, 128, False, 1.18), (256, 64, True, 1.0), (64, 32, True, 0.9), (192, 64, True, 1.0), (64, 64, False, 1.0)])
 def test_decode_qkv_norm_rope_cache_write(cuda, atlas, oracle, head_dim, rotary_dim, offset_one, factor):
     """Q in place, K into the paged cache, V copied — against the reference's fused decode kernel
     (kernels/gb10/common/fused_verify_elemwise.cu) bit for bit, in place on a strided fused QKV buffer, and against the
