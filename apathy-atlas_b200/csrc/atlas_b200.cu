@@ -1084,9 +1084,10 @@ static int kv_norm_rope_cache_write(const void* k_in, const void* v_in, uint32_t
     p.in_row_stride = in_row_stride; p.rms_eps = rms_eps; p.theta = theta; p.fp8_inv_scale = fp8_inv_scale;
     const dim3 grid((tokens + KVE_TOKENS - 1) / KVE_TOKENS), block(KVE_WARPS * 32);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (head_dim <= 64) kv_norm_rope_cache_kernel<2><<<grid, block, 0, st>>>(p);
-    else if (head_dim <= 128) kv_norm_rope_cache_kernel<4><<<grid, block, 0, st>>>(p);
-    else kv_norm_rope_cache_kernel<8><<<grid, block, 0, st>>>(p);
+    const bool exact = rotary_dim == 64 && fp8_inv_scale == 0.0f && (head_dim == 64 || head_dim == 128 || head_dim == 256);
+    if (head_dim <= 64) exact ? kv_norm_rope_cache_kernel<2, true><<<grid, block, 0, st>>>(p) : kv_norm_rope_cache_kernel<2, false><<<grid, block, 0, st>>>(p);
+    else if (head_dim <= 128) exact ? kv_norm_rope_cache_kernel<4, true><<<grid, block, 0, st>>>(p) : kv_norm_rope_cache_kernel<4, false><<<grid, block, 0, st>>>(p);
+    else exact ? kv_norm_rope_cache_kernel<8, true><<<grid, block, 0, st>>>(p) : kv_norm_rope_cache_kernel<8, false><<<grid, block, 0, st>>>(p);
     return launch_status();
 }
 

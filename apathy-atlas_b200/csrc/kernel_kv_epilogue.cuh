@@ -95,10 +95,14 @@ __device__ __forceinline__ float kve_mean(const float total, const uint32_t head
 constexpr int KVE_TOKENS = 8;                // tokens per CTA (prefill form)
 constexpr int KVE_INFLIGHT = 4;              // heads a warp has loaded before it starts on the first of them
 
-// NG: head_dim / 32 rounded up to 2, 4 or 8 (register arrays sized for the head at hand)
-template <uint32_t NG>
+// NG: head_dim / 32 rounded up to 2, 4 or 8 (register arrays sized for the head at hand).  EXACT: head_dim = 32 NG,
+// rotary_dim = 64 and a BF16 cache, known when the kernel is compiled (the common shapes): no masked groups, and which
+// group holds a pair's other half is a constant.
+template <uint32_t NG, bool EXACT>
 __global__ void __launch_bounds__(KVE_WARPS * 32)
-kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
+kv_norm_rope_cache_kernel(KvEpilogueParams p) {
+    static_assert(KVE_TOKENS == KVE_WARPS, "one warp per token of the CTA");
+    if constexpr (EXACT) { p.head_dim = 32u * NG; p.rotary_dim = 64u; p.fp8_inv_scale = 0.0f; }
     // One CTA per KVE_TOKENS tokens.  The rotation's frequency depends on the pair only and its cosine and sine on
     // (token, pair) only, so the FP64 power is evaluated once per CTA and pair, the two transcendental calls once per
     // token and pair — the reference evaluates all three per element — and every head reads them from shared memory.
@@ -126,35 +130,33 @@ kv_norm_rope_cache_kernel(const KvEpilogueParams p) {
     __syncthreads();
     const uint32_t heads_all = p.kv_heads * (p.v_in ? 2u : 1u);           // K heads, then V heads
     const uint32_t n_grp = p.head_dim / 32u;                               // elements per lane (head_dim: a multiple of 32, <= 256)
-    const uint32_t n_items = n_tok * heads_all;
     const bool fp8 = p.fp8_inv_scale != 0.0f;
-    for (uint32_t base = warp; base < n_items; base += KVE_WARPS * KVE_INFLIGHT) {
+    const uint32_t tk = warp;                                              // a warp takes all heads of one token
+    if (tk >= n_tok) return;
+    const long long slot = p.slot_mapping[token0 + tk];
+    if (slot < 0) return;                                                  // padding token
+    const uint16_t* const k_tok = p.k_in + size_t(token0 + tk) * p.in_row_stride;
+    const uint16_t* const v_tok = p.v_in ? p.v_in + size_t(token0 + tk) * p.in_row_stride : nullptr;
+    // page slot / block_size, offset slot % block_size in a cache of [pages, block_size, kv_heads, head_dim]: row `slot`
+    const size_t row_at = size_t(slot) * (size_t(p.kv_heads) * p.head_dim);
+    for (uint32_t h0 = 0; h0 < heads_all; h0 += KVE_INFLIGHT) {
         uint16_t raw[KVE_INFLIGHT][NG];
-        long long slot_r[KVE_INFLIGHT];
 #pragma unroll
         for (uint32_t r = 0; r < uint32_t(KVE_INFLIGHT); ++r) {
-            const uint32_t item = base + r * KVE_WARPS;
-            slot_r[r] = -1;
-            if (item >= n_items) continue;
-            const uint32_t tk = item / heads_all, h = item - tk * heads_all;
-            slot_r[r] = p.slot_mapping[token0 + tk];
-            if (slot_r[r] < 0) continue;                                   // padding token
-            const bool is_v = h >= p.kv_heads;
-            const uint16_t* src = (is_v ? p.v_in : p.k_in) + size_t(token0 + tk) * p.in_row_stride + size_t(is_v ? h - p.kv_heads : h) * p.head_dim;
+            const uint32_t h = h0 + r;
+            if (h >= heads_all) continue;
+            const uint16_t* src = h < p.kv_heads ? k_tok + h * p.head_dim : v_tok + (h - p.kv_heads) * p.head_dim;
 #pragma unroll
             for (uint32_t j = 0; j < NG; ++j)
                 if (j < n_grp) raw[r][j] = src[lane + 32u * j];
         }
 #pragma unroll
         for (uint32_t r = 0; r < uint32_t(KVE_INFLIGHT); ++r) {
-            const uint32_t item = base + r * KVE_WARPS;
-            if (item >= n_items || slot_r[r] < 0) continue;               // (warp-uniform)
-            const uint32_t tk = item / heads_all, h = item - tk * heads_all;
+            const uint32_t h = h0 + r;
+            if (h >= heads_all) continue;                                  // (warp-uniform)
             const bool is_v = h >= p.kv_heads;
             const uint32_t head = is_v ? h - p.kv_heads : h;
-            const long long slot = slot_r[r];
-            // page slot / block_size, offset slot % block_size in a cache of [pages, block_size, kv_heads, head_dim]: row `slot`
-            const size_t dst_at = size_t(slot) * (size_t(p.kv_heads) * p.head_dim) + size_t(head) * p.head_dim;
+            const size_t dst_at = row_at + head * p.head_dim;
             if (is_v) {
                 uint16_t* dst = p.v_cache + dst_at;
 #pragma unroll
