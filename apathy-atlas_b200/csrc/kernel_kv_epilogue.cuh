@@ -7,13 +7,14 @@
 // same chain ending in value * inv_scale cast to E4M3 with saturation: one block of head_dim threads per (token, head), K taken
 // from a contiguous [tokens, kv_heads, head_dim] copy) and the V side with a separate cache-write launch.  Here one
 // launch covers both and reads K and V where the projection left them — column ranges of the fused QKV output, with
-// its row stride — so no contiguous copies are made.  One warp works on one (token, head) at a time: lane l holds elements l, l+32,
-// l+64, ... of the head, so the sum of squares needs only shuffles and, for rotary_dim a multiple of 64, both
-// elements of every rotated pair (d, d + rotary_dim/2) sit in the same lane.
+// its row stride — so no contiguous copies are made.  A warp takes the heads of one token, one (token, head) at a time:
+// lane l holds elements l, l+32, l+64, ... of the head, so the sum of squares needs only shuffles and, for rotary_dim a
+// multiple of 64, both elements of every rotated pair (d, d + rotary_dim/2) sit in the same lane.
 //
 // The arithmetic follows the reference operation by operation, in FP32 with every product and sum rounded on its own
 // (the reference is built without FMA contraction) and in the reference's summation order — a butterfly over each
-// group of 32 consecutive elements, then a butterfly over the group sums — so that the result is the same BF16 bits.
+// group of 32 consecutive elements, then a butterfly over the group sums; `kve_group_total` walks the same tree with
+// fewer shuffles — so that the result is the same BF16 bits.
 #pragma once
 
 #include <cstdint>
@@ -24,7 +25,7 @@
 
 namespace atlas {
 
-constexpr int KVE_WARPS = 8;                 // warps per CTA; the (token, head) items of a CTA are dealt out to them
+constexpr int KVE_WARPS = 8;                 // warps per CTA
 constexpr int KVE_MAX_HEAD_DIM = 256;
 
 struct KvEpilogueParams {
@@ -107,7 +108,7 @@ kv_norm_rope_cache_kernel(KvEpilogueParams p) {
     // (token, pair) only, so the FP64 power is evaluated once per CTA and pair, the two transcendental calls once per
     // token and pair — the reference evaluates all three per element — and every head reads them from shared memory.
     // Same calls on the same arguments: same bits.  The op is a stream; what limits it is the latency of a head's chain
-    // (load, two butterflies, rsqrt, store), so a warp loads KVE_INFLIGHT heads before it works on the first.
+    // (load, group sums, rsqrt, store), so a warp loads KVE_INFLIGHT heads before it works on the first.
     __shared__ float cos_s[KVE_TOKENS][KVE_MAX_HEAD_DIM / 2], sin_s[KVE_TOKENS][KVE_MAX_HEAD_DIM / 2];
     __shared__ float freq_s[KVE_MAX_HEAD_DIM / 2];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -216,8 +217,9 @@ kv_norm_rope_cache_kernel(KvEpilogueParams p) {
 // (kernels/gb10/common/fused_verify_elemwise.cu:78-224): the normed head is rounded to BF16 before the rotation
 // (the chain it replaced stored it), the angle is position * inv_freq[pair] from a table, cosine and sine are scaled by
 // the attention factor (YaRN), and the weight is `w` or `1 + w`.  One warp per (token, head), Q, K and V read where the
-// projection wrote them (row strides given), the BF16 normed head staged in the warp's own shared-memory strip so that
-// a lane can read the partner element of its pair.
+// projection wrote them (row strides given).  A lane reads the partner element of its pair by one shuffle when
+// rotary_dim = 64 (the halves of a pair are then 16 lanes apart in the head's first 64 channels), otherwise from the
+// BF16 normed head staged in the warp's own shared-memory strip.
 //
 // Summation order of the reference (one block of head_dim threads, thread t squaring the packed pair (2t, 2t + 1), a
 // butterfly per warp, then a butterfly over the warp sums): group g of 64 elements = the reference's warp g, lane l of
